@@ -1,0 +1,156 @@
+/*
+ * nihilus_b200 -- C ABI of the B200 (sm_100a) Q8_0 mul_mat path.
+ *
+ * This is the boundary a Nihilus maintainer binds: plain C types, device pointers owned by the
+ * caller, no exceptions, no implicit device synchronisation.  Every entry point returns an int
+ * status (0 = ok, negative = error, text via nhb_last_error).  Each declaration cites the piece of
+ * the reference it stands in for (paths relative to the reference's include/nihilus-incl/).
+ *
+ * Conventions (same as the reference's tensors, infra/core_traits.hpp:145-182):
+ *   weight  W : N rows, each K/32 Q8_0 blocks of 34 bytes {fp16 d; int8 qs[32]}  (ne0 = K contiguous)
+ *   input   X : M rows of K floats, row m at x + m*ldx                             (ne0 = K contiguous)
+ *   output  Y : M rows of N floats, Y[m*ldy + n] = W[n,:] . X[m,:]                 (ne0 = N contiguous)
+ * A context owns one GPU and one row shard [n0, n1) of every weight it uploads; with world > 1 it
+ * writes only columns [n0, n1) of Y and nhb_all_gather completes the rows on every rank.
+ */
+#ifndef NIHILUS_B200_H
+#define NIHILUS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NHB_VERSION 100
+
+enum nhb_status {
+	NHB_OK				= 0,
+	NHB_ERR_ARG			= -1, /* null pointer, K not a multiple of 32, M < 0, bad leading dimension ... */
+	NHB_ERR_CUDA		= -2, /* a CUDA runtime call failed (text in nhb_last_error) */
+	NHB_ERR_NCCL		= -3,
+	NHB_ERR_TIMEOUT		= -4, /* a bounded device-side wait ran out; the context stays usable */
+	NHB_ERR_UNSUPPORTED = -5,
+	NHB_ERR_NOMEM		= -6
+};
+
+/* Which of the reference's two arithmetics to run (both exist in cpu/avx_2.hpp):
+ *   NHB_ACT_Q8  activations quantised to Q8_0 (quantize_row_q8_0, :4439-4489), exact int8 block dots, scales
+ *               applied per block (vec_dot_q8_0_q8_0, :4534-4780)
+ *   NHB_ACT_F32 f32 activations times dequantised weights (vec_dot_q8_f32, :4782-4852) */
+enum nhb_act_mode { NHB_ACT_Q8 = 0, NHB_ACT_F32 = 1 };
+
+/* kernel choice; AUTO picks from M (the reference picks by processing_phases, common/kernel_traits.hpp:114-117) */
+enum nhb_kernel {
+	NHB_KERNEL_AUTO		   = 0,
+	NHB_KERNEL_GEMV_LDG	   = 1, /* any K % 32 == 0: coalesced 128-bit loads, dp4a, warp-shuffle reduce */
+	NHB_KERNEL_GEMV_STREAM = 2, /* K % 256 == 0, K <= 16384: persistent CTAs fed by a bulk-copy (TMA) ring */
+	NHB_KERNEL_GEMM_TC	   = 3  /* tcgen05 / TMEM tensor-core contraction for prefill */
+};
+
+typedef struct nhb_ctx nhb_ctx;
+typedef struct nhb_weight nhb_weight;
+typedef struct nhb_graph nhb_graph;
+
+typedef struct nhb_weight_info {
+	int64_t N, K;	  /* full logical shape */
+	int64_t n0, n1;	  /* rows held by this context */
+	const void* q;	  /* device: int8 plane  [n1-n0][K], 256-byte aligned */
+	const void* d;	  /* device: fp16 plane  [n1-n0][K/32], 256-byte aligned */
+	int64_t bytes_q8; /* (n1-n0) * (K/32) * 34: the Q8_0 bytes this shard stands for */
+} nhb_weight_info;
+
+/* one independent mul_mat of a batch (no op of a batch may read another op's output) */
+typedef struct nhb_mul_mat_op {
+	const nhb_weight* w;
+	const float* x; /* device */
+	int64_t ldx;
+	float* y; /* device */
+	int64_t ldy;
+	int64_t M;
+} nhb_mul_mat_op;
+
+/* ---- library ---- */
+int nhb_version(void);
+/* compute capability the kernels were built for (100); replaces the build-time arch index of
+ * infra/monolithic_dispatcher.hpp:30-39, which has no entry for compute capability 10 */
+int nhb_arch(void);
+/* last error text of this thread (ctx may be NULL for errors raised before a context existed) */
+const char* nhb_last_error(const nhb_ctx* ctx);
+
+/* ---- host-only helpers (no GPU needed) ---- */
+/* rows [n0, n1) of an N-row weight owned by `rank` of `world`; the remainder goes to the lowest ranks.
+ * No counterpart in the reference (device 0 is hard-wired, cuda/common.hpp:36-40). */
+int nhb_shard_rows(int64_t N, int world, int rank, int64_t* n0, int64_t* n1);
+/* 34-byte blocks -> int8 plane + fp16 plane for rows [n0, n1); the layout nhb_weight_upload_q8_0 builds on the GPU */
+int nhb_repack_q8_0_host(const void* blocks34, int64_t N, int64_t K, int64_t n0, int64_t n1, int8_t* q_plane, uint16_t* d_plane);
+int nhb_unpack_q8_0_host(const int8_t* q_plane, const uint16_t* d_plane, int64_t rows, int64_t K, void* blocks34);
+/* GEMV (1), or GEMM (3) for this M?  The runtime form of the reference's compile-time eval/prompt split. */
+int nhb_choose_kernel(int64_t N, int64_t K, int64_t M, int act_mode);
+/* algorithmic bytes / flops of one mul_mat: N*(K/32)*34 + 4*M*K + 4*M*N and 2*M*N*K */
+int64_t nhb_mul_mat_bytes(int64_t N, int64_t K, int64_t M);
+int64_t nhb_mul_mat_flops(int64_t N, int64_t K, int64_t M);
+
+/* ---- context: replaces thread_pool<gpu> + memory_buffer<gpu> for this path (cuda/thread_pool.hpp:46-67,
+ *      cuda/memory_buffer.hpp:78-152) ---- */
+int nhb_ctx_create(nhb_ctx** out, int device, int rank, int world);
+int nhb_ctx_destroy(nhb_ctx* ctx);
+/* run everything on the caller's cudaStream_t (NULL = the context's own non-blocking stream) */
+int nhb_ctx_set_stream(nhb_ctx* ctx, void* cuda_stream);
+/* explicit synchronisation + device status check; the reference syncs after every launch (cuda/cuda_12.hpp:679) */
+int nhb_sync(nhb_ctx* ctx);
+/* largest M served by the GEMV family under NHB_KERNEL_AUTO (default 8) */
+int nhb_ctx_set_gemv_max_m(nhb_ctx* ctx, int max_m);
+/* tuning knobs: "pdl" (programmatic dependent launch, default 1), "ctas_per_sm" (1 or 2), "gemv_max_m" */
+int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value);
+/* kernels this context has launched so far (upload, mul_mat, gather ...) */
+long long nhb_ctx_launch_count(const nhb_ctx* ctx);
+/* asynchronous copies on the context stream: memory_transfer<gpu>::host_to_device / device_to_host
+ * (cuda/memory_buffer.hpp:33-74) without the blocking */
+int nhb_memcpy_h2d(nhb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int nhb_memcpy_d2h(nhb_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+
+/* ---- weights: replaces the verbatim 34-byte upload of infra/model_parser.hpp:151-154, :933-937 ---- */
+/* host_blocks34 = the tensor's bytes as they sit in the GGUF file (N*(K/32)*34 bytes, whole tensor);
+ * only this context's row shard is copied to the GPU and repacked there into the two planes. */
+int nhb_weight_upload_q8_0(nhb_ctx* ctx, const void* host_blocks34, int64_t N, int64_t K, nhb_weight** out);
+int nhb_weight_free(nhb_ctx* ctx, nhb_weight* w);
+int nhb_weight_info_get(const nhb_weight* w, nhb_weight_info* info);
+/* planes back to 34-byte blocks on the host (rows n0..n1 only) -- for round-trip checks */
+int nhb_weight_download_q8_0(nhb_ctx* ctx, const nhb_weight* w, void* host_blocks34_shard);
+
+/* ---- the operator: fills the empty GPU cores of cuda/cuda_12.hpp:803-952; arithmetic of cpu/avx_2.hpp:4749-5004 ---- */
+int nhb_mul_mat(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev, int64_t ldx, float* y_dev, int64_t ldy, int64_t M, int act_mode,
+	int kernel);
+/* several independent mul_mats (q/k/v of one layer, gate/up of one layer ...) in one persistent launch */
+int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int act_mode, int kernel);
+/* same operator with HOST activations and outputs: copies X up, runs, copies this shard's Y columns back
+ * (asynchronous on the context stream; the buffers must stay valid until nhb_sync) */
+int nhb_mul_mat_host(nhb_ctx* ctx, const nhb_weight* w, const float* x_host, int64_t ldx, float* y_host, int64_t ldy, int64_t M,
+	int act_mode, int kernel);
+/* exact per-block int32 dots of the Q8 arithmetic: dots[((m*rows)+r)*(K/32)+b] for this shard's rows */
+int nhb_mul_mat_block_dots(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev, int64_t ldx, int64_t M, int32_t* dots_dev);
+/* the activation quantiser alone (quantize_row_q8_0, cpu/avx_2.hpp:4439-4489): int8 [M][K] and f32 scales
+ * (the fp16-rounded d, widened) [M][K/32] */
+int nhb_quantize_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, int64_t M, int64_t K, int8_t* q_dev, float* d_dev);
+
+/* ---- launch-overhead removal: record a sequence of nhb_mul_mat* calls once, replay it per token ---- */
+int nhb_graph_begin(nhb_ctx* ctx);
+int nhb_graph_end(nhb_ctx* ctx, nhb_graph** out);
+int nhb_graph_launch(nhb_ctx* ctx, nhb_graph* g);
+int nhb_graph_free(nhb_ctx* ctx, nhb_graph* g);
+
+/* ---- multi-GPU (one context per GPU / per process); no counterpart in the reference ---- */
+/* 128-byte NCCL unique id made by rank 0 and handed to every rank by the caller's own transport */
+int nhb_comm_unique_id(void* id128);
+int nhb_comm_init(nhb_ctx* ctx, const void* id128);
+/* complete Y[M][N] (ldy) on every rank from the column slices each rank wrote */
+int nhb_all_gather(nhb_ctx* ctx, float* y_dev, int64_t ldy, int64_t M, int64_t N);
+/* several outputs in one grouped collective (q/k/v, gate/up) */
+int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, const int64_t* M, const int64_t* N, int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,295 @@
+"""ctypes binding of libnihilus_b200.so (see include/nihilus_b200.h) plus small torch conveniences.
+
+No fallback: if the shared library is absent this module raises at import, and every call below runs
+the CUDA kernels through the C ABI.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libnihilus_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m nihilus_b200.build` (nvcc, sm_100a). "
+        "nihilus_b200 has no CPU or PyTorch fallback."
+    )
+
+lib = C.CDLL(LIB_PATH)
+
+ACT_Q8, ACT_F32 = 0, 1
+KERNEL_AUTO, KERNEL_GEMV_LDG, KERNEL_GEMV_STREAM, KERNEL_GEMM_TC = 0, 1, 2, 3
+OK, ERR_ARG, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NOMEM = 0, -1, -2, -3, -4, -5, -6
+
+# every symbol include/nihilus_b200.h declares
+EXPORTS = (
+    "nhb_version", "nhb_arch", "nhb_last_error", "nhb_shard_rows", "nhb_repack_q8_0_host", "nhb_unpack_q8_0_host",
+    "nhb_choose_kernel", "nhb_mul_mat_bytes", "nhb_mul_mat_flops", "nhb_ctx_create", "nhb_ctx_destroy", "nhb_ctx_set_stream",
+    "nhb_sync", "nhb_ctx_set_gemv_max_m", "nhb_ctx_set_option", "nhb_ctx_launch_count", "nhb_memcpy_h2d", "nhb_memcpy_d2h",
+    "nhb_weight_upload_q8_0", "nhb_weight_free", "nhb_weight_info_get", "nhb_weight_download_q8_0", "nhb_mul_mat",
+    "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
+    "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
+)
+
+
+class WeightInfo(C.Structure):
+    _fields_ = [("N", C.c_int64), ("K", C.c_int64), ("n0", C.c_int64), ("n1", C.c_int64), ("q", C.c_void_p), ("d", C.c_void_p),
+                ("bytes_q8", C.c_int64)]
+
+
+class MulMatOp(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("x", C.c_void_p), ("ldx", C.c_int64), ("y", C.c_void_p), ("ldy", C.c_int64), ("M", C.c_int64)]
+
+
+def _sig(name, restype, *argtypes):
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = list(argtypes)
+    return fn
+
+
+_vp, _i, _i64 = C.c_void_p, C.c_int, C.c_int64
+_sig("nhb_version", _i)
+_sig("nhb_arch", _i)
+_sig("nhb_last_error", C.c_char_p, _vp)
+_sig("nhb_shard_rows", _i, _i64, _i, _i, C.POINTER(_i64), C.POINTER(_i64))
+_sig("nhb_repack_q8_0_host", _i, _vp, _i64, _i64, _i64, _i64, _vp, _vp)
+_sig("nhb_unpack_q8_0_host", _i, _vp, _vp, _i64, _i64, _vp)
+_sig("nhb_choose_kernel", _i, _i64, _i64, _i64, _i)
+_sig("nhb_mul_mat_bytes", _i64, _i64, _i64, _i64)
+_sig("nhb_mul_mat_flops", _i64, _i64, _i64, _i64)
+_sig("nhb_ctx_create", _i, C.POINTER(_vp), _i, _i, _i)
+_sig("nhb_ctx_destroy", _i, _vp)
+_sig("nhb_ctx_set_stream", _i, _vp, _vp)
+_sig("nhb_sync", _i, _vp)
+_sig("nhb_ctx_set_gemv_max_m", _i, _vp, _i)
+_sig("nhb_ctx_set_option", _i, _vp, C.c_char_p, _i)
+_sig("nhb_ctx_launch_count", C.c_longlong, _vp)
+_sig("nhb_memcpy_h2d", _i, _vp, _vp, _vp, C.c_size_t)
+_sig("nhb_memcpy_d2h", _i, _vp, _vp, _vp, C.c_size_t)
+_sig("nhb_weight_upload_q8_0", _i, _vp, _vp, _i64, _i64, C.POINTER(_vp))
+_sig("nhb_weight_free", _i, _vp, _vp)
+_sig("nhb_weight_info_get", _i, _vp, C.POINTER(WeightInfo))
+_sig("nhb_weight_download_q8_0", _i, _vp, _vp, _vp)
+_sig("nhb_mul_mat", _i, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i, _i)
+_sig("nhb_mul_mat_batch", _i, _vp, C.POINTER(MulMatOp), _i, _i, _i)
+_sig("nhb_mul_mat_host", _i, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i, _i)
+_sig("nhb_mul_mat_block_dots", _i, _vp, _vp, _vp, _i64, _i64, _vp)
+_sig("nhb_quantize_q8_0", _i, _vp, _vp, _i64, _i64, _i64, _vp, _vp)
+_sig("nhb_graph_begin", _i, _vp)
+_sig("nhb_graph_end", _i, _vp, C.POINTER(_vp))
+_sig("nhb_graph_launch", _i, _vp, _vp)
+_sig("nhb_graph_free", _i, _vp, _vp)
+_sig("nhb_comm_unique_id", _i, _vp)
+_sig("nhb_comm_init", _i, _vp, _vp)
+_sig("nhb_all_gather", _i, _vp, _vp, _i64, _i64, _i64)
+_sig("nhb_all_gather_batch", _i, _vp, C.POINTER(_vp), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), _i)
+
+
+class NhbError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"nihilus_b200 error {code}: {msg}")
+        self.code = code
+
+
+def last_error(ctx=None) -> str:
+    s = lib.nhb_last_error(ctx)
+    return s.decode() if s else ""
+
+
+def _check(rc: int, ctx=None):
+    if rc != OK:
+        raise NhbError(rc, last_error(ctx))
+
+
+def shard_rows(N: int, world: int, rank: int) -> tuple[int, int]:
+    a, b = _i64(), _i64()
+    _check(lib.nhb_shard_rows(N, world, rank, C.byref(a), C.byref(b)))
+    return a.value, b.value
+
+
+def repack_host(blocks: np.ndarray, n0: int = 0, n1: int | None = None):
+    """uint8 [N, K/32, 34] -> (int8 [rows, K], uint16 [rows, K/32]) on the host (no GPU)."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    N, nb, _ = blocks.shape
+    n1 = N if n1 is None else n1
+    q = np.empty((max(n1 - n0, 0), nb * 32), dtype=np.int8)
+    d = np.empty((max(n1 - n0, 0), nb), dtype=np.uint16)
+    _check(lib.nhb_repack_q8_0_host(blocks.ctypes.data, N, nb * 32, n0, n1, q.ctypes.data, d.ctypes.data))
+    return q, d
+
+
+def unpack_host(q: np.ndarray, d: np.ndarray) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.int8)
+    d = np.ascontiguousarray(d, dtype=np.uint16)
+    rows, K = q.shape
+    out = np.empty((rows, K // 32, 34), dtype=np.uint8)
+    _check(lib.nhb_unpack_q8_0_host(q.ctypes.data, d.ctypes.data, rows, K, out.ctypes.data))
+    return out
+
+
+class Weight:
+    def __init__(self, ctx: "Context", handle: int):
+        self.ctx = ctx
+        self.handle = handle
+        info = WeightInfo()
+        _check(lib.nhb_weight_info_get(handle, C.byref(info)))
+        self.N, self.K, self.n0, self.n1 = info.N, info.K, info.n0, info.n1
+        self.q_ptr, self.d_ptr, self.bytes_q8 = info.q, info.d, info.bytes_q8
+
+    def download(self) -> np.ndarray:
+        out = np.empty((self.n1 - self.n0, self.K // 32, 34), dtype=np.uint8)
+        _check(lib.nhb_weight_download_q8_0(self.ctx.handle, self.handle, out.ctypes.data), self.ctx.handle)
+        return out
+
+    def free(self):
+        if self.handle:
+            lib.nhb_weight_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+class Graph:
+    def __init__(self, ctx: "Context", handle: int):
+        self.ctx, self.handle = ctx, handle
+
+    def launch(self):
+        _check(lib.nhb_graph_launch(self.ctx.handle, self.handle), self.ctx.handle)
+
+    def free(self):
+        if self.handle:
+            lib.nhb_graph_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+class Context:
+    """One GPU, one row shard (rank of world)."""
+
+    def __init__(self, device: int = 0, rank: int = 0, world: int = 1):
+        h = _vp()
+        _check(lib.nhb_ctx_create(C.byref(h), device, rank, world))
+        self.handle = h.value
+        self.device, self.rank, self.world = device, rank, world
+
+    def close(self):
+        if self.handle:
+            lib.nhb_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def set_stream(self, cuda_stream: int | None):
+        _check(lib.nhb_ctx_set_stream(self.handle, cuda_stream), self.handle)
+
+    def set_option(self, name: str, value: int):
+        _check(lib.nhb_ctx_set_option(self.handle, name.encode(), value), self.handle)
+
+    def sync(self):
+        _check(lib.nhb_sync(self.handle), self.handle)
+
+    @property
+    def launches(self) -> int:
+        return int(lib.nhb_ctx_launch_count(self.handle))
+
+    def upload(self, blocks: np.ndarray) -> Weight:
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        N, nb, bb = blocks.shape
+        assert bb == 34
+        h = _vp()
+        _check(lib.nhb_weight_upload_q8_0(self.handle, blocks.ctypes.data, N, nb * 32, C.byref(h)), self.handle)
+        return Weight(self, h.value)
+
+    # ---- device-pointer level (torch tensors supply the memory) ----
+    def mul_mat(self, w: Weight, x, y=None, act_mode: int = ACT_Q8, kernel: int = KERNEL_AUTO):
+        """x: torch cuda f32 [M, K] (row stride allowed) -> y f32 [M, N] (this shard's columns written)."""
+        import torch
+
+        M = x.shape[0]
+        if y is None:
+            y = torch.zeros((M, w.N), dtype=torch.float32, device=x.device)
+        _check(lib.nhb_mul_mat(self.handle, w.handle, x.data_ptr(), x.stride(0) if M > 0 else w.K, y.data_ptr(),
+                               y.stride(0) if M > 0 else max(w.N, 1), M, act_mode, kernel), self.handle)
+        return y
+
+    def mul_mat_batch(self, ops, act_mode: int = ACT_Q8, kernel: int = KERNEL_AUTO):
+        """ops: list of (Weight, x, y) torch tensors."""
+        arr = (MulMatOp * len(ops))()
+        for i, (w, x, y) in enumerate(ops):
+            arr[i] = MulMatOp(w.handle, x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.shape[0])
+        _check(lib.nhb_mul_mat_batch(self.handle, arr, len(ops), act_mode, kernel), self.handle)
+
+    def mul_mat_host(self, w: Weight, x: np.ndarray, y: np.ndarray | None = None, act_mode: int = ACT_Q8, kernel: int = KERNEL_AUTO,
+                     sync: bool = True) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        if x.ndim == 1:
+            x = x[None, :]
+        M = x.shape[0]
+        if y is None:
+            y = np.zeros((M, w.N), dtype=np.float32)
+        _check(lib.nhb_mul_mat_host(self.handle, w.handle, x.ctypes.data, x.shape[1], y.ctypes.data, max(w.N, 1), M, act_mode, kernel),
+               self.handle)
+        if sync:
+            self.sync()
+        return y
+
+    def block_dots(self, w: Weight, x):
+        import torch
+
+        M = x.shape[0]
+        out = torch.zeros((M, w.n1 - w.n0, w.K // 32), dtype=torch.int32, device=x.device)
+        _check(lib.nhb_mul_mat_block_dots(self.handle, w.handle, x.data_ptr(), x.stride(0), M, out.data_ptr()), self.handle)
+        return out
+
+    def quantize(self, x):
+        import torch
+
+        M, K = x.shape
+        q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+        d = torch.empty((M, K // 32), dtype=torch.float32, device=x.device)
+        _check(lib.nhb_quantize_q8_0(self.handle, x.data_ptr(), x.stride(0), M, K, q.data_ptr(), d.data_ptr()), self.handle)
+        return q, d
+
+    def memcpy_h2d(self, dst_ptr: int, src_ptr: int, nbytes: int):
+        _check(lib.nhb_memcpy_h2d(self.handle, dst_ptr, src_ptr, nbytes), self.handle)
+
+    def memcpy_d2h(self, dst_ptr: int, src_ptr: int, nbytes: int):
+        _check(lib.nhb_memcpy_d2h(self.handle, dst_ptr, src_ptr, nbytes), self.handle)
+
+    # ---- graphs ----
+    def graph_begin(self):
+        _check(lib.nhb_graph_begin(self.handle), self.handle)
+
+    def graph_end(self) -> Graph:
+        h = _vp()
+        _check(lib.nhb_graph_end(self.handle, C.byref(h)), self.handle)
+        return Graph(self, h.value)
+
+    # ---- multi-GPU ----
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        _check(lib.nhb_comm_unique_id(buf))
+        return buf.raw
+
+    def comm_init(self, uid: bytes):
+        buf = C.create_string_buffer(uid, 128)
+        _check(lib.nhb_comm_init(self.handle, buf), self.handle)
+
+    def all_gather(self, y):
+        M, N = y.shape
+        _check(lib.nhb_all_gather(self.handle, y.data_ptr(), y.stride(0), M, N), self.handle)
+
+    def all_gather_batch(self, ys):
+        n = len(ys)
+        ptrs = (_vp * n)(*[y.data_ptr() for y in ys])
+        ld = (_i64 * n)(*[y.stride(0) for y in ys])
+        ms = (_i64 * n)(*[y.shape[0] for y in ys])
+        ns = (_i64 * n)(*[y.shape[1] for y in ys])
+        _check(lib.nhb_all_gather_batch(self.handle, ptrs, ld, ms, ns, n), self.handle)

@@ -1,0 +1,827 @@
+// extern "C" layer of libnihilus_b200.so: contexts, weight upload + repack + row sharding, the mul_mat
+// dispatch by M, graphs, NCCL all-gather.  Host code only; kernels live in gemv.cu, gemm_tc.cu, repack.cu.
+//
+// There is deliberately no CPU fallback: when a CUDA call fails the entry point returns NHB_ERR_CUDA.
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "internal.h"
+
+using namespace nhb;
+
+// ---------------------------------------------------------------------------------------------------------------
+// NCCL is bound at run time (dlopen) so that the library loads on machines without it and shares the copy a host
+// process (e.g. PyTorch) has already loaded.
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+	typedef struct ncclComm* ncclComm_t;
+	struct nccl_uid {
+		char internal[128];
+	};
+	enum { nccl_float = 7, nccl_success = 0 };
+
+	struct nccl_api {
+		void* handle											  = nullptr;
+		int (*GetUniqueId)(nccl_uid*)							  = nullptr;
+		int (*CommInitRank)(ncclComm_t*, int, nccl_uid, int)	  = nullptr;
+		int (*CommDestroy)(ncclComm_t)							  = nullptr;
+		int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t)	   = nullptr;
+		int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+		int (*GroupStart)()										  = nullptr;
+		int (*GroupEnd)()										  = nullptr;
+		const char* (*GetErrorString)(int)						  = nullptr;
+		bool ok													  = false;
+	};
+
+	nccl_api& nccl() {
+		static nccl_api api;
+		static std::once_flag once;
+		std::call_once(once, [] {
+			const char* names[] = { "libnccl.so.2", "libnccl.so" };
+			for (const char* n: names) {
+				api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+				if (api.handle)
+					break;
+			}
+			if (!api.handle)
+				return;
+#define NHB_SYM(field, name) api.field = reinterpret_cast<decltype(api.field)>(dlsym(api.handle, name))
+			NHB_SYM(GetUniqueId, "ncclGetUniqueId");
+			NHB_SYM(CommInitRank, "ncclCommInitRank");
+			NHB_SYM(CommDestroy, "ncclCommDestroy");
+			NHB_SYM(AllGather, "ncclAllGather");
+			NHB_SYM(Broadcast, "ncclBroadcast");
+			NHB_SYM(GroupStart, "ncclGroupStart");
+			NHB_SYM(GroupEnd, "ncclGroupEnd");
+			NHB_SYM(GetErrorString, "ncclGetErrorString");
+#undef NHB_SYM
+			api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.Broadcast && api.GroupStart && api.GroupEnd;
+		});
+		return api;
+	}
+
+	thread_local std::string g_err;
+
+}
+
+struct nhb_ctx {
+	int device		   = 0;
+	int rank		   = 0;
+	int world		   = 1;
+	int sm_count	   = 148;
+	cudaStream_t own   = nullptr;
+	cudaStream_t stream = nullptr;
+	int* dev_status	   = nullptr;
+	int* host_status   = nullptr;// pinned
+	void* scratch	   = nullptr;
+	size_t scratch_cap = 0;
+	void* io		   = nullptr;
+	size_t io_cap	   = 0;
+	ncclComm_t comm	   = nullptr;
+	bool pdl		   = true;
+	int gemv_max_m	   = 8;
+	int ctas_per_sm	   = 1;
+	bool capturing	   = false;
+	long long launches = 0;
+	std::string err;
+};
+
+struct nhb_weight {
+	int64_t N = 0, K = 0, n0 = 0, n1 = 0;
+	int8_t* q  = nullptr;
+	__half* d  = nullptr;
+	int device = 0;
+};
+
+struct nhb_graph {
+	cudaGraph_t graph	 = nullptr;
+	cudaGraphExec_t exec = nullptr;
+};
+
+namespace {
+
+	int fail(nhb_ctx* ctx, int code, const std::string& msg) {
+		g_err = msg;
+		if (ctx)
+			ctx->err = msg;
+		return code;
+	}
+
+	int fail_cuda(nhb_ctx* ctx, cudaError_t e, const char* what) {
+		return fail(ctx, NHB_ERR_CUDA, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+	}
+
+#define NHB_CUDA(ctx, call) \
+	do { \
+		cudaError_t e__ = (call); \
+		if (e__ != cudaSuccess) \
+			return fail_cuda(ctx, e__, #call); \
+	} while (0)
+
+	struct device_guard {
+		int prev = -1;
+		bool ok	 = true;
+		explicit device_guard(int dev) {
+			if (cudaGetDevice(&prev) != cudaSuccess) {
+				ok = false;
+				return;
+			}
+			if (prev != dev && cudaSetDevice(dev) != cudaSuccess)
+				ok = false;
+		}
+		~device_guard() {
+			if (prev >= 0)
+				cudaSetDevice(prev);
+		}
+	};
+
+	int env_int(const char* name, int dflt) {
+		const char* v = std::getenv(name);
+		return (v && *v) ? std::atoi(v) : dflt;
+	}
+
+	launch_cfg cfg_of(nhb_ctx* ctx) {
+		launch_cfg c;
+		c.stream	 = ctx->stream;
+		c.sm_count	 = ctx->sm_count;
+		c.pdl		 = ctx->pdl;
+		c.dev_status = ctx->dev_status;
+		return c;
+	}
+
+	int ensure(nhb_ctx* ctx, void** buf, size_t* cap, size_t need, const char* what) {
+		if (need <= *cap)
+			return NHB_OK;
+		if (ctx->capturing)
+			return fail(ctx, NHB_ERR_UNSUPPORTED, std::string(what) + " must grow during graph capture; run the same calls once before nhb_graph_begin");
+		NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+		if (*buf)
+			NHB_CUDA(ctx, cudaFree(*buf));
+		*buf = nullptr;
+		*cap = 0;
+		need = (need + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+		NHB_CUDA(ctx, cudaMalloc(buf, need));
+		*cap = need;
+		return NHB_OK;
+	}
+
+	int check_mm_args(nhb_ctx* ctx, const nhb_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy, int64_t M) {
+		if (!ctx || !w)
+			return fail(ctx, NHB_ERR_ARG, "null context or weight");
+		if (w->device != ctx->device)
+			return fail(ctx, NHB_ERR_ARG, "weight was uploaded through a context of another device");
+		if (M < 0)
+			return fail(ctx, NHB_ERR_ARG, "M < 0");
+		if (M == 0)
+			return NHB_OK;
+		if (!x || !y)
+			return fail(ctx, NHB_ERR_ARG, "null activation or output pointer");
+		if (ldx < w->K || ldy < w->N)
+			return fail(ctx, NHB_ERR_ARG, "leading dimension smaller than the row length");
+		if ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx & 3))
+			return fail(ctx, NHB_ERR_ARG, "activations must be 16-byte aligned with ldx a multiple of 4");
+		if (M > (int64_t(1) << 20))
+			return fail(ctx, NHB_ERR_ARG, "M too large");
+		return NHB_OK;
+	}
+
+	// GEMV family over M rows (looping over row groups the kernels support)
+	int run_gemv(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int act_mode, int kernel) {
+		const int64_t M = ops[0].M;
+		launch_cfg cfg	= cfg_of(ctx);
+		int launches	= 0;
+		bool stream_ok	= act_mode == NHB_ACT_Q8 && kernel != NHB_KERNEL_GEMV_LDG;
+		for (int i = 0; i < n_ops && stream_ok; ++i)
+			stream_ok = gemv_stream_supports(ops[i].w->K, 1);
+		if (kernel == NHB_KERNEL_GEMV_STREAM && !stream_ok)
+			return fail(ctx, NHB_ERR_UNSUPPORTED, "streaming GEMV needs Q8 activations, K % 256 == 0 and 1024 <= K <= 16384");
+		if (stream_ok) {
+			int64_t kmax = 0;
+			for (int i = 0; i < n_ops; ++i)
+				kmax = std::max<int64_t>(kmax, ops[i].w->K);
+			int mt_max = 1;
+			while (mt_max < 8 && gemv_stream_supports(kmax, mt_max + 1))
+				++mt_max;
+			for (int64_t m0 = 0; m0 < M; m0 += mt_max) {
+				const int mt = static_cast<int>(std::min<int64_t>(mt_max, M - m0));
+				stream_batch b{};
+				b.n_ops = 0;
+				for (int i = 0; i < n_ops; ++i) {
+					const nhb_weight* w = ops[i].w;
+					if (w->n1 == w->n0)
+						continue;
+					stream_op& so = b.op[b.n_ops++];
+					so.wq		  = w->q;
+					so.wd		  = w->d;
+					so.x		  = ops[i].x + m0 * ops[i].ldx;
+					so.y		  = ops[i].y + m0 * ops[i].ldy + w->n0;
+					so.ldx		  = ops[i].ldx;
+					so.ldy		  = ops[i].ldy;
+					so.rows		  = static_cast<int>(w->n1 - w->n0);
+					so.K		  = static_cast<int>(w->K);
+				}
+				if (b.n_ops == 0)
+					break;
+				cudaError_t e = launch_gemv_stream(b, mt, cfg, ctx->ctas_per_sm, &launches);
+				if (e != cudaSuccess)
+					return fail_cuda(ctx, e, "gemv_q8_stream launch");
+			}
+		} else {
+			for (int i = 0; i < n_ops; ++i) {
+				const nhb_weight* w = ops[i].w;
+				const int rows		= static_cast<int>(w->n1 - w->n0);
+				if (rows == 0)
+					continue;
+				const int mt_max = gemv_ldg_max_m(w->K, act_mode);
+				if (mt_max < 1)
+					return fail(ctx, NHB_ERR_UNSUPPORTED, "K too large for the GEMV fallback's shared memory");
+				for (int64_t m0 = 0; m0 < M; m0 += mt_max) {
+					const int mt  = static_cast<int>(std::min<int64_t>(mt_max, M - m0));
+					cudaError_t e = launch_gemv_ldg(w->q, w->d, ops[i].x + m0 * ops[i].ldx, ops[i].ldx, ops[i].y + m0 * ops[i].ldy + w->n0, ops[i].ldy, rows,
+						static_cast<int>(w->K), mt, act_mode, cfg, &launches);
+					if (e != cudaSuccess)
+						return fail_cuda(ctx, e, "gemv_q8_ldg launch");
+				}
+			}
+		}
+		ctx->launches += launches;
+		return NHB_OK;
+	}
+
+	int run_gemm(nhb_ctx* ctx, const nhb_mul_mat_op& op) {
+		const nhb_weight* w = op.w;
+		const int rows		= static_cast<int>(w->n1 - w->n0);
+		if (rows == 0)
+			return NHB_OK;
+		const size_t need = gemm_tc_scratch_bytes(w->K, op.M);
+		int rc			  = ensure(ctx, &ctx->scratch, &ctx->scratch_cap, need, "GEMM scratch");
+		if (rc != NHB_OK)
+			return rc;
+		int launches = 0;
+		std::string err;
+		cudaError_t e = launch_gemm_tc(w->q, w->d, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
+			cfg_of(ctx), &launches, &err);
+		ctx->launches += launches;
+		if (e != cudaSuccess)
+			return fail_cuda(ctx, e, err.empty() ? "gemm_q8_tc launch" : err.c_str());
+		return NHB_OK;
+	}
+
+}
+
+extern "C" {
+
+int nhb_version(void) {
+	return NHB_VERSION;
+}
+
+int nhb_arch(void) {
+	return 100;
+}
+
+const char* nhb_last_error(const nhb_ctx* ctx) {
+	if (ctx && !ctx->err.empty())
+		return ctx->err.c_str();
+	return g_err.c_str();
+}
+
+int nhb_shard_rows(int64_t N, int world, int rank, int64_t* n0, int64_t* n1) {
+	if (N < 0 || world < 1 || rank < 0 || rank >= world || !n0 || !n1)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_shard_rows: bad arguments");
+	const int64_t base = N / world, rem = N % world;
+	*n0 = rank * base + std::min<int64_t>(rank, rem);
+	*n1 = *n0 + base + (rank < rem ? 1 : 0);
+	return NHB_OK;
+}
+
+int nhb_repack_q8_0_host(const void* blocks34, int64_t N, int64_t K, int64_t n0, int64_t n1, int8_t* q_plane, uint16_t* d_plane) {
+	if (!blocks34 || !q_plane || !d_plane || N < 0 || K <= 0 || K % 32 != 0 || n0 < 0 || n1 > N || n0 > n1)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_repack_q8_0_host: bad arguments");
+	const int64_t nb   = K / 32;
+	const uint8_t* src = static_cast<const uint8_t*>(blocks34) + n0 * nb * 34;
+	for (int64_t i = 0; i < (n1 - n0) * nb; ++i) {
+		std::memcpy(&d_plane[i], src + i * 34, 2);
+		std::memcpy(q_plane + i * 32, src + i * 34 + 2, 32);
+	}
+	return NHB_OK;
+}
+
+int nhb_unpack_q8_0_host(const int8_t* q_plane, const uint16_t* d_plane, int64_t rows, int64_t K, void* blocks34) {
+	if (!blocks34 || !q_plane || !d_plane || rows < 0 || K <= 0 || K % 32 != 0)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_unpack_q8_0_host: bad arguments");
+	uint8_t* dst = static_cast<uint8_t*>(blocks34);
+	for (int64_t i = 0; i < rows * (K / 32); ++i) {
+		std::memcpy(dst + i * 34, &d_plane[i], 2);
+		std::memcpy(dst + i * 34 + 2, q_plane + i * 32, 32);
+	}
+	return NHB_OK;
+}
+
+int nhb_choose_kernel(int64_t N, int64_t K, int64_t M, int act_mode) {
+	(void)N;
+	if (act_mode == NHB_ACT_F32)
+		return NHB_KERNEL_GEMV_LDG;
+	if (M <= 8)
+		return gemv_stream_supports(K, 1) ? NHB_KERNEL_GEMV_STREAM : NHB_KERNEL_GEMV_LDG;
+	return NHB_KERNEL_GEMM_TC;
+}
+
+int64_t nhb_mul_mat_bytes(int64_t N, int64_t K, int64_t M) {
+	return N * (K / 32) * 34 + 4 * M * K + 4 * M * N;
+}
+
+int64_t nhb_mul_mat_flops(int64_t N, int64_t K, int64_t M) {
+	return 2 * M * N * K;
+}
+
+int nhb_ctx_create(nhb_ctx** out, int device, int rank, int world) {
+	if (!out || world < 1 || rank < 0 || rank >= world || device < 0)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_ctx_create: bad arguments");
+	*out = nullptr;
+	int n_dev = 0;
+	NHB_CUDA(nullptr, cudaGetDeviceCount(&n_dev));
+	if (device >= n_dev)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_ctx_create: no such device");
+	device_guard g(device);
+	if (!g.ok)
+		return fail(nullptr, NHB_ERR_CUDA, "cudaSetDevice failed");
+	cudaDeviceProp prop{};
+	NHB_CUDA(nullptr, cudaGetDeviceProperties(&prop, device));
+	if (prop.major != 10)
+		return fail(nullptr, NHB_ERR_UNSUPPORTED, "this library holds sm_100a code only; device is compute capability " + std::to_string(prop.major) + "." + std::to_string(prop.minor));
+	nhb_ctx* ctx  = new nhb_ctx();
+	ctx->device	  = device;
+	ctx->rank	  = rank;
+	ctx->world	  = world;
+	ctx->sm_count = prop.multiProcessorCount;
+	cudaError_t e = cudaStreamCreateWithFlags(&ctx->own, cudaStreamNonBlocking);
+	if (e == cudaSuccess)
+		e = cudaMalloc(&ctx->dev_status, NHB_STATUS_WORDS * sizeof(int));
+	if (e == cudaSuccess)
+		e = cudaMemset(ctx->dev_status, 0, NHB_STATUS_WORDS * sizeof(int));
+	if (e == cudaSuccess)
+		e = cudaMallocHost(&ctx->host_status, NHB_STATUS_WORDS * sizeof(int));
+	if (e != cudaSuccess) {
+		int rc = fail_cuda(nullptr, e, "nhb_ctx_create");
+		if (ctx->own)
+			cudaStreamDestroy(ctx->own);
+		if (ctx->dev_status)
+			cudaFree(ctx->dev_status);
+		delete ctx;
+		return rc;
+	}
+	ctx->stream		 = ctx->own;
+	ctx->pdl		 = env_int("NHB_PDL", 1) != 0;
+	ctx->gemv_max_m	 = env_int("NHB_GEMV_MAX_M", 8);
+	ctx->ctas_per_sm = env_int("NHB_CTAS_PER_SM", 1);
+	*out			 = ctx;
+	return NHB_OK;
+}
+
+int nhb_ctx_destroy(nhb_ctx* ctx) {
+	if (!ctx)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	cudaStreamSynchronize(ctx->stream);
+	if (ctx->comm && nccl().ok)
+		nccl().CommDestroy(ctx->comm);
+	if (ctx->scratch)
+		cudaFree(ctx->scratch);
+	if (ctx->io)
+		cudaFree(ctx->io);
+	if (ctx->dev_status)
+		cudaFree(ctx->dev_status);
+	if (ctx->host_status)
+		cudaFreeHost(ctx->host_status);
+	if (ctx->own)
+		cudaStreamDestroy(ctx->own);
+	delete ctx;
+	return NHB_OK;
+}
+
+int nhb_ctx_set_stream(nhb_ctx* ctx, void* cuda_stream) {
+	if (!ctx)
+		return fail(nullptr, NHB_ERR_ARG, "null context");
+	ctx->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->own;
+	return NHB_OK;
+}
+
+int nhb_ctx_set_gemv_max_m(nhb_ctx* ctx, int max_m) {
+	if (!ctx || max_m < 1)
+		return fail(ctx, NHB_ERR_ARG, "nhb_ctx_set_gemv_max_m: bad arguments");
+	ctx->gemv_max_m = max_m;
+	return NHB_OK;
+}
+
+int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
+	if (!ctx || !name)
+		return fail(ctx, NHB_ERR_ARG, "nhb_ctx_set_option: bad arguments");
+	if (!std::strcmp(name, "pdl"))
+		ctx->pdl = value != 0;
+	else if (!std::strcmp(name, "ctas_per_sm"))
+		ctx->ctas_per_sm = value < 1 ? 1 : (value > 2 ? 2 : value);
+	else if (!std::strcmp(name, "gemv_max_m"))
+		ctx->gemv_max_m = value < 1 ? 1 : value;
+	else
+		return fail(ctx, NHB_ERR_ARG, std::string("unknown option ") + name);
+	return NHB_OK;
+}
+
+long long nhb_ctx_launch_count(const nhb_ctx* ctx) {
+	return ctx ? ctx->launches : 0;
+}
+
+int nhb_sync(nhb_ctx* ctx) {
+	if (!ctx)
+		return fail(nullptr, NHB_ERR_ARG, "null context");
+	device_guard g(ctx->device);
+	NHB_CUDA(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, NHB_STATUS_WORDS * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+	NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+	if (ctx->host_status[0] != DEV_OK) {
+		const int code = ctx->host_status[0];
+		cudaMemsetAsync(ctx->dev_status, 0, NHB_STATUS_WORDS * sizeof(int), ctx->stream);
+		cudaStreamSynchronize(ctx->stream);
+		return fail(ctx, NHB_ERR_TIMEOUT, "a device-side wait ran out (code " + std::to_string(code) + "); results of the last launches are invalid");
+	}
+	return NHB_OK;
+}
+
+int nhb_memcpy_h2d(nhb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
+	if (!ctx || (bytes && (!dst_dev || !src_host)))
+		return fail(ctx, NHB_ERR_ARG, "nhb_memcpy_h2d: bad arguments");
+	device_guard g(ctx->device);
+	NHB_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+	return NHB_OK;
+}
+
+int nhb_memcpy_d2h(nhb_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes) {
+	if (!ctx || (bytes && (!dst_host || !src_dev)))
+		return fail(ctx, NHB_ERR_ARG, "nhb_memcpy_d2h: bad arguments");
+	device_guard g(ctx->device);
+	NHB_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+	return NHB_OK;
+}
+
+int nhb_weight_upload_q8_0(nhb_ctx* ctx, const void* host_blocks34, int64_t N, int64_t K, nhb_weight** out) {
+	if (!ctx || !out)
+		return fail(ctx, NHB_ERR_ARG, "nhb_weight_upload_q8_0: null context or output");
+	*out = nullptr;
+	if (N < 0 || K <= 0 || K % 32 != 0)
+		return fail(ctx, NHB_ERR_ARG, "nhb_weight_upload_q8_0: K must be a positive multiple of 32 and N >= 0");
+	if (N > 0 && !host_blocks34)
+		return fail(ctx, NHB_ERR_ARG, "nhb_weight_upload_q8_0: null tensor data");
+	if (ctx->capturing)
+		return fail(ctx, NHB_ERR_UNSUPPORTED, "weight upload during graph capture");
+	device_guard g(ctx->device);
+	nhb_weight* w = new nhb_weight();
+	w->N		  = N;
+	w->K		  = K;
+	w->device	  = ctx->device;
+	nhb_shard_rows(N, ctx->world, ctx->rank, &w->n0, &w->n1);
+	const int64_t rows = w->n1 - w->n0;
+	const int64_t nb   = K / 32;
+	if (rows > 0) {
+		cudaError_t e = cudaMalloc(&w->q, static_cast<size_t>(rows) * K);
+		if (e == cudaSuccess)
+			e = cudaMalloc(&w->d, static_cast<size_t>(rows) * nb * sizeof(__half));
+		if (e != cudaSuccess) {
+			if (w->q)
+				cudaFree(w->q);
+			delete w;
+			return fail_cuda(ctx, e, "weight plane allocation");
+		}
+		// stage raw blocks in row chunks of <= 64 MiB and split them on the device
+		const int64_t row_bytes	 = nb * 34;
+		const int64_t chunk_rows = std::max<int64_t>(1, (int64_t(64) << 20) / row_bytes);
+		void* stage				 = nullptr;
+		const size_t stage_bytes = static_cast<size_t>(std::min(chunk_rows, rows) * row_bytes);
+		e						 = cudaMalloc(&stage, stage_bytes);
+		const uint8_t* src		 = static_cast<const uint8_t*>(host_blocks34) + w->n0 * row_bytes;
+		for (int64_t r0 = 0; r0 < rows && e == cudaSuccess; r0 += chunk_rows) {
+			const int64_t rr = std::min(chunk_rows, rows - r0);
+			e				 = cudaMemcpyAsync(stage, src + r0 * row_bytes, static_cast<size_t>(rr * row_bytes), cudaMemcpyHostToDevice, ctx->stream);
+			if (e == cudaSuccess)
+				e = launch_repack(static_cast<const uint8_t*>(stage), rr, K, w->q + r0 * K, w->d + r0 * nb, ctx->stream);
+			if (e == cudaSuccess)
+				e = cudaStreamSynchronize(ctx->stream);// the next chunk reuses the staging buffer
+		}
+		if (stage)
+			cudaFree(stage);
+		if (e != cudaSuccess) {
+			cudaFree(w->q);
+			cudaFree(w->d);
+			delete w;
+			return fail_cuda(ctx, e, "weight upload");
+		}
+		ctx->launches += (rows + chunk_rows - 1) / chunk_rows;
+	}
+	*out = w;
+	return NHB_OK;
+}
+
+int nhb_weight_free(nhb_ctx* ctx, nhb_weight* w) {
+	if (!w)
+		return NHB_OK;
+	device_guard g(w->device);
+	if (ctx)
+		cudaStreamSynchronize(ctx->stream);
+	if (w->q)
+		cudaFree(w->q);
+	if (w->d)
+		cudaFree(w->d);
+	delete w;
+	return NHB_OK;
+}
+
+int nhb_weight_info_get(const nhb_weight* w, nhb_weight_info* info) {
+	if (!w || !info)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_weight_info_get: null argument");
+	info->N		   = w->N;
+	info->K		   = w->K;
+	info->n0	   = w->n0;
+	info->n1	   = w->n1;
+	info->q		   = w->q;
+	info->d		   = w->d;
+	info->bytes_q8 = (w->n1 - w->n0) * (w->K / 32) * 34;
+	return NHB_OK;
+}
+
+int nhb_weight_download_q8_0(nhb_ctx* ctx, const nhb_weight* w, void* host_blocks34_shard) {
+	if (!ctx || !w || !host_blocks34_shard)
+		return fail(ctx, NHB_ERR_ARG, "nhb_weight_download_q8_0: null argument");
+	device_guard g(ctx->device);
+	const int64_t rows = w->n1 - w->n0;
+	if (rows == 0)
+		return NHB_OK;
+	const size_t bytes = static_cast<size_t>(rows) * (w->K / 32) * 34;
+	void* stage		   = nullptr;
+	NHB_CUDA(ctx, cudaMalloc(&stage, bytes));
+	cudaError_t e = launch_unpack(w->q, w->d, rows, w->K, static_cast<uint8_t*>(stage), ctx->stream);
+	if (e == cudaSuccess)
+		e = cudaMemcpyAsync(host_blocks34_shard, stage, bytes, cudaMemcpyDeviceToHost, ctx->stream);
+	if (e == cudaSuccess)
+		e = cudaStreamSynchronize(ctx->stream);
+	cudaFree(stage);
+	if (e != cudaSuccess)
+		return fail_cuda(ctx, e, "weight download");
+	ctx->launches += 1;
+	return NHB_OK;
+}
+
+int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int act_mode, int kernel) {
+	if (!ctx || (n_ops > 0 && !ops) || n_ops < 0 || n_ops > NHB_MAX_BATCH)
+		return fail(ctx, NHB_ERR_ARG, "nhb_mul_mat_batch: bad batch (at most 8 ops)");
+	if (act_mode != NHB_ACT_Q8 && act_mode != NHB_ACT_F32)
+		return fail(ctx, NHB_ERR_ARG, "unknown activation mode");
+	if (kernel < NHB_KERNEL_AUTO || kernel > NHB_KERNEL_GEMM_TC)
+		return fail(ctx, NHB_ERR_ARG, "unknown kernel id");
+	if (n_ops == 0)
+		return NHB_OK;
+	for (int i = 0; i < n_ops; ++i) {
+		int rc = check_mm_args(ctx, ops[i].w, ops[i].x, ops[i].ldx, ops[i].y, ops[i].ldy, ops[i].M);
+		if (rc != NHB_OK)
+			return rc;
+		if (ops[i].M != ops[0].M)
+			return fail(ctx, NHB_ERR_ARG, "all ops of a batch must share M");
+	}
+	const int64_t M = ops[0].M;
+	if (M == 0)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	const int forced = env_int("NHB_FORCE_KERNEL", 0);
+	if (kernel == NHB_KERNEL_AUTO && forced >= 1 && forced <= 3)
+		kernel = forced;
+	bool use_gemm = false;
+	if (kernel == NHB_KERNEL_GEMM_TC) {
+		use_gemm = true;
+	} else if (kernel == NHB_KERNEL_AUTO) {
+		use_gemm = act_mode == NHB_ACT_Q8 && M > ctx->gemv_max_m;
+		for (int i = 0; i < n_ops && use_gemm; ++i)
+			use_gemm = gemm_tc_supports(ops[i].w->n1 - ops[i].w->n0, ops[i].w->K, M) || ops[i].w->n1 == ops[i].w->n0;
+	}
+	if (use_gemm) {
+		if (act_mode != NHB_ACT_Q8)
+			return fail(ctx, NHB_ERR_UNSUPPORTED, "the tensor-core GEMM implements the Q8-activation arithmetic only");
+		for (int i = 0; i < n_ops; ++i) {
+			if (ops[i].w->n1 > ops[i].w->n0 && !gemm_tc_supports(ops[i].w->n1 - ops[i].w->n0, ops[i].w->K, M))
+				return fail(ctx, NHB_ERR_UNSUPPORTED, "shape not supported by the tensor-core GEMM (needs K % 128 == 0)");
+			int rc = run_gemm(ctx, ops[i]);
+			if (rc != NHB_OK)
+				return rc;
+		}
+		return NHB_OK;
+	}
+	return run_gemv(ctx, ops, n_ops, act_mode, kernel);
+}
+
+int nhb_mul_mat(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev, int64_t ldx, float* y_dev, int64_t ldy, int64_t M, int act_mode, int kernel) {
+	nhb_mul_mat_op op{ w, x_dev, ldx, y_dev, ldy, M };
+	return nhb_mul_mat_batch(ctx, &op, 1, act_mode, kernel);
+}
+
+int nhb_mul_mat_host(nhb_ctx* ctx, const nhb_weight* w, const float* x_host, int64_t ldx, float* y_host, int64_t ldy, int64_t M, int act_mode,
+	int kernel) {
+	if (!ctx || !w)
+		return fail(ctx, NHB_ERR_ARG, "null context or weight");
+	if (M < 0 || (M > 0 && (!x_host || !y_host)) || ldx < w->K || ldy < w->N)
+		return fail(ctx, NHB_ERR_ARG, "nhb_mul_mat_host: bad arguments");
+	if (M == 0)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	const int64_t rows = w->n1 - w->n0;
+	const size_t xb	   = static_cast<size_t>(M) * w->K * 4;
+	const size_t xpad  = (xb + 255) & ~size_t(255);
+	const size_t yb	   = static_cast<size_t>(M) * w->N * 4;
+	int rc			   = ensure(ctx, &ctx->io, &ctx->io_cap, xpad + yb, "host-I/O staging");
+	if (rc != NHB_OK)
+		return rc;
+	float* xd = static_cast<float*>(ctx->io);
+	float* yd = reinterpret_cast<float*>(static_cast<char*>(ctx->io) + xpad);
+	NHB_CUDA(ctx, cudaMemcpy2DAsync(xd, w->K * 4, x_host, ldx * 4, w->K * 4, M, cudaMemcpyHostToDevice, ctx->stream));
+	rc = nhb_mul_mat(ctx, w, xd, w->K, yd, w->N, M, act_mode, kernel);
+	if (rc != NHB_OK)
+		return rc;
+	if (rows > 0)
+		NHB_CUDA(ctx, cudaMemcpy2DAsync(y_host + w->n0, ldy * 4, yd + w->n0, w->N * 4, rows * 4, M, cudaMemcpyDeviceToHost, ctx->stream));
+	return NHB_OK;
+}
+
+int nhb_quantize_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, int64_t M, int64_t K, int8_t* q_dev, float* d_dev) {
+	if (!ctx || M < 0 || K <= 0 || K % 32 != 0 || ldx < K)
+		return fail(ctx, NHB_ERR_ARG, "nhb_quantize_q8_0: bad arguments");
+	if (M == 0)
+		return NHB_OK;
+	if (!x_dev || !q_dev || !d_dev || (reinterpret_cast<uintptr_t>(x_dev) & 15) || (ldx & 3) || (reinterpret_cast<uintptr_t>(q_dev) & 15))
+		return fail(ctx, NHB_ERR_ARG, "nhb_quantize_q8_0: null or misaligned pointer");
+	device_guard g(ctx->device);
+	cudaError_t e = launch_quantize(x_dev, ldx, static_cast<int>(M), static_cast<int>(K), q_dev, d_dev, ctx->stream);
+	if (e != cudaSuccess)
+		return fail_cuda(ctx, e, "quantize_q8 launch");
+	ctx->launches += 1;
+	return NHB_OK;
+}
+
+int nhb_mul_mat_block_dots(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev, int64_t ldx, int64_t M, int32_t* dots_dev) {
+	if (!ctx || !w || M < 0 || (M > 0 && (!x_dev || !dots_dev)) || ldx < w->K)
+		return fail(ctx, NHB_ERR_ARG, "nhb_mul_mat_block_dots: bad arguments");
+	if ((reinterpret_cast<uintptr_t>(x_dev) & 15) || (ldx & 3))
+		return fail(ctx, NHB_ERR_ARG, "activations must be 16-byte aligned with ldx a multiple of 4");
+	const int64_t rows = w->n1 - w->n0;
+	if (M == 0 || rows == 0)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	const size_t qb = (static_cast<size_t>(M) * w->K + 255) & ~size_t(255);
+	int rc			= ensure(ctx, &ctx->scratch, &ctx->scratch_cap, qb + static_cast<size_t>(M) * (w->K / 32) * 4, "block-dot scratch");
+	if (rc != NHB_OK)
+		return rc;
+	int8_t* qa	  = static_cast<int8_t*>(ctx->scratch);
+	float* da	  = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + qb);
+	cudaError_t e = launch_quantize(x_dev, ldx, static_cast<int>(M), static_cast<int>(w->K), qa, da, ctx->stream);
+	if (e == cudaSuccess)
+		e = launch_block_dots(w->q, qa, static_cast<int>(rows), static_cast<int>(w->K), static_cast<int>(M), dots_dev, ctx->stream);
+	if (e != cudaSuccess)
+		return fail_cuda(ctx, e, "block-dot launch");
+	ctx->launches += 2;
+	return NHB_OK;
+}
+
+int nhb_graph_begin(nhb_ctx* ctx) {
+	if (!ctx)
+		return fail(nullptr, NHB_ERR_ARG, "null context");
+	if (ctx->capturing)
+		return fail(ctx, NHB_ERR_ARG, "a capture is already open");
+	device_guard g(ctx->device);
+	NHB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+	ctx->capturing = true;
+	return NHB_OK;
+}
+
+int nhb_graph_end(nhb_ctx* ctx, nhb_graph** out) {
+	if (!ctx || !out)
+		return fail(ctx, NHB_ERR_ARG, "nhb_graph_end: null argument");
+	if (!ctx->capturing)
+		return fail(ctx, NHB_ERR_ARG, "no capture is open");
+	device_guard g(ctx->device);
+	ctx->capturing = false;
+	nhb_graph* gr  = new nhb_graph();
+	cudaError_t e  = cudaStreamEndCapture(ctx->stream, &gr->graph);
+	if (e == cudaSuccess)
+		e = cudaGraphInstantiate(&gr->exec, gr->graph, 0);
+	if (e != cudaSuccess) {
+		if (gr->graph)
+			cudaGraphDestroy(gr->graph);
+		delete gr;
+		return fail_cuda(ctx, e, "graph capture");
+	}
+	*out = gr;
+	return NHB_OK;
+}
+
+int nhb_graph_launch(nhb_ctx* ctx, nhb_graph* gr) {
+	if (!ctx || !gr || !gr->exec)
+		return fail(ctx, NHB_ERR_ARG, "nhb_graph_launch: null argument");
+	device_guard g(ctx->device);
+	NHB_CUDA(ctx, cudaGraphLaunch(gr->exec, ctx->stream));
+	return NHB_OK;
+}
+
+int nhb_graph_free(nhb_ctx* ctx, nhb_graph* gr) {
+	if (!gr)
+		return NHB_OK;
+	if (ctx) {
+		device_guard g(ctx->device);
+		cudaStreamSynchronize(ctx->stream);
+		if (gr->exec)
+			cudaGraphExecDestroy(gr->exec);
+		if (gr->graph)
+			cudaGraphDestroy(gr->graph);
+	}
+	delete gr;
+	return NHB_OK;
+}
+
+int nhb_comm_unique_id(void* id128) {
+	if (!id128)
+		return fail(nullptr, NHB_ERR_ARG, "null id buffer");
+	if (!nccl().ok)
+		return fail(nullptr, NHB_ERR_NCCL, "libnccl.so.2 could not be loaded");
+	nccl_uid id;
+	int rc = nccl().GetUniqueId(&id);
+	if (rc != nccl_success)
+		return fail(nullptr, NHB_ERR_NCCL, std::string("ncclGetUniqueId: ") + (nccl().GetErrorString ? nccl().GetErrorString(rc) : "error"));
+	std::memcpy(id128, &id, sizeof(id));
+	return NHB_OK;
+}
+
+int nhb_comm_init(nhb_ctx* ctx, const void* id128) {
+	if (!ctx || !id128)
+		return fail(ctx, NHB_ERR_ARG, "nhb_comm_init: null argument");
+	if (ctx->world == 1)
+		return NHB_OK;
+	if (!nccl().ok)
+		return fail(ctx, NHB_ERR_NCCL, "libnccl.so.2 could not be loaded");
+	if (ctx->comm)
+		return fail(ctx, NHB_ERR_ARG, "communicator already initialised");
+	device_guard g(ctx->device);
+	nccl_uid id;
+	std::memcpy(&id, id128, sizeof(id));
+	int rc = nccl().CommInitRank(&ctx->comm, ctx->world, id, ctx->rank);
+	if (rc != nccl_success) {
+		ctx->comm = nullptr;
+		return fail(ctx, NHB_ERR_NCCL, std::string("ncclCommInitRank: ") + (nccl().GetErrorString ? nccl().GetErrorString(rc) : "error"));
+	}
+	return NHB_OK;
+}
+
+int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, const int64_t* M, const int64_t* N, int n) {
+	if (!ctx || n < 0 || (n > 0 && (!y_dev || !ldy || !M || !N)))
+		return fail(ctx, NHB_ERR_ARG, "nhb_all_gather_batch: bad arguments");
+	if (ctx->world == 1 || n == 0)
+		return NHB_OK;
+	if (!ctx->comm)
+		return fail(ctx, NHB_ERR_NCCL, "nhb_comm_init has not been called");
+	device_guard g(ctx->device);
+	nccl_api& nc = nccl();
+	int rc		 = nc.GroupStart();
+	for (int i = 0; i < n && rc == nccl_success; ++i) {
+		if (M[i] < 0 || N[i] < 0 || ldy[i] < N[i] || (M[i] > 0 && !y_dev[i])) {
+			nc.GroupEnd();
+			return fail(ctx, NHB_ERR_ARG, "nhb_all_gather_batch: bad entry");
+		}
+		const bool even = N[i] % ctx->world == 0;
+		for (int64_t m = 0; m < M[i] && rc == nccl_success; ++m) {
+			float* row = y_dev[i] + m * ldy[i];
+			if (even) {
+				const int64_t cnt = N[i] / ctx->world;
+				rc				  = nc.AllGather(row + ctx->rank * cnt, row, static_cast<size_t>(cnt), nccl_float, ctx->comm, ctx->stream);
+			} else {
+				for (int r = 0; r < ctx->world && rc == nccl_success; ++r) {
+					int64_t a, b;
+					nhb_shard_rows(N[i], ctx->world, r, &a, &b);
+					if (b > a)
+						rc = nc.Broadcast(row + a, row + a, static_cast<size_t>(b - a), nccl_float, r, ctx->comm, ctx->stream);
+				}
+			}
+		}
+	}
+	int rc2 = nc.GroupEnd();
+	if (rc == nccl_success)
+		rc = rc2;
+	if (rc != nccl_success)
+		return fail(ctx, NHB_ERR_NCCL, std::string("all-gather: ") + (nc.GetErrorString ? nc.GetErrorString(rc) : "error"));
+	ctx->launches += 1;
+	return NHB_OK;
+}
+
+int nhb_all_gather(nhb_ctx* ctx, float* y_dev, int64_t ldy, int64_t M, int64_t N) {
+	return nhb_all_gather_batch(ctx, &y_dev, &ldy, &M, &N, 1);
+}
+}

@@ -1,0 +1,66 @@
+// Internal declarations shared by the translation units of libnihilus_b200.so (not part of the ABI).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/nihilus_b200.h"
+
+#define NHB_MAX_BATCH 8
+#define NHB_STATUS_WORDS 8
+
+namespace nhb {
+
+	// device status word values (written by kernels whose bounded waits ran out)
+	enum : int { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_DRAIN = 3, DEV_TIMEOUT_MMA = 4 };
+
+	// one mul_mat as the streaming GEMV sees it: this context's row shard of the two planes
+	struct stream_op {
+		const int8_t* wq;// [rows][K]
+		const __half* wd;// [rows][K/32]
+		const float* x;// [M][ldx]
+		float* y;// already offset to this shard's first column
+		long long ldx, ldy;
+		int rows;
+		int K;
+		int rows_per_tile;
+		int tile_begin;// index of this op's first tile in the batch-wide tile list
+	};
+
+	struct stream_batch {
+		int n_ops;
+		int total_tiles;
+		int stage_bytes;// ring slot size
+		int n_stages;
+		stream_op op[NHB_MAX_BATCH];
+	};
+
+	struct launch_cfg {
+		cudaStream_t stream;
+		int sm_count;
+		bool pdl;// attach the programmatic-serialization attribute
+		int* dev_status;
+	};
+
+	// gemv.cu
+	cudaError_t launch_gemv_stream(const stream_batch& b, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches);
+	bool gemv_stream_supports(int64_t K, int64_t M);
+	cudaError_t launch_gemv_ldg(const int8_t* wq, const __half* wd, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
+		int act_mode, const launch_cfg& cfg, int* launches);
+	int gemv_ldg_max_m(int64_t K, int act_mode);
+	cudaError_t launch_quantize(const float* x, long long ldx, int M, int K, int8_t* q, float* d, cudaStream_t s);
+	cudaError_t launch_block_dots(const int8_t* wq, const int8_t* qa, int rows, int K, int M, int32_t* dots, cudaStream_t s);
+
+	// repack.cu
+	cudaError_t launch_repack(const uint8_t* blocks34, int64_t rows, int64_t K, int8_t* q, __half* d, cudaStream_t s);
+	cudaError_t launch_unpack(const int8_t* q, const __half* d, int64_t rows, int64_t K, uint8_t* blocks34, cudaStream_t s);
+
+	// gemm_tc.cu
+	bool gemm_tc_supports(int64_t rows, int64_t K, int64_t M);
+	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M);
+	cudaError_t launch_gemm_tc(const int8_t* wq, const __half* wd, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
+		void* scratch, const launch_cfg& cfg, int* launches, std::string* err);
+
+}

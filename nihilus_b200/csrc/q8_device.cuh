@@ -1,0 +1,49 @@
+// Device-side pieces of the Q8_0 arithmetic shared by every kernel: the activation quantiser and the
+// packed int8 dot.  The quantiser reproduces quantize_row_q8_0 of the reference
+// (include/nihilus-incl/cpu/avx_2.hpp:4439-4489) bit for bit: IEEE divide and multiply with no
+// contraction, round-half-even to int, fp16 round-to-nearest-even for the stored scale.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace nhb {
+
+	constexpr int QK = 32;
+
+	struct act_scale {
+		float id;// 127 / amax (0 when amax == 0)
+		float d;// fp16-rounded amax / 127, widened back to f32
+	};
+
+	__device__ __forceinline__ act_scale q8_scales(float amax) {
+		act_scale s;
+		s.d	 = __half2float(__float2half_rn(__fdiv_rn(amax, 127.f)));
+		s.id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
+		return s;
+	}
+
+	// one quant; the reference saturates through two pack instructions, NaN handling differs (0 here)
+	__device__ __forceinline__ int q8_quant(float x, float id) {
+		int q = __float2int_rn(__fmul_rn(x, id));
+		return max(-128, min(127, q));
+	}
+
+	__device__ __forceinline__ uint32_t q8_pack4(float a, float b, float c, float d, float id) {
+		return (static_cast<uint32_t>(q8_quant(a, id)) & 0xffu) | ((static_cast<uint32_t>(q8_quant(b, id)) & 0xffu) << 8) |
+			((static_cast<uint32_t>(q8_quant(c, id)) & 0xffu) << 16) | ((static_cast<uint32_t>(q8_quant(d, id)) & 0xffu) << 24);
+	}
+
+	__device__ __forceinline__ float absmax4(float4 v, float m) {
+		return fmaxf(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))), m);
+	}
+
+	// exact dot of 16 int8 pairs
+	__device__ __forceinline__ int dot16(const uint4& w, const uint4& a) {
+		int s = __dp4a(static_cast<int>(w.x), static_cast<int>(a.x), 0);
+		s	  = __dp4a(static_cast<int>(w.y), static_cast<int>(a.y), s);
+		s	  = __dp4a(static_cast<int>(w.z), static_cast<int>(a.z), s);
+		s	  = __dp4a(static_cast<int>(w.w), static_cast<int>(a.w), s);
+		return s;
+	}
+
+}
