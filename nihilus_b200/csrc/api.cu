@@ -182,7 +182,7 @@ namespace {
 			return fail(ctx, NHB_ERR_ARG, "M < 0");
 		if (M == 0)
 			return NHB_OK;
-		if (!x || !y)
+		if (!x || (!y && w->N > 0))
 			return fail(ctx, NHB_ERR_ARG, "null activation or output pointer");
 		if (ldx < w->K || ldy < w->N)
 			return fail(ctx, NHB_ERR_ARG, "leading dimension smaller than the row length");

@@ -1,0 +1,284 @@
+"""Parity of the CUDA path against the CPU oracle, through the C ABI (needs a B200)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4  # max|err| / max|ref| for f32 outputs; per-block int32 dots must be exact
+
+
+def _rel(y, ref):
+    return float(np.abs(y - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def ctx(capi):
+    c = capi.Context(0)
+    yield c
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def torch_mod():
+    import torch
+
+    return torch
+
+
+def _case(synth, N, K, M, seed):
+    return synth.make_weight(N, K, seed), synth.make_activation(M, K, seed + 1)
+
+
+def _run(ctx, torch, w_handle, x, **kw):
+    xd = torch.from_numpy(x).cuda()
+    y = ctx.mul_mat(w_handle, xd, **kw)
+    ctx.sync()
+    return y.cpu().numpy()
+
+
+def test_loaded_library_is_ours(capi):
+    assert "libnihilus_b200.so" in open("/proc/self/maps").read()
+
+
+def test_upload_repack_round_trip(capi, ctx, oracle):
+    from nihilus_b200 import synth
+
+    for N, K in ((37, 96), (128, 4096), (5, 14336)):
+        w = synth.make_weight(N, K, 5)
+        h = ctx.upload(w)
+        assert (h.download() == w).all()
+        assert h.bytes_q8 == N * (K // 32) * 34
+        h.free()
+
+
+def test_quantiser_bit_exact(capi, ctx, oracle, torch_mod):
+    torch = torch_mod
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((5, 4096)).astype(np.float32)
+    x[0, :32] = 0.0
+    x[1, :64] *= 1e-6
+    x[2, 100] = 1e4
+    x[3, :32] = [0.5 * i for i in range(32)]  # exact ties after scaling by 127/15.5
+    q, d = ctx.quantize(torch.from_numpy(x).cuda())
+    ctx.sync()
+    blocks = oracle.quantize_rows(x)
+    want_q = blocks[:, :, 2:].view(np.int8).reshape(5, 4096)
+    want_d = blocks[:, :, :2].copy().view(np.float16).astype(np.float32).reshape(5, 128)
+    assert (q.cpu().numpy() == want_q).all()
+    assert (d.cpu().numpy().view(np.uint32) == want_d.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("N,K", [(8, 32), (9, 64), (33, 96), (64, 256), (17, 1024), (40, 2048), (31, 4096), (6, 14336)])
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8])
+def test_small_shapes_q8(capi, ctx, oracle, torch_mod, N, K, M):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    w, x = _case(synth, N, K, M, 1000 + N + K + M)
+    h = ctx.upload(w)
+    ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
+    y = _run(ctx, torch_mod, h, x)
+    assert _rel(y, ref) <= TOL
+    # exact integer block dots
+    dots = ctx.block_dots(h, torch_mod.from_numpy(x).cuda())
+    ctx.sync()
+    assert (dots.cpu().numpy() == oracle.block_dots(w, x)).all()
+    h.free()
+
+
+@pytest.mark.parametrize("kernel_name", ["KERNEL_GEMV_LDG", "KERNEL_GEMV_STREAM"])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+def test_llama_shapes_m1_both_gemv_kernels(capi, ctx, oracle, torch_mod, kernel_name, N, K):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    w, x = _case(synth, N, K, 1, 20250000 + N + K)
+    h = ctx.upload(w)
+    ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
+    y = _run(ctx, torch_mod, h, x, kernel=getattr(capi, kernel_name))
+    assert _rel(y, ref) <= TOL
+    truth = oracle.mul_mat(po.Q8ACT_F64, w, x)
+    assert _rel(y, truth) <= TOL
+    h.free()
+
+
+def test_lm_head_full_size(capi, ctx, oracle, torch_mod):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    N, K = 128256, 4096
+    w, x = _case(synth, N, K, 1, 20252007)
+    h = ctx.upload(w)
+    y = _run(ctx, torch_mod, h, x)
+    ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
+    assert _rel(y, ref) <= TOL
+    # size-independent property: permuting weight rows permutes outputs, bit for bit
+    perm = np.random.default_rng(1).permutation(N)
+    h2 = ctx.upload(w[perm])
+    y2 = _run(ctx, torch_mod, h2, x)
+    assert (y2.view(np.uint32) == y[:, perm].view(np.uint32)).all()
+    h.free()
+    h2.free()
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 7, 8, 11])
+def test_multi_row_stream_and_ldg_agree(capi, ctx, oracle, torch_mod, M):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    for N, K in ((512, 4096), (256, 14336)):
+        w, x = _case(synth, N, K, M, 77 + M)
+        h = ctx.upload(w)
+        ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
+        ys = _run(ctx, torch_mod, h, x, kernel=capi.KERNEL_GEMV_STREAM)
+        yl = _run(ctx, torch_mod, h, x, kernel=capi.KERNEL_GEMV_LDG)
+        assert _rel(ys, ref) <= TOL and _rel(yl, ref) <= TOL
+        h.free()
+
+
+@pytest.mark.parametrize("N,K,M", [(64, 256, 1), (100, 4096, 3), (32, 14336, 2), (9, 96, 5)])
+def test_f32_activation_mode(capi, ctx, oracle, torch_mod, N, K, M):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    w, x = _case(synth, N, K, M, 4242 + N)
+    h = ctx.upload(w)
+    ref = oracle.mul_mat(po.F32ACT_EVAL, w, x)
+    y = _run(ctx, torch_mod, h, x, act_mode=capi.ACT_F32)
+    assert _rel(y, ref) <= TOL
+    assert _rel(y, oracle.mul_mat(po.F32ACT_PROMPT, w, x)) <= TOL
+    h.free()
+
+
+def test_ragged_leading_dimensions_and_untouched_padding(capi, ctx, oracle, torch_mod):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    torch = torch_mod
+    N, K, M = 130, 4096, 3
+    w, x = _case(synth, N, K, M, 9)
+    h = ctx.upload(w)
+    xd = torch.full((M, K + 64), 7.0, device="cuda")
+    xd[:, :K] = torch.from_numpy(x).cuda()
+    yd = torch.full((M, N + 6), -3.0, device="cuda")
+    capi._check(capi.lib.nhb_mul_mat(ctx.handle, h.handle, xd.data_ptr(), K + 64, yd.data_ptr(), N + 6, M, capi.ACT_Q8, capi.KERNEL_AUTO), ctx.handle)
+    ctx.sync()
+    y = yd.cpu().numpy()
+    assert _rel(y[:, :N], oracle.mul_mat(po.Q8ACT_LANES, w, x)) <= TOL
+    assert (y[:, N:] == -3.0).all()
+    h.free()
+
+
+def test_empty_inputs_and_argument_errors(capi, ctx, torch_mod):
+    from nihilus_b200 import synth
+
+    torch = torch_mod
+    w = synth.make_weight(16, 64, 3)
+    h = ctx.upload(w)
+    x0 = torch.zeros((0, 64), device="cuda")
+    assert ctx.mul_mat(h, x0).shape == (0, 16)
+    hz = ctx.upload(w[:0])  # a weight with no rows
+    y = ctx.mul_mat(hz, torch.zeros((2, 64), device="cuda"))
+    ctx.sync()
+    assert y.shape == (2, 0)
+    x = torch.zeros((1, 64), device="cuda")
+    yb = torch.zeros((1, 16), device="cuda")
+    lib = capi.lib
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, None, 64, yb.data_ptr(), 16, 1, 0, 0) == capi.ERR_ARG
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 32, yb.data_ptr(), 16, 1, 0, 0) == capi.ERR_ARG  # ldx < K
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 8, 1, 0, 0) == capi.ERR_ARG  # ldy < N
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, -1, 0, 0) == capi.ERR_ARG
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, 1, 9, 0) == capi.ERR_ARG  # mode
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr() + 4, 64, yb.data_ptr(), 16, 1, 0, 0) == capi.ERR_ARG  # misaligned
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, 1, 0, capi.KERNEL_GEMV_STREAM) == capi.ERR_UNSUPPORTED
+    assert "K" in capi.last_error(ctx.handle)
+    import ctypes as C
+
+    out = C.c_void_p()
+    assert lib.nhb_weight_upload_q8_0(ctx.handle, w.ctypes.data, 16, 48, C.byref(out)) == capi.ERR_ARG  # K % 32
+    ctx.sync()  # the context is still usable
+    h.free()
+    hz.free()
+
+
+def test_batched_launch_equals_single_launches(capi, ctx, oracle, torch_mod):
+    from nihilus_b200 import synth
+
+    torch = torch_mod
+    shapes = [(4096, 4096), (1024, 4096), (1024, 4096), (640, 14336)]
+    hs, xs, singles = [], [], []
+    for i, (N, K) in enumerate(shapes):
+        w = synth.make_weight(N, K, 300 + i)
+        hs.append(ctx.upload(w))
+        xs.append(torch.from_numpy(synth.make_activation(1, K, 400 + i)).cuda())
+        singles.append(ctx.mul_mat(hs[-1], xs[-1], kernel=capi.KERNEL_GEMV_STREAM))
+    ys = [torch.zeros((1, N), device="cuda") for N, _ in shapes]
+    ctx.mul_mat_batch([(h, x, y) for h, x, y in zip(hs, xs, ys)])
+    ctx.sync()
+    for a, b in zip(singles, ys):
+        assert torch.equal(a, b)
+    for h in hs:
+        h.free()
+
+
+def test_emulated_row_shards_are_bit_identical_to_one_gpu(capi, ctx, oracle, torch_mod):
+    """world = 2, 4 and 3 (uneven) emulated as several contexts on this GPU: concatenated slices == unsharded."""
+    from nihilus_b200 import synth
+
+    torch = torch_mod
+    N, K, M = 1030, 4096, 2
+    w, x = _case(synth, N, K, M, 555)
+    h = ctx.upload(w)
+    full = _run(ctx, torch, h, x)
+    h.free()
+    xd = torch.from_numpy(x).cuda()
+    for world in (2, 3, 4):
+        y = torch.zeros((M, N), device="cuda")
+        for r in range(world):
+            c = capi.Context(0, r, world)
+            hr = c.upload(w)
+            assert (hr.n0, hr.n1) == capi.shard_rows(N, world, r)
+            c.mul_mat(hr, xd, y)
+            c.sync()
+            hr.free()
+            c.close()
+        assert (y.cpu().numpy().view(np.uint32) == full.view(np.uint32)).all()
+
+
+def test_graph_replay_and_determinism(capi, ctx, oracle, torch_mod):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    torch = torch_mod
+    N, K = 2048, 4096
+    w, x = _case(synth, N, K, 1, 808)
+    h = ctx.upload(w)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.zeros((1, N), device="cuda")
+    ctx.mul_mat(h, xd, y)
+    ctx.sync()
+    first = y.clone()
+    ctx.graph_begin()
+    for _ in range(3):
+        ctx.mul_mat(h, xd, y)
+    g = ctx.graph_end()
+    y.zero_()
+    g.launch()
+    g.launch()
+    ctx.sync()
+    assert torch.equal(first, y)
+    assert _rel(y.cpu().numpy(), oracle.mul_mat(po.Q8ACT_LANES, w, x)) <= TOL
+    g.free()
+    h.free()
+
+
+def test_host_buffer_entry_point(capi, ctx, oracle):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    N, K, M = 300, 4096, 2
+    w, x = _case(synth, N, K, M, 99)
+    h = ctx.upload(w)
+    y = ctx.mul_mat_host(h, x)
+    assert _rel(y, oracle.mul_mat(po.Q8ACT_LANES, w, x)) <= TOL
+    h.free()
