@@ -46,7 +46,8 @@ enum nhb_kernel {
 	NHB_KERNEL_AUTO		   = 0,
 	NHB_KERNEL_GEMV_LDG	   = 1, /* any K % 32 == 0: coalesced 128-bit loads, dp4a, warp-shuffle reduce */
 	NHB_KERNEL_GEMV_STREAM = 2, /* K % 256 == 0, K <= 16384: persistent CTAs fed by a bulk-copy (TMA) ring */
-	NHB_KERNEL_GEMM_TC	   = 3  /* tcgen05 / TMEM tensor-core contraction for prefill */
+	NHB_KERNEL_GEMM_TC	   = 3, /* tcgen05 / TMEM tensor-core contraction for prefill */
+	NHB_KERNEL_GEMV_ROWS   = 4	/* default GEMV: warp per row, batched ops, weight loads issued ahead of the previous kernel's end */
 };
 
 typedef struct nhb_ctx nhb_ctx;
@@ -102,7 +103,8 @@ int nhb_ctx_set_stream(nhb_ctx* ctx, void* cuda_stream);
 int nhb_sync(nhb_ctx* ctx);
 /* largest M served by the GEMV family under NHB_KERNEL_AUTO (default 8) */
 int nhb_ctx_set_gemv_max_m(nhb_ctx* ctx, int max_m);
-/* tuning knobs: "pdl" (programmatic dependent launch, default 1), "ctas_per_sm" (1 or 2), "gemv_max_m" */
+/* tuning knobs: "pdl" (programmatic dependent launch, default 1), "gemv_kernel" (1, 2 or 4: what AUTO uses for
+ * small M), "rows_ctas_per_sm", "prequantize", "ctas_per_sm" (streaming GEMV, 1 or 2), "gemv_max_m" */
 int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value);
 /* kernels this context has launched so far (upload, mul_mat, gather ...) */
 long long nhb_ctx_launch_count(const nhb_ctx* ctx);

@@ -22,7 +22,7 @@ if not os.path.exists(LIB_PATH):
 lib = C.CDLL(LIB_PATH)
 
 ACT_Q8, ACT_F32 = 0, 1
-KERNEL_AUTO, KERNEL_GEMV_LDG, KERNEL_GEMV_STREAM, KERNEL_GEMM_TC = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_GEMV_LDG, KERNEL_GEMV_STREAM, KERNEL_GEMM_TC, KERNEL_GEMV_ROWS = 0, 1, 2, 3, 4
 OK, ERR_ARG, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NOMEM = 0, -1, -2, -3, -4, -5, -6
 
 # every symbol include/nihilus_b200.h declares

@@ -88,7 +88,10 @@ struct nhb_ctx {
 	ncclComm_t comm	   = nullptr;
 	bool pdl		   = true;
 	int gemv_max_m	   = 8;
-	int ctas_per_sm	   = 1;
+	int ctas_per_sm	   = 1;// streaming GEMV: persistent CTAs per SM
+	int rows_cps	   = 3;// warp-per-row GEMV: grid cap in CTAs per SM
+	int preq		   = 0;// warp-per-row GEMV: quantise activations in a separate kernel
+	int gemv_default   = NHB_KERNEL_GEMV_ROWS;
 	bool capturing	   = false;
 	long long launches = 0;
 	std::string err;
@@ -198,7 +201,85 @@ namespace {
 		const int64_t M = ops[0].M;
 		launch_cfg cfg	= cfg_of(ctx);
 		int launches	= 0;
-		bool stream_ok	= act_mode == NHB_ACT_Q8 && kernel != NHB_KERNEL_GEMV_LDG;
+		if (kernel == NHB_KERNEL_AUTO)
+			kernel = ctx->gemv_default;
+		// ---- warp-per-row GEMV: the default ----
+		if (act_mode == NHB_ACT_Q8 && kernel == NHB_KERNEL_GEMV_ROWS) {
+			int mt_max = 4;
+			for (int i = 0; i < n_ops; ++i)
+				while (mt_max > 0 && !gemv_rows_supports(ops[i].w->K, mt_max))
+					--mt_max;
+			size_t act_total = 0;
+			for (int i = 0; i < n_ops && mt_max > 0; ++i)
+				act_total += gemv_rows_act_bytes(ops[i].w->K, 1);
+			while (mt_max > 1 && act_total * mt_max > 96 * 1024)
+				--mt_max;
+			if (mt_max >= 1 && act_total <= 96 * 1024) {
+				for (int64_t m0 = 0; m0 < M; m0 += mt_max) {
+					const int mt = static_cast<int>(std::min<int64_t>(mt_max, M - m0));
+					rows_batch b{};
+					size_t off = 0;
+					for (int i = 0; i < n_ops; ++i) {
+						const nhb_weight* w = ops[i].w;
+						if (w->n1 == w->n0)
+							continue;
+						rows_op& ro = b.op[b.n_ops];
+						ro.wq		= w->q;
+						ro.wd		= w->d;
+						ro.x		= ops[i].x + m0 * ops[i].ldx;
+						ro.y		= ops[i].y + m0 * ops[i].ldy + w->n0;
+						ro.ldx		= ops[i].ldx;
+						ro.ldy		= ops[i].ldy;
+						ro.rows		= static_cast<int>(w->n1 - w->n0);
+						ro.K		= static_cast<int>(w->K);
+						int slot	= -1;
+						for (int s = 0; s < b.n_slots; ++s) {
+							const rows_op& so = b.op[b.slot_op[s]];
+							if (so.x == ro.x && so.ldx == ro.ldx && so.K == ro.K)
+								slot = s;
+						}
+						if (slot < 0) {
+							b.slot_op[b.n_slots++] = b.n_ops;
+							ro.act_off			   = static_cast<int>(off);
+							ro.preq_off			   = static_cast<int>(off);
+							off += gemv_rows_act_bytes(ro.K, mt);
+						} else {
+							ro.act_off	= b.op[b.slot_op[slot]].act_off;
+							ro.preq_off = ro.act_off;
+						}
+						++b.n_ops;
+					}
+					if (b.n_ops == 0)
+						break;
+					b.act_bytes = static_cast<int>(off);
+					if (ctx->preq) {
+						int rc = ensure(ctx, &ctx->scratch, &ctx->scratch_cap, off, "activation scratch");
+						if (rc != NHB_OK)
+							return rc;
+						b.preq		= 1;
+						b.preq_base = static_cast<const unsigned char*>(ctx->scratch);
+						for (int s = 0; s < b.n_slots; ++s) {
+							const rows_op& so = b.op[b.slot_op[s]];
+							int8_t* q		  = static_cast<int8_t*>(ctx->scratch) + so.preq_off;
+							float* d		  = reinterpret_cast<float*>(q + static_cast<size_t>(mt) * so.K);
+							cudaError_t e	  = launch_quantize(so.x, so.ldx, mt, so.K, q, d, ctx->stream, ctx->pdl);
+							if (e != cudaSuccess)
+								return fail_cuda(ctx, e, "quantize_q8 launch");
+							++launches;
+						}
+					}
+					cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches);
+					if (e != cudaSuccess)
+						return fail_cuda(ctx, e, "gemv_q8_rows launch");
+				}
+				ctx->launches += launches;
+				return NHB_OK;
+			}
+			if (kernel == NHB_KERNEL_GEMV_ROWS && ctx->gemv_default != NHB_KERNEL_GEMV_ROWS)
+				return fail(ctx, NHB_ERR_UNSUPPORTED, "K too large for the warp-per-row GEMV's shared memory");
+			kernel = NHB_KERNEL_GEMV_LDG;
+		}
+		bool stream_ok	= act_mode == NHB_ACT_Q8 && kernel == NHB_KERNEL_GEMV_STREAM;
 		for (int i = 0; i < n_ops && stream_ok; ++i)
 			stream_ok = gemv_stream_supports(ops[i].w->K, 1);
 		if (kernel == NHB_KERNEL_GEMV_STREAM && !stream_ok)
@@ -330,7 +411,7 @@ int nhb_choose_kernel(int64_t N, int64_t K, int64_t M, int act_mode) {
 	if (act_mode == NHB_ACT_F32)
 		return NHB_KERNEL_GEMV_LDG;
 	if (M <= 8)
-		return gemv_stream_supports(K, 1) ? NHB_KERNEL_GEMV_STREAM : NHB_KERNEL_GEMV_LDG;
+		return gemv_rows_supports(K, 1) ? NHB_KERNEL_GEMV_ROWS : NHB_KERNEL_GEMV_LDG;
 	return NHB_KERNEL_GEMM_TC;
 }
 
@@ -382,6 +463,13 @@ int nhb_ctx_create(nhb_ctx** out, int device, int rank, int world) {
 	ctx->pdl		 = env_int("NHB_PDL", 1) != 0;
 	ctx->gemv_max_m	 = env_int("NHB_GEMV_MAX_M", 8);
 	ctx->ctas_per_sm = env_int("NHB_CTAS_PER_SM", 1);
+	ctx->rows_cps	 = env_int("NHB_ROWS_CPS", 3);
+	ctx->preq		 = env_int("NHB_PREQ", 0);
+	{
+		const int k = env_int("NHB_GEMV_KERNEL", NHB_KERNEL_GEMV_ROWS);
+		if (k == NHB_KERNEL_GEMV_LDG || k == NHB_KERNEL_GEMV_STREAM || k == NHB_KERNEL_GEMV_ROWS)
+			ctx->gemv_default = k;
+	}
 	*out			 = ctx;
 	return NHB_OK;
 }
@@ -430,6 +518,15 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 		ctx->ctas_per_sm = value < 1 ? 1 : (value > 2 ? 2 : value);
 	else if (!std::strcmp(name, "gemv_max_m"))
 		ctx->gemv_max_m = value < 1 ? 1 : value;
+	else if (!std::strcmp(name, "rows_ctas_per_sm"))
+		ctx->rows_cps = value < 1 ? 1 : (value > 8 ? 8 : value);
+	else if (!std::strcmp(name, "prequantize"))
+		ctx->preq = value != 0;
+	else if (!std::strcmp(name, "gemv_kernel")) {
+		if (value != NHB_KERNEL_GEMV_LDG && value != NHB_KERNEL_GEMV_STREAM && value != NHB_KERNEL_GEMV_ROWS)
+			return fail(ctx, NHB_ERR_ARG, "gemv_kernel must be 1, 2 or 4");
+		ctx->gemv_default = value;
+	}
 	else
 		return fail(ctx, NHB_ERR_ARG, std::string("unknown option ") + name);
 	return NHB_OK;
@@ -581,7 +678,7 @@ int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int ac
 		return fail(ctx, NHB_ERR_ARG, "nhb_mul_mat_batch: bad batch (at most 8 ops)");
 	if (act_mode != NHB_ACT_Q8 && act_mode != NHB_ACT_F32)
 		return fail(ctx, NHB_ERR_ARG, "unknown activation mode");
-	if (kernel < NHB_KERNEL_AUTO || kernel > NHB_KERNEL_GEMM_TC)
+	if (kernel < NHB_KERNEL_AUTO || kernel > NHB_KERNEL_GEMV_ROWS)
 		return fail(ctx, NHB_ERR_ARG, "unknown kernel id");
 	if (n_ops == 0)
 		return NHB_OK;
@@ -597,7 +694,7 @@ int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int ac
 		return NHB_OK;
 	device_guard g(ctx->device);
 	const int forced = env_int("NHB_FORCE_KERNEL", 0);
-	if (kernel == NHB_KERNEL_AUTO && forced >= 1 && forced <= 3)
+	if (kernel == NHB_KERNEL_AUTO && forced >= 1 && forced <= 4)
 		kernel = forced;
 	bool use_gemm = false;
 	if (kernel == NHB_KERNEL_GEMM_TC) {

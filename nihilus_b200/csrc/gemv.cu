@@ -304,6 +304,8 @@ namespace nhb {
 
 		// quantize_row_q8_0 on its own: one thread per 32-wide block
 		__global__ void quantize_q8_kernel(const float* __restrict__ x, long long ldx, int M, int K, int8_t* __restrict__ q, float* __restrict__ d) {
+			pdl_launch_dependents();
+			pdl_wait_prior_grids();
 			const int nb		= K >> 5;
 			const long long tot = static_cast<long long>(M) * nb;
 			for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < tot; i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -484,14 +486,16 @@ namespace nhb {
 		return e;
 	}
 
-	cudaError_t launch_quantize(const float* x, long long ldx, int M, int K, int8_t* q, float* d, cudaStream_t s) {
+	cudaError_t launch_quantize(const float* x, long long ldx, int M, int K, int8_t* q, float* d, cudaStream_t s, bool pdl) {
 		const long long tot = static_cast<long long>(M) * (K / 32);
 		if (tot == 0)
 			return cudaSuccess;
 		long long grid = (tot + 127) / 128;
 		grid		   = grid > 148 * 16 ? 148 * 16 : grid;
-		quantize_q8_kernel<<<static_cast<int>(grid), 128, 0, s>>>(x, ldx, M, K, q, d);
-		return cudaGetLastError();
+		launch_cfg cfg{};
+		cfg.stream = s;
+		cfg.pdl	   = pdl;
+		return launch_pdl(quantize_q8_kernel, dim3(static_cast<int>(grid)), dim3(128), 0, cfg, x, ldx, M, K, q, d);
 	}
 
 	cudaError_t launch_block_dots(const int8_t* wq, const int8_t* qa, int rows, int K, int M, int32_t* dots, cudaStream_t s) {

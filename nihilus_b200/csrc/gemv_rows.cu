@@ -1,0 +1,260 @@
+// gemv_q8_rows: the decode GEMV (sm_100a).  One warp per weight row, 256-bit coalesced loads of the int8
+// plane, packed int8 dot products (dp4a) against Q8_0-quantised activations staged in shared memory,
+// warp-shuffle reduction.  Several independent mul_mats (q/k/v, gate/up) run in one launch.
+//
+// Built for back-to-back launches: every warp issues the loads of its first weight rows BEFORE it waits for
+// the previous kernel (programmatic dependent launch) -- weights never depend on an earlier kernel, the
+// activations do -- so the weight stream of launch i+1 overlaps the tail of launch i.
+//
+// Arithmetic: quantize_row_q8_0 + vec_dot_q8_0_q8_0 of the reference (include/nihilus-incl/cpu/avx_2.hpp
+// :4439-4489, :4749-4780); per 32-wide block  acc = fma(float(exact int32 block dot), d_w * d_a, acc).  The
+// summation order depends on K only, so any row sharding gives bit-identical outputs.
+#include "internal.h"
+#include "ptx.cuh"
+#include "q8_device.cuh"
+
+namespace nhb {
+
+	namespace {
+
+		constexpr int ROWS_WARPS = 8;
+		constexpr int ROWS_TPB	 = ROWS_WARPS * 32;
+		constexpr int ITEM		 = 4;// 32-byte Q8 blocks per lane per step: 4 KB of a row per warp
+
+		__device__ __forceinline__ int rows_find_op(const rows_batch& b, int row, int cur) {
+			while (cur + 1 < b.n_ops && row >= b.op[cur + 1].row_begin)
+				++cur;
+			return cur;
+		}
+
+		struct blk32 {
+			uint4 lo, hi;
+		};
+
+		// one whole 32-byte block per lane: 256-bit load, streamed past L1, first to leave L2
+		__device__ __forceinline__ blk32 ldg_block(const void* p) {
+			blk32 v;
+			asm("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+						 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+						 : "l"(p));
+			return v;
+		}
+
+		struct item_regs {
+			blk32 w[ITEM];
+			uint16_t d[ITEM];
+		};
+
+		// everything a warp needs to stream one weight row, held in registers
+		struct row_desc {
+			const int8_t* wrow;
+			const uint16_t* drow;
+			int nb;
+		};
+
+		__device__ __forceinline__ row_desc make_row(const rows_op* op, int lrow) {
+			row_desc r;
+			const int K = op->K;
+			r.nb		= K >> 5;
+			r.wrow		= op->wq + static_cast<size_t>(lrow) * K;
+			r.drow		= reinterpret_cast<const uint16_t*>(op->wd) + static_cast<size_t>(lrow) * r.nb;
+			return r;
+		}
+
+		// blocks b0 + lane + 32*i of the row
+		__device__ __forceinline__ void load_item(item_regs& r, const row_desc rd, int b0, int lane) {
+#pragma unroll
+			for (int i = 0; i < ITEM; ++i) {
+				const int blk = b0 + lane + 32 * i;
+				if (blk < rd.nb) {
+					r.w[i] = ldg_block(rd.wrow + static_cast<size_t>(blk) * QK);
+					r.d[i] = __ldg(rd.drow + blk);
+				}
+			}
+		}
+
+		// Activations of one input in shared memory, per row m: the first 16 bytes of every block (uint4 [nb]), then the
+		// second 16 bytes (uint4 [nb]) -- two planes, so that a warp reading one block per lane touches consecutive
+		// 16-byte words (no bank conflicts) -- and after all MT rows the f32 scales [MT][nb].
+		template<int MT> __device__ __forceinline__ void compute_item(const item_regs& r, float (&acc)[MT], const unsigned char* act, int nb, int b0, int lane) {
+			const float* da = reinterpret_cast<const float*>(act + static_cast<size_t>(MT) * nb * QK);
+#pragma unroll
+			for (int i = 0; i < ITEM; ++i) {
+				const int blk = b0 + lane + 32 * i;
+				if (blk < nb) {
+					const float dw = __half2float(__ushort_as_half(r.d[i]));
+#pragma unroll
+					for (int m = 0; m < MT; ++m) {
+						const uint4* lo = reinterpret_cast<const uint4*>(act + static_cast<size_t>(m) * nb * QK);
+						// copy to registers first: a reference into shared memory would be read word by word
+						const uint4 a0 = lo[blk];
+						const uint4 a1 = lo[nb + blk];
+						const int sumi = dot16(r.w[i].lo, a0) + dot16(r.w[i].hi, a1);// the exact block dot
+						acc[m]		   = fmaf(static_cast<float>(sumi), dw * da[m * nb + blk], acc[m]);
+					}
+				}
+			}
+		}
+
+		template<int MT, int OCC> __global__ void __launch_bounds__(ROWS_TPB, OCC) gemv_q8_rows(const __grid_constant__ rows_batch b) {
+			extern __shared__ __align__(128) unsigned char act_smem[];
+			const int tid		 = threadIdx.x;
+			const int lane		 = tid & 31;
+			const int warp		 = tid >> 5;
+			const int W			 = gridDim.x * ROWS_WARPS;
+			const int row0		 = blockIdx.x * ROWS_WARPS + warp;
+			const int total_rows = b.total_rows;
+			const int n_ops		 = b.n_ops;
+			int cur				 = 0;
+			bool pre			 = false;
+			item_regs regs;
+			// ---- weights first: they never depend on the previous kernel ----
+			if (row0 < total_rows) {
+				cur = rows_find_op(b, row0, 0);
+				load_item(regs, make_row(&b.op[cur], row0 - b.op[cur].row_begin), 0, lane);
+				pre = true;
+			}
+			pdl_launch_dependents();
+			pdl_wait_prior_grids();
+			// ---- activations: quantise every distinct input of the batch into shared memory ----
+			for (int s = 0; s < b.n_slots; ++s) {
+				const rows_op* op  = &b.op[b.slot_op[s]];
+				unsigned char* act = act_smem + op->act_off;
+				const int K		   = op->K;
+				const int nb	   = K >> 5;
+				float* sda		   = reinterpret_cast<float*>(act + static_cast<size_t>(MT) * K);
+				if (b.preq) {
+					// quantised by quantize_q8_kernel into global scratch: int8 [MT][K] then f32 [MT][nb]
+					const unsigned char* src = b.preq_base + op->preq_off;
+					for (int i = tid; i < MT * nb * 2; i += ROWS_TPB) {
+						const int hb  = i >> 1;
+						const int m	  = hb / nb;
+						const int blk = hb - m * nb;
+						reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+					}
+					const float* sd = reinterpret_cast<const float*>(src + static_cast<size_t>(MT) * K);
+					for (int i = tid; i < MT * nb; i += ROWS_TPB)
+						sda[i] = __ldg(sd + i);
+				} else {
+					// two threads per 32-wide block (16 floats each); the pair shares its absmax by shuffle
+					const float* x		= op->x;
+					const long long ldx = op->ldx;
+					for (int i = tid; i < MT * nb * 2; i += ROWS_TPB) {
+						const int hb	= i >> 1;
+						const int m		= hb / nb;
+						const int blk	= hb - m * nb;
+						const float4* p = reinterpret_cast<const float4*>(x + static_cast<size_t>(m) * ldx + static_cast<size_t>(blk) * QK) + (i & 1) * 4;
+						const float4 v0 = __ldg(p), v1 = __ldg(p + 1), v2 = __ldg(p + 2), v3 = __ldg(p + 3);
+						float amax		= absmax4(v0, absmax4(v1, absmax4(v2, absmax4(v3, 0.f))));
+						amax			= fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
+						const act_scale sc = q8_scales(amax);
+						reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] =
+							make_uint4(q8_pack4(v0.x, v0.y, v0.z, v0.w, sc.id), q8_pack4(v1.x, v1.y, v1.z, v1.w, sc.id),
+								q8_pack4(v2.x, v2.y, v2.z, v2.w, sc.id), q8_pack4(v3.x, v3.y, v3.z, v3.w, sc.id));
+						if ((i & 1) == 0)
+							sda[hb] = sc.d;
+					}
+				}
+			}
+			__syncthreads();
+			// ---- rows ----
+			for (int row = row0; row < total_rows; row += W) {
+				while (cur + 1 < n_ops && row >= b.op[cur + 1].row_begin)
+					++cur;
+				const rows_op* op		 = &b.op[cur];
+				const int lrow			 = row - op->row_begin;
+				const row_desc rd		 = make_row(op, lrow);
+				const unsigned char* act = act_smem + op->act_off;
+				float* const yrow		 = op->y + lrow;
+				const long long ldy		 = op->ldy;
+				float acc[MT];
+#pragma unroll
+				for (int m = 0; m < MT; ++m)
+					acc[m] = 0.f;
+				for (int b0 = 0; b0 < rd.nb; b0 += 32 * ITEM) {
+					if (!pre)
+						load_item(regs, rd, b0, lane);
+					pre = false;
+					compute_item<MT>(regs, acc, act, rd.nb, b0, lane);
+				}
+#pragma unroll
+				for (int m = 0; m < MT; ++m) {
+					const float v = warp_sum(acc[m]);
+					if (lane == 0)
+						yrow[static_cast<size_t>(m) * ldy] = v;
+				}
+			}
+		}
+
+	}
+
+	size_t gemv_rows_act_bytes(int64_t K, int M) {
+		return static_cast<size_t>(((M * (K + (K / 32) * 4)) + 127) & ~int64_t(127));
+	}
+
+	bool gemv_rows_supports(int64_t K, int64_t M) {
+		return K % 32 == 0 && M >= 1 && M <= 4 && gemv_rows_act_bytes(K, static_cast<int>(M)) <= 96 * 1024;
+	}
+
+	// `b` arrives with op pointers/shapes, act_off/slot tables and preq fields filled by the caller.
+	cudaError_t launch_gemv_rows(const rows_batch& b_in, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches) {
+		rows_batch b = b_in;
+		int rows	 = 0;
+		for (int i = 0; i < b.n_ops; ++i) {
+			b.op[i].row_begin = rows;
+			rows += b.op[i].rows;
+		}
+		b.total_rows = rows;
+		if (rows == 0)
+			return cudaSuccess;
+		if (ctas_per_sm < 1)
+			ctas_per_sm = 1;
+		int grid	  = (rows + ROWS_WARPS - 1) / ROWS_WARPS;
+		const int cap = cfg.sm_count * ctas_per_sm;
+		if (grid > cap) {
+			// even split: every warp gets ceil(rows / W) or one fewer rows, with as few short warps as possible
+			const int per_warp = (rows + cap * ROWS_WARPS - 1) / (cap * ROWS_WARPS);
+			grid			   = (rows + per_warp * ROWS_WARPS - 1) / (per_warp * ROWS_WARPS);
+		}
+		const size_t smem = static_cast<size_t>(b.act_bytes);
+		cudaError_t e	  = cudaErrorInvalidValue;
+		cudaLaunchConfig_t lc{};
+		lc.gridDim			= dim3(grid);
+		lc.blockDim			= dim3(ROWS_TPB);
+		lc.dynamicSmemBytes = smem;
+		lc.stream			= cfg.stream;
+		cudaLaunchAttribute attr[1];
+		attr[0].id										   = cudaLaunchAttributeProgrammaticStreamSerialization;
+		attr[0].val.programmaticStreamSerializationAllowed = 1;
+		lc.attrs										   = attr;
+		lc.numAttrs										   = cfg.pdl ? 1 : 0;
+		// registers per thread are capped by the occupancy the grid was sized for (2, 3 or 4 CTAs per SM)
+		const int occ = ctas_per_sm >= 4 ? 4 : (ctas_per_sm == 3 ? 3 : 2);
+#define NHB_ROWS_CASE(MT, OCC) \
+	if (M == MT && occ == OCC) { \
+		auto kern = gemv_q8_rows<MT, OCC>; \
+		e		  = cudaSuccess; \
+		if (smem > 48 * 1024) \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+		if (e == cudaSuccess) \
+			e = cudaLaunchKernelEx(&lc, kern, b); \
+	}
+		NHB_ROWS_CASE(1, 2)
+		NHB_ROWS_CASE(1, 3)
+		NHB_ROWS_CASE(1, 4)
+		NHB_ROWS_CASE(2, 2)
+		NHB_ROWS_CASE(2, 3)
+		NHB_ROWS_CASE(2, 4)
+		NHB_ROWS_CASE(3, 2)
+		NHB_ROWS_CASE(3, 3)
+		NHB_ROWS_CASE(3, 4)
+		NHB_ROWS_CASE(4, 2)
+		NHB_ROWS_CASE(4, 3)
+		NHB_ROWS_CASE(4, 4)
+#undef NHB_ROWS_CASE
+		if (e == cudaSuccess && launches)
+			*launches += 1;
+		return e;
+	}
+
+}

@@ -37,6 +37,33 @@ namespace nhb {
 		stream_op op[NHB_MAX_BATCH];
 	};
 
+	// one mul_mat as the warp-per-row GEMV sees it
+	struct rows_op {
+		const int8_t* wq;
+		const __half* wd;
+		const float* x;
+		float* y;// already offset to this shard's first column
+		long long ldx, ldy;
+		int rows;
+		int K;
+		int row_begin;// first row of this op in the batch-wide row list
+		int act_off;// byte offset of this op's quantised activations in shared memory
+		int preq_off;// byte offset of the same data in the pre-quantised scratch (preq mode)
+		int pad;
+	};
+
+	struct rows_batch {
+		int n_ops;
+		int total_rows;
+		int act_bytes;// dynamic shared memory
+		int n_slots;// distinct activation inputs
+		int slot_op[NHB_MAX_BATCH];// a representative op per slot
+		int preq;// 1: activations were quantised by a separate kernel into preq_base
+		int pad;
+		const unsigned char* preq_base;
+		rows_op op[NHB_MAX_BATCH];
+	};
+
 	struct launch_cfg {
 		cudaStream_t stream;
 		int sm_count;
@@ -50,7 +77,12 @@ namespace nhb {
 	cudaError_t launch_gemv_ldg(const int8_t* wq, const __half* wd, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
 		int act_mode, const launch_cfg& cfg, int* launches);
 	int gemv_ldg_max_m(int64_t K, int act_mode);
-	cudaError_t launch_quantize(const float* x, long long ldx, int M, int K, int8_t* q, float* d, cudaStream_t s);
+	cudaError_t launch_quantize(const float* x, long long ldx, int M, int K, int8_t* q, float* d, cudaStream_t s, bool pdl = false);
+
+	// gemv_rows.cu
+	size_t gemv_rows_act_bytes(int64_t K, int M);
+	bool gemv_rows_supports(int64_t K, int64_t M);
+	cudaError_t launch_gemv_rows(const rows_batch& b, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches);
 	cudaError_t launch_block_dots(const int8_t* wq, const int8_t* qa, int rows, int K, int M, int32_t* dots, cudaStream_t s);
 
 	// repack.cu

@@ -61,9 +61,9 @@ def test_repack_host_round_trip_and_matches_oracle(capi, oracle):
 def test_choose_kernel_and_work_formulas(capi):
     from nihilus_b200 import shapes
 
-    assert capi.lib.nhb_choose_kernel(4096, 4096, 1, capi.ACT_Q8) == capi.KERNEL_GEMV_STREAM
-    assert capi.lib.nhb_choose_kernel(4096, 4096, 8, capi.ACT_Q8) == capi.KERNEL_GEMV_STREAM
-    assert capi.lib.nhb_choose_kernel(4096, 96, 1, capi.ACT_Q8) == capi.KERNEL_GEMV_LDG
+    assert capi.lib.nhb_choose_kernel(4096, 4096, 1, capi.ACT_Q8) == capi.KERNEL_GEMV_ROWS
+    assert capi.lib.nhb_choose_kernel(4096, 4096, 8, capi.ACT_Q8) == capi.KERNEL_GEMV_ROWS
+    assert capi.lib.nhb_choose_kernel(4096, 96, 1, capi.ACT_Q8) == capi.KERNEL_GEMV_ROWS
     assert capi.lib.nhb_choose_kernel(4096, 4096, 512, capi.ACT_Q8) == capi.KERNEL_GEMM_TC
     assert capi.lib.nhb_choose_kernel(4096, 4096, 1, capi.ACT_F32) == capi.KERNEL_GEMV_LDG
     assert capi.lib.nhb_mul_mat_bytes(4096, 4096, 1) == 17825792 + 16384 + 16384 == shapes.mul_mat_bytes(4096, 4096, 1)

@@ -86,7 +86,7 @@ def test_small_shapes_q8(capi, ctx, oracle, torch_mod, N, K, M):
     h.free()
 
 
-@pytest.mark.parametrize("kernel_name", ["KERNEL_GEMV_LDG", "KERNEL_GEMV_STREAM"])
+@pytest.mark.parametrize("kernel_name", ["KERNEL_GEMV_LDG", "KERNEL_GEMV_STREAM", "KERNEL_GEMV_ROWS"])
 @pytest.mark.parametrize("N,K", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
 def test_llama_shapes_m1_both_gemv_kernels(capi, ctx, oracle, torch_mod, kernel_name, N, K):
     from nihilus_b200 import synth
@@ -132,7 +132,8 @@ def test_multi_row_stream_and_ldg_agree(capi, ctx, oracle, torch_mod, M):
         ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
         ys = _run(ctx, torch_mod, h, x, kernel=capi.KERNEL_GEMV_STREAM)
         yl = _run(ctx, torch_mod, h, x, kernel=capi.KERNEL_GEMV_LDG)
-        assert _rel(ys, ref) <= TOL and _rel(yl, ref) <= TOL
+        yr = _run(ctx, torch_mod, h, x, kernel=capi.KERNEL_GEMV_ROWS)
+        assert _rel(ys, ref) <= TOL and _rel(yl, ref) <= TOL and _rel(yr, ref) <= TOL
         h.free()
 
 
@@ -190,6 +191,7 @@ def test_empty_inputs_and_argument_errors(capi, ctx, torch_mod):
     assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, -1, 0, 0) == capi.ERR_ARG
     assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, 1, 9, 0) == capi.ERR_ARG  # mode
     assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr() + 4, 64, yb.data_ptr(), 16, 1, 0, 0) == capi.ERR_ARG  # misaligned
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, 1, 0, 99) == capi.ERR_ARG  # kernel id
     assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, 1, 0, capi.KERNEL_GEMV_STREAM) == capi.ERR_UNSUPPORTED
     assert "K" in capi.last_error(ctx.handle)
     import ctypes as C
@@ -201,24 +203,63 @@ def test_empty_inputs_and_argument_errors(capi, ctx, torch_mod):
     hz.free()
 
 
-def test_batched_launch_equals_single_launches(capi, ctx, oracle, torch_mod):
+@pytest.mark.parametrize("kernel_name", ["KERNEL_GEMV_STREAM", "KERNEL_GEMV_ROWS", "KERNEL_AUTO"])
+def test_batched_launch_equals_single_launches(capi, ctx, oracle, torch_mod, kernel_name):
     from nihilus_b200 import synth
 
     torch = torch_mod
+    kern = getattr(capi, kernel_name)
     shapes = [(4096, 4096), (1024, 4096), (1024, 4096), (640, 14336)]
     hs, xs, singles = [], [], []
     for i, (N, K) in enumerate(shapes):
         w = synth.make_weight(N, K, 300 + i)
         hs.append(ctx.upload(w))
         xs.append(torch.from_numpy(synth.make_activation(1, K, 400 + i)).cuda())
-        singles.append(ctx.mul_mat(hs[-1], xs[-1], kernel=capi.KERNEL_GEMV_STREAM))
+        singles.append(ctx.mul_mat(hs[-1], xs[-1], kernel=kern))
     ys = [torch.zeros((1, N), device="cuda") for N, _ in shapes]
-    ctx.mul_mat_batch([(h, x, y) for h, x, y in zip(hs, xs, ys)])
+    ctx.mul_mat_batch([(h, x, y) for h, x, y in zip(hs, xs, ys)], kernel=kern)
     ctx.sync()
     for a, b in zip(singles, ys):
         assert torch.equal(a, b)
     for h in hs:
         h.free()
+
+
+def test_rows_kernel_options_do_not_change_results(capi, oracle, torch_mod):
+    """Grid size (CTAs per SM), register cap and separate activation quantisation leave every bit unchanged."""
+    from nihilus_b200 import synth
+
+    torch = torch_mod
+    base = None
+    w1 = synth.make_weight(1500, 4096, 61)
+    w2 = synth.make_weight(700, 4096, 62)
+    w3 = synth.make_weight(300, 14336, 63)
+    x1 = torch.from_numpy(synth.make_activation(2, 4096, 64)).cuda()
+    x3 = torch.from_numpy(synth.make_activation(2, 14336, 65)).cuda()
+    for cps in (2, 3, 4):
+        for preq in (0, 1):
+            for pdl in (0, 1):
+                c = capi.Context(0)
+                c.set_option("rows_ctas_per_sm", cps)
+                c.set_option("prequantize", preq)
+                c.set_option("pdl", pdl)
+                hs = [c.upload(w1), c.upload(w2), c.upload(w3)]
+                ys = [torch.zeros((2, 1500), device="cuda"), torch.zeros((2, 700), device="cuda"), torch.zeros((2, 300), device="cuda")]
+                for _ in range(2):  # back-to-back launches exercise the programmatic-dependent-launch path
+                    c.mul_mat_batch([(hs[0], x1, ys[0]), (hs[1], x1, ys[1]), (hs[2], x3, ys[2])], kernel=capi.KERNEL_GEMV_ROWS)
+                c.sync()
+                got = [y.cpu().numpy().copy() for y in ys]
+                if base is None:
+                    base = got
+                for a, b in zip(base, got):
+                    assert (a.view(np.uint32) == b.view(np.uint32)).all(), (cps, preq, pdl)
+                for h in hs:
+                    h.free()
+                c.close()
+    from oracle import pyoracle as po
+
+    assert _rel(base[0], oracle.mul_mat(po.Q8ACT_LANES, w1, x1.cpu().numpy())) <= TOL
+    assert _rel(base[2], oracle.mul_mat(po.Q8ACT_LANES, w3, x3.cpu().numpy())) <= TOL
 
 
 def test_emulated_row_shards_are_bit_identical_to_one_gpu(capi, ctx, oracle, torch_mod):
