@@ -188,6 +188,12 @@ class Context:
     def set_stream(self, cuda_stream: int | None):
         _check(lib.nhb_ctx_set_stream(self.handle, cuda_stream), self.handle)
 
+    def use_torch_stream(self):
+        """Run on torch's current stream, so tensors made by torch and kernels launched here are ordered."""
+        import torch
+
+        self.set_stream(torch.cuda.current_stream().cuda_stream)
+
     def set_option(self, name: str, value: int):
         _check(lib.nhb_ctx_set_option(self.handle, name.encode(), value), self.handle)
 

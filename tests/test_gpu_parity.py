@@ -14,6 +14,7 @@ def _rel(y, ref):
 @pytest.fixture(scope="module")
 def ctx(capi):
     c = capi.Context(0)
+    c.use_torch_stream()
     yield c
     c.close()
 
@@ -240,6 +241,7 @@ def test_rows_kernel_options_do_not_change_results(capi, oracle, torch_mod):
         for preq in (0, 1):
             for pdl in (0, 1):
                 c = capi.Context(0)
+                c.use_torch_stream()
                 c.set_option("rows_ctas_per_sm", cps)
                 c.set_option("prequantize", preq)
                 c.set_option("pdl", pdl)
@@ -277,6 +279,7 @@ def test_emulated_row_shards_are_bit_identical_to_one_gpu(capi, ctx, oracle, tor
         y = torch.zeros((M, N), device="cuda")
         for r in range(world):
             c = capi.Context(0, r, world)
+            c.use_torch_stream()
             hr = c.upload(w)
             assert (hr.n0, hr.n1) == capi.shard_rows(N, world, r)
             c.mul_mat(hr, xd, y)
