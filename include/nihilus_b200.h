@@ -137,6 +137,26 @@ int nhb_mul_mat_block_dots(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev
  * (the fp16-rounded d, widened) [M][K/32] */
 int nhb_quantize_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, int64_t M, int64_t K, int8_t* q_dev, float* d_dev);
 
+/* ---- for callers that cannot allocate ---- */
+/* No counterpart in the reference.  The decode GEMV (Q8 arithmetic, M <= 4) without a context, a weight handle or
+ * any allocation: the caller passes the two device planes of a weight (as nhb_weight_info_get returns them, or as
+ * nhb_repack_q8_0_host lays them out: int8 [rows][K], 32-byte aligned, and fp16 [rows][K/32]), device activations
+ * and outputs, and a cudaStream_t.  It is meant for hosts that must not call cudaMalloc where they run the
+ * operator: an engine that split one device arena at start-up by a fixed memory plan, code between
+ * cudaStreamBeginCapture and cudaStreamEndCapture, a token loop that cannot afford the device-wide
+ * synchronisation an allocation may cause.  The only temporary -- the Q8_0-quantised activations -- lives in a
+ * fixed 96 KiB array inside the library image (every GPU that loads the library holds it until the process
+ * exits), so a call is rejected with NHB_ERR_UNSUPPORTED unless M <= 4 and M * (K + K/8) <= 98304 bytes.
+ * The first call on each device looks up the array's device address; make that first call outside any stream
+ * capture.  All calls share the array and it keeps what the last call wrote (each call rewrites every byte it
+ * later reads, so nothing needs clearing): calls that overlap on the GPU -- two streams, two host threads -- race
+ * on it and must be serialised by the caller.  Never calls cudaMalloc, cudaFree or any allocating routine. */
+int nhb_mul_mat_q8_0_noalloc(const void* q_plane, const void* d_plane, int64_t rows, int64_t K, const float* x_dev, int64_t ldx,
+	float* y_dev, int64_t ldy, int64_t M, void* cuda_stream);
+/* capacity of that array in bytes (98304) and the last error text of this thread for the call above */
+int64_t nhb_noalloc_max_bytes(void);
+const char* nhb_noalloc_last_error(void);
+
 /* ---- launch-overhead removal: record a sequence of nhb_mul_mat* calls once, replay it per token ---- */
 int nhb_graph_begin(nhb_ctx* ctx);
 int nhb_graph_end(nhb_ctx* ctx, nhb_graph** out);

@@ -33,6 +33,7 @@ EXPORTS = (
     "nhb_weight_upload_q8_0", "nhb_weight_free", "nhb_weight_info_get", "nhb_weight_download_q8_0", "nhb_mul_mat",
     "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
+    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error",
 )
 
 
@@ -87,6 +88,9 @@ _sig("nhb_graph_free", _i, _vp, _vp)
 _sig("nhb_comm_unique_id", _i, _vp)
 _sig("nhb_comm_init", _i, _vp, _vp)
 _sig("nhb_all_gather", _i, _vp, _vp, _i64, _i64, _i64)
+_sig("nhb_mul_mat_q8_0_noalloc", _i, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i64, _vp)
+_sig("nhb_noalloc_max_bytes", _i64)
+_sig("nhb_noalloc_last_error", C.c_char_p)
 _sig("nhb_all_gather_batch", _i, _vp, C.POINTER(_vp), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), _i)
 
 
