@@ -96,6 +96,72 @@ namespace nhb {
 			}
 		}
 
+		// Prologue of both GEMV variants: quantise every distinct input of the batch into shared memory.
+		template<int MT> __device__ __forceinline__ void quantize_inputs(const rows_batch& b, unsigned char* act_smem, int tid) {
+		const uint32_t cn = cluster_size();
+		const uint32_t cr = cluster_rank();
+		for (int s = 0; s < b.n_slots; ++s) {
+			const rows_op* op  = &b.op[b.slot_op[s]];
+			unsigned char* act = act_smem + op->act_off;
+			const int K		   = op->K;
+			const int nb	   = K >> 5;
+			float* sda		   = reinterpret_cast<float*>(act + static_cast<size_t>(MT) * K);
+			if (b.preq) {
+				// quantised by quantize_q8_kernel into global scratch: int8 [MT][K] then f32 [MT][nb]
+				const unsigned char* src = b.preq_base + op->preq_off;
+				for (int i = tid; i < MT * nb * 2; i += ROWS_TPB) {
+					const int hb  = i >> 1;
+					const int m	  = hb / nb;
+					const int blk = hb - m * nb;
+					reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+				}
+				const float* sd = reinterpret_cast<const float*>(src + static_cast<size_t>(MT) * K);
+				for (int i = tid; i < MT * nb; i += ROWS_TPB)
+					sda[i] = __ldg(sd + i);
+			} else {
+				// two threads per 32-wide block (16 floats each); the pair shares its absmax by shuffle.  In a cluster
+				// launch every CTA quantises 1/cn of the input and writes it into the shared memory of all cn CTAs.
+				const float* x		= op->x;
+				const long long ldx = op->ldx;
+				const int n			= MT * nb * 2;
+				const int per		= ((n / 2 + static_cast<int>(cn) - 1) / static_cast<int>(cn)) * 2;
+				const int i_begin	= static_cast<int>(cr) * per;
+				const int i_end		= min(n, i_begin + per);
+				for (int i = i_begin + tid; i < i_end; i += ROWS_TPB) {
+					const int hb	= i >> 1;
+					const int m		= hb / nb;
+					const int blk	= hb - m * nb;
+					const float4* p = reinterpret_cast<const float4*>(x + static_cast<size_t>(m) * ldx + static_cast<size_t>(blk) * QK) + (i & 1) * 4;
+					const float4 v0 = __ldg(p), v1 = __ldg(p + 1), v2 = __ldg(p + 2), v3 = __ldg(p + 3);
+					float amax		= absmax4(v0, absmax4(v1, absmax4(v2, absmax4(v3, 0.f))));
+					amax			= fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
+					const act_scale sc = q8_scales(amax);
+					const uint4 qv	   = make_uint4(q8_pack4(v0.x, v0.y, v0.z, v0.w, sc.id), q8_pack4(v1.x, v1.y, v1.z, v1.w, sc.id),
+						   q8_pack4(v2.x, v2.y, v2.z, v2.w, sc.id), q8_pack4(v3.x, v3.y, v3.z, v3.w, sc.id));
+					uint4* dst		   = reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K) + ((i & 1) * nb + blk);
+					if (cn == 1) {
+						*dst = qv;
+						if ((i & 1) == 0)
+							sda[hb] = sc.d;
+					} else {
+						const uint32_t a_q = smem_u32(dst);
+						const uint32_t a_d = smem_u32(sda + hb);
+						for (uint32_t r = 0; r < cn; ++r) {
+							cluster_st_v4(cluster_map(a_q, r), qv);
+							if ((i & 1) == 0)
+								cluster_st_f32(cluster_map(a_d, r), sc.d);
+						}
+					}
+				}
+			}
+		}
+		// everyone's activations are complete (own writes and, in a cluster, the peers' remote stores)
+		if (cn == 1)
+			__syncthreads();
+		else
+			cluster_barrier();
+		}
+
 		template<int MT, int OCC> __global__ void __launch_bounds__(ROWS_TPB, OCC) gemv_q8_rows(const __grid_constant__ rows_batch b) {
 			extern __shared__ __align__(128) unsigned char act_smem[];
 			const int tid		 = threadIdx.x;
@@ -116,47 +182,7 @@ namespace nhb {
 			}
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
-			// ---- activations: quantise every distinct input of the batch into shared memory ----
-			for (int s = 0; s < b.n_slots; ++s) {
-				const rows_op* op  = &b.op[b.slot_op[s]];
-				unsigned char* act = act_smem + op->act_off;
-				const int K		   = op->K;
-				const int nb	   = K >> 5;
-				float* sda		   = reinterpret_cast<float*>(act + static_cast<size_t>(MT) * K);
-				if (b.preq) {
-					// quantised by quantize_q8_kernel into global scratch: int8 [MT][K] then f32 [MT][nb]
-					const unsigned char* src = b.preq_base + op->preq_off;
-					for (int i = tid; i < MT * nb * 2; i += ROWS_TPB) {
-						const int hb  = i >> 1;
-						const int m	  = hb / nb;
-						const int blk = hb - m * nb;
-						reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] = __ldg(reinterpret_cast<const uint4*>(src) + i);
-					}
-					const float* sd = reinterpret_cast<const float*>(src + static_cast<size_t>(MT) * K);
-					for (int i = tid; i < MT * nb; i += ROWS_TPB)
-						sda[i] = __ldg(sd + i);
-				} else {
-					// two threads per 32-wide block (16 floats each); the pair shares its absmax by shuffle
-					const float* x		= op->x;
-					const long long ldx = op->ldx;
-					for (int i = tid; i < MT * nb * 2; i += ROWS_TPB) {
-						const int hb	= i >> 1;
-						const int m		= hb / nb;
-						const int blk	= hb - m * nb;
-						const float4* p = reinterpret_cast<const float4*>(x + static_cast<size_t>(m) * ldx + static_cast<size_t>(blk) * QK) + (i & 1) * 4;
-						const float4 v0 = __ldg(p), v1 = __ldg(p + 1), v2 = __ldg(p + 2), v3 = __ldg(p + 3);
-						float amax		= absmax4(v0, absmax4(v1, absmax4(v2, absmax4(v3, 0.f))));
-						amax			= fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
-						const act_scale sc = q8_scales(amax);
-						reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] =
-							make_uint4(q8_pack4(v0.x, v0.y, v0.z, v0.w, sc.id), q8_pack4(v1.x, v1.y, v1.z, v1.w, sc.id),
-								q8_pack4(v2.x, v2.y, v2.z, v2.w, sc.id), q8_pack4(v3.x, v3.y, v3.z, v3.w, sc.id));
-						if ((i & 1) == 0)
-							sda[hb] = sc.d;
-					}
-				}
-			}
-			__syncthreads();
+			quantize_inputs<MT>(b, act_smem, tid);
 			// ---- rows ----
 			for (int row = row0; row < total_rows; row += W) {
 				while (cur + 1 < n_ops && row >= b.op[cur + 1].row_begin)
@@ -186,6 +212,107 @@ namespace nhb {
 			}
 		}
 
+
+		// ---- double-buffered variant: two 4 KB items in flight per warp ----
+		// A position in a warp's work list: one item (32*ITEM blocks) of one row, with everything needed to stream it.
+		struct item_pos {
+			row_desc rd;
+			const unsigned char* act;
+			float* yrow;
+			long long ldy;
+			int row;// batch-wide row index; >= total_rows means "past the end"
+			int b0;
+			int cur;// op index
+		};
+
+		__device__ __forceinline__ void pos_set_row(item_pos& p, const rows_batch& b, const unsigned char* act_smem, int row, int total_rows, int n_ops) {
+			p.row = row;
+			p.b0  = 0;
+			if (row < total_rows) {
+				while (p.cur + 1 < n_ops && row >= b.op[p.cur + 1].row_begin)
+					++p.cur;
+				const rows_op* op = &b.op[p.cur];
+				const int lrow	  = row - op->row_begin;
+				p.rd			  = make_row(op, lrow);
+				p.act			  = act_smem + op->act_off;
+				p.yrow			  = op->y + lrow;
+				p.ldy			  = op->ldy;
+			}
+		}
+
+		// the item after `p` in this warp's list
+		__device__ __forceinline__ item_pos pos_next(const item_pos& p, const rows_batch& b, const unsigned char* act_smem, int W, int total_rows, int n_ops) {
+			item_pos n = p;
+			n.b0	   = p.b0 + 32 * ITEM;
+			if (n.b0 >= p.rd.nb)
+				pos_set_row(n, b, act_smem, p.row + W, total_rows, n_ops);
+			return n;
+		}
+
+		template<int MT> __global__ void __launch_bounds__(ROWS_TPB, 2) gemv_q8_rows_db(const __grid_constant__ rows_batch b) {
+			extern __shared__ __align__(128) unsigned char act_smem[];
+			const int tid		 = threadIdx.x;
+			const int lane		 = tid & 31;
+			const int warp		 = tid >> 5;
+			const int W			 = gridDim.x * ROWS_WARPS;
+			const int total_rows = b.total_rows;
+			const int n_ops		 = b.n_ops;
+			item_regs ra, rb;
+			item_pos pa, pb;
+			pa.cur = 0;
+			pos_set_row(pa, b, act_smem, blockIdx.x * ROWS_WARPS + warp, total_rows, n_ops);
+			// ---- weights first: both buffers are filled before waiting for the previous kernel ----
+			if (pa.row < total_rows)
+				load_item(ra, pa.rd, pa.b0, lane);
+			pb = pa;
+			if (pa.row < total_rows) {
+				pb = pos_next(pa, b, act_smem, W, total_rows, n_ops);
+				if (pb.row < total_rows)
+					load_item(rb, pb.rd, pb.b0, lane);
+			}
+			pdl_launch_dependents();
+			pdl_wait_prior_grids();
+			quantize_inputs<MT>(b, act_smem, tid);
+			float acc[MT];
+#pragma unroll
+			for (int m = 0; m < MT; ++m)
+				acc[m] = 0.f;
+			auto finish_row = [&](const item_pos& p) {
+#pragma unroll
+				for (int m = 0; m < MT; ++m) {
+					const float v = warp_sum(acc[m]);
+					if (lane == 0)
+						p.yrow[static_cast<size_t>(m) * p.ldy] = v;
+					acc[m] = 0.f;
+				}
+			};
+			while (true) {
+				if (pa.row >= total_rows)
+					break;
+				compute_item<MT>(ra, acc, pa.act, pa.rd.nb, pa.b0, lane);
+				{
+					const bool row_end = pa.b0 + 32 * ITEM >= pa.rd.nb;
+					const item_pos done = pa;
+					pa = pos_next(pb, b, act_smem, W, total_rows, n_ops);
+					if (pb.row < total_rows && pa.row < total_rows)
+						load_item(ra, pa.rd, pa.b0, lane);
+					if (row_end)
+						finish_row(done);
+				}
+				if (pb.row >= total_rows)
+					break;
+				compute_item<MT>(rb, acc, pb.act, pb.rd.nb, pb.b0, lane);
+				{
+					const bool row_end = pb.b0 + 32 * ITEM >= pb.rd.nb;
+					const item_pos done = pb;
+					pb = pos_next(pa, b, act_smem, W, total_rows, n_ops);
+					if (pa.row < total_rows && pb.row < total_rows)
+						load_item(rb, pb.rd, pb.b0, lane);
+					if (row_end)
+						finish_row(done);
+				}
+			}
+		}
 	}
 
 	size_t gemv_rows_act_bytes(int64_t K, int M) {
@@ -197,7 +324,7 @@ namespace nhb {
 	}
 
 	// `b` arrives with op pointers/shapes, act_off/slot tables and preq fields filled by the caller.
-	cudaError_t launch_gemv_rows(const rows_batch& b_in, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches) {
+	cudaError_t launch_gemv_rows(const rows_batch& b_in, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer, int cluster) {
 		rows_batch b = b_in;
 		int rows	 = 0;
 		for (int i = 0; i < b.n_ops; ++i) {
@@ -223,13 +350,27 @@ namespace nhb {
 		lc.blockDim			= dim3(ROWS_TPB);
 		lc.dynamicSmemBytes = smem;
 		lc.stream			= cfg.stream;
-		cudaLaunchAttribute attr[1];
-		attr[0].id										   = cudaLaunchAttributeProgrammaticStreamSerialization;
-		attr[0].val.programmaticStreamSerializationAllowed = 1;
-		lc.attrs										   = attr;
-		lc.numAttrs										   = cfg.pdl ? 1 : 0;
+		cudaLaunchAttribute attr[2];
+		int n_attr = 0;
+		if (cfg.pdl) {
+			attr[n_attr].id											= cudaLaunchAttributeProgrammaticStreamSerialization;
+			attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+			++n_attr;
+		}
+		if (cluster > 1 && !b.preq) {
+			cluster = cluster >= 8 ? 8 : (cluster >= 4 ? 4 : 2);
+			grid	= ((grid + cluster - 1) / cluster) * cluster;
+			attr[n_attr].id				  = cudaLaunchAttributeClusterDimension;
+			attr[n_attr].val.clusterDim.x = static_cast<unsigned>(cluster);
+			attr[n_attr].val.clusterDim.y = 1;
+			attr[n_attr].val.clusterDim.z = 1;
+			++n_attr;
+			lc.gridDim = dim3(grid);
+		}
+		lc.attrs	= attr;
+		lc.numAttrs = n_attr;
 		// registers per thread are capped by the occupancy the grid was sized for (2, 3 or 4 CTAs per SM)
-		const int occ = ctas_per_sm >= 4 ? 4 : (ctas_per_sm == 3 ? 3 : 2);
+		const int occ = double_buffer ? 0 : (ctas_per_sm >= 4 ? 4 : (ctas_per_sm == 3 ? 3 : 2));
 #define NHB_ROWS_CASE(MT, OCC) \
 	if (M == MT && occ == OCC) { \
 		auto kern = gemv_q8_rows<MT, OCC>; \
@@ -252,6 +393,20 @@ namespace nhb {
 		NHB_ROWS_CASE(4, 3)
 		NHB_ROWS_CASE(4, 4)
 #undef NHB_ROWS_CASE
+#define NHB_ROWS_DB_CASE(MT) \
+	if (double_buffer && M == MT) { \
+		auto kern = gemv_q8_rows_db<MT>; \
+		e		  = cudaSuccess; \
+		if (smem > 48 * 1024) \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+		if (e == cudaSuccess) \
+			e = cudaLaunchKernelEx(&lc, kern, b); \
+	}
+		NHB_ROWS_DB_CASE(1)
+		NHB_ROWS_DB_CASE(2)
+		NHB_ROWS_DB_CASE(3)
+		NHB_ROWS_DB_CASE(4)
+#undef NHB_ROWS_DB_CASE
 		if (e == cudaSuccess && launches)
 			*launches += 1;
 		return e;

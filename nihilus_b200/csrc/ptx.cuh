@@ -99,6 +99,35 @@ namespace nhb {
 		return out != 0;
 	}
 
+	// ---- thread-block clusters: distributed shared memory (plain remote stores, no multicast copies) ----
+	__device__ __forceinline__ uint32_t cluster_size() {
+		uint32_t n;
+		asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+		return n;
+	}
+	__device__ __forceinline__ uint32_t cluster_rank() {
+		uint32_t r;
+		asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+		return r;
+	}
+	// address of the same shared-memory location in CTA `rank` of this cluster
+	__device__ __forceinline__ uint32_t cluster_map(uint32_t local_smem_addr, uint32_t rank) {
+		uint32_t a;
+		asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_smem_addr), "r"(rank));
+		return a;
+	}
+	__device__ __forceinline__ void cluster_st_v4(uint32_t addr, const uint4& v) {
+		asm volatile("st.shared::cluster.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+	}
+	__device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v) {
+		asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+	}
+	// all threads of all CTAs of the cluster; remote stores issued before it are visible after it
+	__device__ __forceinline__ void cluster_barrier() {
+		asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+		asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+	}
+
 	__device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
 		for (int o = 16; o > 0; o >>= 1)

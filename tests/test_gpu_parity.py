@@ -237,11 +237,13 @@ def test_rows_kernel_options_do_not_change_results(capi, oracle, torch_mod):
     w3 = synth.make_weight(300, 14336, 63)
     x1 = torch.from_numpy(synth.make_activation(2, 4096, 64)).cuda()
     x3 = torch.from_numpy(synth.make_activation(2, 14336, 65)).cuda()
-    for cps in (2, 3, 4):
+    for cps, db, cl in ((2, 0, 1), (3, 0, 1), (4, 0, 1), (2, 1, 1), (3, 1, 1), (3, 0, 2), (3, 0, 4), (2, 0, 8), (2, 1, 4)):
         for preq in (0, 1):
             for pdl in (0, 1):
                 c = capi.Context(0)
                 c.use_torch_stream()
+                c.set_option("rows_double_buffer", db)
+                c.set_option("rows_cluster", cl)
                 c.set_option("rows_ctas_per_sm", cps)
                 c.set_option("prequantize", preq)
                 c.set_option("pdl", pdl)
@@ -254,7 +256,7 @@ def test_rows_kernel_options_do_not_change_results(capi, oracle, torch_mod):
                 if base is None:
                     base = got
                 for a, b in zip(base, got):
-                    assert (a.view(np.uint32) == b.view(np.uint32)).all(), (cps, preq, pdl)
+                    assert (a.view(np.uint32) == b.view(np.uint32)).all(), (cps, db, cl, preq, pdl)
                 for h in hs:
                     h.free()
                 c.close()
