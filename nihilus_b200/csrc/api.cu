@@ -101,9 +101,10 @@ struct nhb_ctx {
 
 struct nhb_weight {
 	int64_t N = 0, K = 0, n0 = 0, n1 = 0;
-	int8_t* q  = nullptr;
-	__half* d  = nullptr;
-	int device = 0;
+	int8_t* q	= nullptr;
+	__half* d	= nullptr;
+	__half* w16 = nullptr;// fp16 copy of the quants for the tensor-core GEMM, made on first use
+	int device	= 0;
 };
 
 struct nhb_graph {
@@ -349,8 +350,20 @@ namespace {
 		if (rc != NHB_OK)
 			return rc;
 		int launches = 0;
+		if (!w->w16) {
+			// the tensor cores take fp16 operands: keep an exact fp16 copy of the int8 plane (2 bytes per weight)
+			if (ctx->capturing)
+				return fail(ctx, NHB_ERR_UNSUPPORTED, "the weight's fp16 plane must exist before graph capture; run the GEMM once first");
+			nhb_weight* wm = const_cast<nhb_weight*>(w);
+			NHB_CUDA(ctx, cudaMalloc(&wm->w16, static_cast<size_t>(rows) * w->K * sizeof(__half)));
+			cudaError_t ew = launch_widen_i8_f16(w->q, wm->w16, rows, w->K, ctx->stream);
+			if (ew != cudaSuccess)
+				return fail_cuda(ctx, ew, "widen_i8_f16 launch");
+			NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));// a programmatic-dependent launch after it must not overtake it
+			++launches;
+		}
 		std::string err;
-		cudaError_t e = launch_gemm_tc(w->q, w->d, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
+		cudaError_t e = launch_gemm_tc(w->w16, w->d, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
 			cfg_of(ctx), &launches, &err);
 		ctx->launches += launches;
 		if (e != cudaSuccess)
@@ -642,6 +655,8 @@ int nhb_weight_free(nhb_ctx* ctx, nhb_weight* w) {
 		cudaFree(w->q);
 	if (w->d)
 		cudaFree(w->d);
+	if (w->w16)
+		cudaFree(w->w16);
 	delete w;
 	return NHB_OK;
 }
@@ -717,7 +732,7 @@ int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int ac
 			return fail(ctx, NHB_ERR_UNSUPPORTED, "the tensor-core GEMM implements the Q8-activation arithmetic only");
 		for (int i = 0; i < n_ops; ++i) {
 			if (ops[i].w->n1 > ops[i].w->n0 && !gemm_tc_supports(ops[i].w->n1 - ops[i].w->n0, ops[i].w->K, M))
-				return fail(ctx, NHB_ERR_UNSUPPORTED, "shape not supported by the tensor-core GEMM (needs K % 128 == 0)");
+				return fail(ctx, NHB_ERR_UNSUPPORTED, "shape not supported by the tensor-core GEMM (needs K % 256 == 0)");
 			int rc = run_gemm(ctx, ops[i]);
 			if (rc != NHB_OK)
 				return rc;

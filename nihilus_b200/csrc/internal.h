@@ -92,7 +92,8 @@ namespace nhb {
 	// gemm_tc.cu
 	bool gemm_tc_supports(int64_t rows, int64_t K, int64_t M);
 	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M);
-	cudaError_t launch_gemm_tc(const int8_t* wq, const __half* wd, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
+	cudaError_t launch_widen_i8_f16(const int8_t* q, __half* out, int64_t rows, int64_t K, cudaStream_t s);
+	cudaError_t launch_gemm_tc(const __half* w16, const __half* wd, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
 		void* scratch, const launch_cfg& cfg, int* launches, std::string* err);
 
 }

@@ -138,6 +138,55 @@ def test_multi_row_stream_and_ldg_agree(capi, ctx, oracle, torch_mod, M):
         h.free()
 
 
+@pytest.mark.parametrize("N,K,M", [(128, 256, 9), (128, 256, 16), (300, 512, 17), (130, 1024, 33), (256, 4096, 64), (1000, 4096, 100),
+                                   (384, 4096, 128), (512, 4096, 200), (256, 14336, 257), (640, 4096, 512)])
+def test_tensor_core_gemm_prefill(capi, ctx, oracle, torch_mod, N, K, M):
+    """tcgen05 GEMM: exact int block dots on the tensor cores, f32 outputs within 1e-4 of the oracle; AUTO picks it for M > 8."""
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    w, x = _case(synth, N, K, M, 31337 + N + M)
+    h = ctx.upload(w)
+    ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
+    y = _run(ctx, torch_mod, h, x, kernel=capi.KERNEL_GEMM_TC)
+    assert _rel(y, ref) <= TOL
+    assert _rel(y, oracle.mul_mat(po.Q8ACT_F64, w, x)) <= TOL
+    ya = _run(ctx, torch_mod, h, x)  # AUTO
+    assert (ya.view(np.uint32) == y.view(np.uint32)).all()
+    # GEMV passes over the same rows agree to the tolerance as well (different summation order)
+    yg = _run(ctx, torch_mod, h, x[:8], kernel=capi.KERNEL_GEMV_ROWS)
+    assert _rel(y[:8], yg) <= TOL
+    h.free()
+
+
+def test_tensor_core_gemm_ragged_output_and_sharding(capi, ctx, oracle, torch_mod):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    torch = torch_mod
+    N, K, M = 777, 4096, 48
+    w, x = _case(synth, N, K, M, 4711)
+    xd = torch.from_numpy(x).cuda()
+    ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
+    full = None
+    for world in (1, 2, 3):
+        y = torch.full((M, N + 3), -7.0, device="cuda")
+        for r in range(world):
+            c = capi.Context(0, r, world)
+            c.use_torch_stream()
+            hr = c.upload(w)
+            capi._check(capi.lib.nhb_mul_mat(c.handle, hr.handle, xd.data_ptr(), K, y.data_ptr(), N + 3, M, capi.ACT_Q8, capi.KERNEL_GEMM_TC), c.handle)
+            c.sync()
+            hr.free()
+            c.close()
+        yy = y.cpu().numpy()
+        assert (yy[:, N:] == -7.0).all()
+        assert _rel(yy[:, :N], ref) <= TOL
+        if full is None:
+            full = yy.copy()
+        assert (yy.view(np.uint32) == full.view(np.uint32)).all()  # row shards are bit-identical to one GPU
+
+
 @pytest.mark.parametrize("N,K,M", [(64, 256, 1), (100, 4096, 3), (32, 14336, 2), (9, 96, 5)])
 def test_f32_activation_mode(capi, ctx, oracle, torch_mod, N, K, M):
     from nihilus_b200 import synth
