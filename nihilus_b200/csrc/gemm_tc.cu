@@ -13,7 +13,7 @@
 //               Q8 blocks of the K slice (plain bulk copies).  No multicast.
 //   warp 1      allocates TMEM, issues tcgen05.mma.kind::f16 (2 x K=16 per Q8 block) and the commits.
 //   warps 4-19  epilogue (4 token-column groups x 4 TMEM lane quarters): tcgen05.ld the block's int dots,
-//               acc = fma(P * d_w, d_a, acc) on packed fp32 pairs in registers, store Y.
+//               acc = fma(P * d_w, d_a, acc) in registers, store Y.
 // Every mbarrier wait is bounded; when one runs out the CTA records a code for the host, stops, frees its
 // tensor memory and returns.
 #include <cuda.h>
@@ -102,26 +102,6 @@ namespace nhb {
 		}
 		__device__ __forceinline__ void tmem_ld_wait() {
 			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-		}
-
-		// packed fp32 pairs (sm_100): one instruction, two lanes of IEEE fp32 math
-		__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-			uint64_t r;
-			asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-			return r;
-		}
-		__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-			asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-		}
-		__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-			uint64_t r;
-			asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-			return r;
-		}
-		__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-			uint64_t r;
-			asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-			return r;
 		}
 
 		// shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 bytes apart, 8-row groups 1024 bytes apart
@@ -283,10 +263,10 @@ namespace nhb {
 				const bool n_valid = n < p.rows;
 				const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 				const uint4* dw_row		 = reinterpret_cast<const uint4*>(p.wd + static_cast<size_t>(n_valid ? n : 0) * (p.K >> 5));
-				uint64_t acc[CW / 2];// fp32 pairs
+				float acc[CW];
 #pragma unroll
-				for (int i = 0; i < CW / 2; ++i)
-					acc[i] = 0ull;
+				for (int i = 0; i < CW; ++i)
+					acc[i] = 0.f;
 				uint4 dw8 = make_uint4(0, 0, 0, 0);
 				bool ok	  = true;
 				for (int t = 0; t < n_blk && ok; ++t) {
@@ -310,7 +290,6 @@ namespace nhb {
 					tc_fence_after();
 					const uint32_t w32 = (t & 7) < 2 ? dw8.x : ((t & 7) < 4 ? dw8.y : ((t & 7) < 6 ? dw8.z : dw8.w));
 					const float dw	   = __half2float(__ushort_as_half(static_cast<unsigned short>((t & 1) ? (w32 >> 16) : (w32 & 0xffffu))));
-					const uint64_t dw2 = pack2(dw, dw);
 					const float* da_s  = reinterpret_cast<const float*>(ring + static_cast<size_t>(s) * L::stage_bytes + L::a_bytes + L::b_bytes) + (t & 1) * N_T + g * CW;
 					const uint32_t col = static_cast<uint32_t>(a * N_T + g * CW);
 					constexpr int CH   = CW >= 16 ? 16 : CW;// columns per tcgen05.ld
@@ -334,9 +313,10 @@ namespace nhb {
 #pragma unroll
 						for (int i = 0; i < CH; i += 4) {
 							const float4 d4 = *reinterpret_cast<const float4*>(da_s + c0 + i);
-							const int j		= (c0 + i) >> 1;
-							acc[j]			= fma2(mul2(pack2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), dw2), pack2(d4.x, d4.y), acc[j]);
-							acc[j + 1]		= fma2(mul2(pack2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), dw2), pack2(d4.z, d4.w), acc[j + 1]);
+							acc[c0 + i + 0] = fmaf(__uint_as_float(v[i + 0]) * dw, d4.x, acc[c0 + i + 0]);
+							acc[c0 + i + 1] = fmaf(__uint_as_float(v[i + 1]) * dw, d4.y, acc[c0 + i + 1]);
+							acc[c0 + i + 2] = fmaf(__uint_as_float(v[i + 2]) * dw, d4.z, acc[c0 + i + 2]);
+							acc[c0 + i + 3] = fmaf(__uint_as_float(v[i + 3]) * dw, d4.w, acc[c0 + i + 3]);
 						}
 					}
 					if (t & 1) {
@@ -351,14 +331,10 @@ namespace nhb {
 						atomicExch(dev_status, DEV_TIMEOUT_MMA);
 				} else if (n_valid) {
 #pragma unroll
-					for (int i = 0; i < CW / 2; ++i) {
-						float lo, hi;
-						unpack2(acc[i], lo, hi);
-						const int m = m0 + g * CW + 2 * i;
+					for (int i = 0; i < CW; ++i) {
+						const int m = m0 + g * CW + i;
 						if (m < p.M)
-							p.y[static_cast<size_t>(m) * p.ldy + n] = lo;
-						if (m + 1 < p.M)
-							p.y[static_cast<size_t>(m + 1) * p.ldy + n] = hi;
+							p.y[static_cast<size_t>(m) * p.ldy + n] = acc[i];
 					}
 				}
 			}
