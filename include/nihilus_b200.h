@@ -112,6 +112,10 @@ long long nhb_ctx_launch_count(const nhb_ctx* ctx);
  * (cuda/memory_buffer.hpp:33-74) without the blocking */
 int nhb_memcpy_h2d(nhb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
 int nhb_memcpy_d2h(nhb_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+/* plain device memory on the context's GPU for activations and outputs: what memory_buffer<gpu>::init does for the
+ * reference's arena (cuda/memory_buffer.hpp:78-152).  256-byte aligned; not for use during graph capture. */
+int nhb_device_alloc(nhb_ctx* ctx, size_t bytes, void** out_dev);
+int nhb_device_free(nhb_ctx* ctx, void* dev);
 
 /* ---- weights: replaces the verbatim 34-byte upload of infra/model_parser.hpp:151-154, :933-937 ---- */
 /* host_blocks34 = the tensor's bytes as they sit in the GGUF file (N*(K/32)*34 bytes, whole tensor);
@@ -142,9 +146,8 @@ int nhb_quantize_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, int64_t M, 
  * any allocation: the caller passes the two device planes of a weight (as nhb_weight_info_get returns them, or as
  * nhb_repack_q8_0_host lays them out: int8 [rows][K], 32-byte aligned, and fp16 [rows][K/32]), device activations
  * and outputs, and a cudaStream_t.  It is meant for hosts that must not call cudaMalloc where they run the
- * operator: an engine that split one device arena at start-up by a fixed memory plan, code between
- * cudaStreamBeginCapture and cudaStreamEndCapture, a token loop that cannot afford the device-wide
- * synchronisation an allocation may cause.  The only temporary -- the Q8_0-quantised activations -- lives in a
+ * operator: an engine that split one device arena at start-up by a fixed memory plan, or a token loop that cannot
+ * afford the device-wide synchronisation an allocation may cause.  The only temporary -- the Q8_0-quantised activations -- lives in a
  * fixed 96 KiB array inside the library image (every GPU that loads the library holds it until the process
  * exits), so a call is rejected with NHB_ERR_UNSUPPORTED unless M <= 4 and M * (K + K/8) <= 98304 bytes.
  * The first call on each device looks up the array's device address; make that first call outside any stream

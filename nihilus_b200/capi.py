@@ -33,7 +33,7 @@ EXPORTS = (
     "nhb_weight_upload_q8_0", "nhb_weight_free", "nhb_weight_info_get", "nhb_weight_download_q8_0", "nhb_mul_mat",
     "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
-    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error",
+    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free",
 )
 
 
@@ -72,6 +72,8 @@ _sig("nhb_ctx_set_option", _i, _vp, C.c_char_p, _i)
 _sig("nhb_ctx_launch_count", C.c_longlong, _vp)
 _sig("nhb_memcpy_h2d", _i, _vp, _vp, _vp, C.c_size_t)
 _sig("nhb_memcpy_d2h", _i, _vp, _vp, _vp, C.c_size_t)
+_sig("nhb_device_alloc", _i, _vp, C.c_size_t, C.POINTER(_vp))
+_sig("nhb_device_free", _i, _vp, _vp)
 _sig("nhb_weight_upload_q8_0", _i, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("nhb_weight_free", _i, _vp, _vp)
 _sig("nhb_weight_info_get", _i, _vp, C.POINTER(WeightInfo))

@@ -588,6 +588,36 @@ int nhb_memcpy_d2h(nhb_ctx* ctx, void* dst_host, const void* src_dev, size_t byt
 	return NHB_OK;
 }
 
+int nhb_device_alloc(nhb_ctx* ctx, size_t bytes, void** out_dev) {
+	if (!ctx || !out_dev)
+		return fail(ctx, NHB_ERR_ARG, "nhb_device_alloc: null argument");
+	*out_dev = nullptr;
+	if (ctx->capturing)
+		return fail(ctx, NHB_ERR_UNSUPPORTED, "allocation during graph capture");
+	if (bytes == 0)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	cudaError_t e = cudaMalloc(out_dev, bytes);
+	if (e == cudaErrorMemoryAllocation) {
+		cudaGetLastError();
+		return fail(ctx, NHB_ERR_NOMEM, "nhb_device_alloc: out of device memory");
+	}
+	if (e != cudaSuccess)
+		return fail_cuda(ctx, e, "cudaMalloc");
+	return NHB_OK;
+}
+
+int nhb_device_free(nhb_ctx* ctx, void* dev) {
+	if (!ctx)
+		return fail(nullptr, NHB_ERR_ARG, "null context");
+	if (!dev)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+	NHB_CUDA(ctx, cudaFree(dev));
+	return NHB_OK;
+}
+
 int nhb_weight_upload_q8_0(nhb_ctx* ctx, const void* host_blocks34, int64_t N, int64_t K, nhb_weight** out) {
 	if (!ctx || !out)
 		return fail(ctx, NHB_ERR_ARG, "nhb_weight_upload_q8_0: null context or output");

@@ -1,9 +1,9 @@
 // nhb_mul_mat_q8_0_noalloc: the decode GEMV for callers that must not allocate.
 //
 // Some hosts of this library cannot call cudaMalloc at the point where they need a mul_mat: an engine that
-// reserved its whole device arena up front and hands out offsets from a fixed memory plan, code running
-// between cudaStreamBeginCapture and cudaStreamEndCapture, or a latency-critical token loop where an
-// allocation would mean an implicit device-wide synchronisation.  The regular entry points keep their
+// reserved its whole device arena up front and hands out offsets from a fixed memory plan (the reference's
+// memory_buffer works this way), or a latency-critical token loop where an allocation would mean an implicit
+// device-wide synchronisation.  The regular entry points keep their
 // temporary buffers in a context that grows them with cudaMalloc on demand; this one needs no context and no
 // weight handle.  Its only temporary -- the activations after Q8_0 quantisation, which the quantiser kernel
 // writes and the GEMV kernel reads -- lives in a fixed array that is part of the library image.

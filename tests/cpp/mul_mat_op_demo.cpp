@@ -1,0 +1,128 @@
+// Drives the Q8_0 mul_mat through the C++23 operator interface (include/nihilus_b200/mul_mat_op.hpp) the way the
+// reference engine would: upload two per-block weights, patch the runtime sequence length, dispatch one core.
+//
+//   mul_mat_op_demo check                                  compile-time and host-only checks, no GPU
+//   mul_mat_op_demo run <wk.bin> <wv.bin> <x.bin> M <yk.bin> <yv.bin>
+//        wk/wv: raw Q8_0 blocks of two 1024 x 4096 weights, x: f32 [M][4096]; writes f32 [M][1024] each
+#include <nihilus_b200/mul_mat_op.hpp>
+
+#include <cstring>
+#include <fstream>
+#include <iostream>
+#include <vector>
+
+using namespace nihilus_b200;
+
+// the static contract (same rules as the reference's kernel_traits)
+using k_traits = llama3_8b::attn_k::traits_type;
+static_assert(k_traits::K == 4096 && k_traits::N == 1024);
+static_assert(k_traits::derived_output_dims()[0] == 1024);
+static_assert(llama3_8b::ffn_down::traits_type::K == 14336 && llama3_8b::ffn_down::traits_type::N == 4096);
+static_assert(llama3_8b::output::traits_type::N == 128256);
+static_assert(llama3_8b::qkv_core::node_count == 3 && llama3_8b::gate_up_core::node_count == 2);
+static_assert(llama3_8b::act_t<4096>::runtime_dim == 1);
+
+static std::vector<char> slurp(const char* path) {
+	std::ifstream f(path, std::ios::binary);
+	if (!f)
+		throw std::runtime_error(std::string("cannot open ") + path);
+	return std::vector<char>((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+}
+
+static int check() {
+	// a dispatch without a context must surface as the library's error, through the exception convention
+	using core_t = mul_mat_core<llama3_8b::attn_k>;
+	core_t core{};
+	std::get<0>(core.nodes).activation.get_seq_length_dim() = 1;
+	bool threw = false;
+	try {
+		kernel_dispatcher<gpu_config<true>, processing_phases::eval_time, core_t>::impl(core, 0);
+	} catch (const mul_mat_error& e) {
+		threw = e.status == NHB_ERR_ARG;
+	}
+	if (!threw) {
+		std::cerr << "expected NHB_ERR_ARG for a null context\n";
+		return 1;
+	}
+	// eval_time is the one-token phase
+	std::get<0>(core.nodes).activation.get_seq_length_dim() = 4;
+	threw = false;
+	try {
+		kernel_dispatcher<gpu_config<true>, processing_phases::eval_time, core_t>::impl(core, 0);
+	} catch (const mul_mat_error&) {
+		threw = true;
+	}
+	if (!threw) {
+		std::cerr << "expected an error for eval_time with 4 tokens\n";
+		return 1;
+	}
+	std::cout << "check ok\n";
+	return 0;
+}
+
+static int run(char** a) {
+	const auto wk = slurp(a[0]), wv = slurp(a[1]), x = slurp(a[2]);
+	const int64_t M = std::atoll(a[3]);
+	constexpr int64_t K = 4096, N = 1024;
+	if (wk.size() != size_t(N) * (K / 32) * 34 || wv.size() != wk.size() || x.size() != size_t(M) * K * 4)
+		throw std::runtime_error("input sizes do not match attn_k / attn_v and M");
+	using cfg	 = gpu_config<true>;
+	using core_t = mul_mat_core<llama3_8b::attn_k, llama3_8b::attn_v>;
+	nhb_ctx* ctx = nullptr;
+	if (nhb_ctx_create(&ctx, 0, 0, 1) != NHB_OK)
+		raise<true>(NHB_ERR_CUDA, "nhb_ctx_create", nullptr);
+	nhb_weight *hk = nullptr, *hv = nullptr;
+	if (nhb_weight_upload_q8_0(ctx, wk.data(), N, K, &hk) != NHB_OK || nhb_weight_upload_q8_0(ctx, wv.data(), N, K, &hv) != NHB_OK)
+		raise<true>(NHB_ERR_CUDA, "nhb_weight_upload_q8_0", ctx);
+	void *xd = nullptr, *yk = nullptr, *yv = nullptr;
+	if (nhb_device_alloc(ctx, x.size(), &xd) != NHB_OK || nhb_device_alloc(ctx, size_t(M) * N * 4, &yk) != NHB_OK ||
+		nhb_device_alloc(ctx, size_t(M) * N * 4, &yv) != NHB_OK)
+		raise<true>(NHB_ERR_NOMEM, "nhb_device_alloc", ctx);
+	nhb_memcpy_h2d(ctx, xd, x.data(), x.size());
+
+	core_t core{};
+	core.ctx				= ctx;
+	constexpr int64_t block = 3;// any transformer block: each holds its own weight handle
+	auto& nk				= std::get<0>(core.nodes);
+	auto& nv				= std::get<1>(core.nodes);
+	nk.weight.data[block]	= hk;
+	nv.weight.data[block]	= hv;
+	nk.activation.data[0] = nv.activation.data[0] = xd;
+	nk.output.data[0]							  = yk;
+	nv.output.data[0]							  = yv;
+	nk.activation.get_seq_length_dim() = nv.activation.get_seq_length_dim() = static_cast<uint64_t>(M);
+	if (M == 1)
+		kernel_dispatcher<cfg, processing_phases::eval_time, core_t>::impl(core, block);
+	else
+		kernel_dispatcher<cfg, processing_phases::prompt_eval_time, core_t>::impl(core, block);
+
+	std::vector<float> ok(size_t(M) * N), ov(size_t(M) * N);
+	nhb_memcpy_d2h(ctx, ok.data(), yk, ok.size() * 4);
+	nhb_memcpy_d2h(ctx, ov.data(), yv, ov.size() * 4);
+	if (nhb_sync(ctx) != NHB_OK)
+		raise<true>(NHB_ERR_CUDA, "nhb_sync", ctx);
+	std::ofstream(a[4], std::ios::binary).write(reinterpret_cast<const char*>(ok.data()), ok.size() * 4);
+	std::ofstream(a[5], std::ios::binary).write(reinterpret_cast<const char*>(ov.data()), ov.size() * 4);
+	nhb_weight_free(ctx, hk);
+	nhb_weight_free(ctx, hv);
+	nhb_device_free(ctx, xd);
+	nhb_device_free(ctx, yk);
+	nhb_device_free(ctx, yv);
+	nhb_ctx_destroy(ctx);
+	std::cout << "run ok\n";
+	return 0;
+}
+
+int main(int argc, char** argv) {
+	try {
+		if (argc == 2 && !std::strcmp(argv[1], "check"))
+			return check();
+		if (argc == 8 && !std::strcmp(argv[1], "run"))
+			return run(argv + 2);
+	} catch (const std::exception& e) {
+		std::cerr << "error: " << e.what() << "\n";
+		return 2;
+	}
+	std::cerr << "usage: mul_mat_op_demo check | run wk.bin wv.bin x.bin M yk.bin yv.bin\n";
+	return 64;
+}

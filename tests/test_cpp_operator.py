@@ -1,0 +1,72 @@
+"""The C++23 operator interface (include/nihilus_b200/mul_mat_op.hpp) compiled with g++ and driven like the
+reference engine drives a core: traits -> kernel_dispatcher -> C ABI.  The host-only part runs without a GPU."""
+import os
+import shutil
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SRC = os.path.join(ROOT, "tests", "cpp", "mul_mat_op_demo.cpp")
+
+
+@pytest.fixture(scope="module")
+def demo(capi, tmp_path_factory):
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("g++ not available")
+    out = str(tmp_path_factory.mktemp("cpp") / "mul_mat_op_demo")
+    lib_dir = os.path.dirname(capi.LIB_PATH)
+    cmd = [gxx, "-std=c++23", "-O1", "-Wall", "-Werror", "-I" + os.path.join(ROOT, "include"), SRC, "-o", out, "-L" + lib_dir,
+           "-lnihilus_b200", "-Wl,-rpath," + lib_dir]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return out
+
+
+def test_traits_compile_and_errors_follow_the_exception_convention(demo):
+    r = subprocess.run([demo, "check"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "check ok" in r.stdout
+
+
+def test_static_checks_reject_a_mismatched_mul_mat(capi, tmp_path):
+    """K of the weight and of the activation differ: the trait must refuse to compile, like the reference's."""
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("g++ not available")
+    bad = tmp_path / "bad.cpp"
+    bad.write_text(
+        "#include <nihilus_b200/mul_mat_op.hpp>\n"
+        "using namespace nihilus_b200;\n"
+        "using w = operand<core_trait_dims<4096, 1024, 1, 1>, block_q8_0>;\n"
+        "using a = operand<core_trait_dims<2048, 1, 1, 1, 1>, float>;\n"
+        "using o = operand<core_trait_dims<1024, 1, 1, 1, 1>, float>;\n"
+        "using t = kernel_traits<kernel_types::mul_mat, o, w, a>;\n"
+        "int main() { return static_cast<int>(t::K); }\n"
+    )
+    r = subprocess.run([gxx, "-std=c++23", "-fsyntax-only", "-I" + os.path.join(ROOT, "include"), str(bad)], capture_output=True, text=True)
+    assert r.returncode != 0
+    assert "inner dimensions must match" in r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 5, 40])
+def test_dispatch_through_the_cpp_interface_matches_the_oracle(demo, oracle, tmp_path, M):
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    N, K = 1024, 4096
+    wk, wv = synth.make_weight(N, K, 901), synth.make_weight(N, K, 902)
+    x = synth.make_activation(M, K, 903 + M)
+    p = {n: str(tmp_path / n) for n in ("wk", "wv", "x", "yk", "yv")}
+    wk.tofile(p["wk"])
+    wv.tofile(p["wv"])
+    x.tofile(p["x"])
+    r = subprocess.run([demo, "run", p["wk"], p["wv"], p["x"], str(M), p["yk"], p["yv"]], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    for w, name in ((wk, "yk"), (wv, "yv")):
+        y = np.fromfile(p[name], dtype=np.float32).reshape(M, N)
+        ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
+        assert float(np.abs(y - ref).max() / np.abs(ref).max()) <= 1e-4

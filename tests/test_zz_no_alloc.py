@@ -3,7 +3,7 @@
 Collected last on purpose: a run that stops at the first failure has by then exercised every other test.
 
 Who needs it: a host that may not allocate where it calls the operator -- an engine that carved up one device
-arena at start-up and runs from a fixed memory plan, code inside a stream capture, a token loop that cannot
+arena at start-up and runs from a fixed memory plan, or a token loop that cannot
 afford the device-wide synchronisation an allocation may bring.  The entry point takes raw device pointers
 (weight planes, activations, outputs) and keeps its one temporary, the quantised activations, in a fixed
 96 KiB array inside the library.
