@@ -97,7 +97,8 @@ int64_t nhb_mul_mat_flops(int64_t N, int64_t K, int64_t M);
  *      cuda/memory_buffer.hpp:78-152) ---- */
 int nhb_ctx_create(nhb_ctx** out, int device, int rank, int world);
 int nhb_ctx_destroy(nhb_ctx* ctx);
-/* run everything on the caller's cudaStream_t (NULL = the context's own non-blocking stream) */
+/* run everything on the caller's cudaStream_t.  NULL selects the context's own non-blocking stream; to name the
+ * legacy default stream pass cudaStreamLegacy, not 0. */
 int nhb_ctx_set_stream(nhb_ctx* ctx, void* cuda_stream);
 /* explicit synchronisation + device status check; the reference syncs after every launch (cuda/cuda_12.hpp:679) */
 int nhb_sync(nhb_ctx* ctx);

@@ -198,7 +198,9 @@ class Context:
         """Run on torch's current stream, so tensors made by torch and kernels launched here are ordered."""
         import torch
 
-        self.set_stream(torch.cuda.current_stream().cuda_stream)
+        # torch reports its default stream as handle 0, which nhb_ctx_set_stream reads as "the context's own
+        # stream"; 1 is cudaStreamLegacy, the same default stream named explicitly
+        self.set_stream(torch.cuda.current_stream().cuda_stream or 1)
 
     def set_option(self, name: str, value: int):
         _check(lib.nhb_ctx_set_option(self.handle, name.encode(), value), self.handle)

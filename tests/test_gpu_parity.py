@@ -340,31 +340,36 @@ def test_emulated_row_shards_are_bit_identical_to_one_gpu(capi, ctx, oracle, tor
         assert (y.cpu().numpy().view(np.uint32) == full.view(np.uint32)).all()
 
 
-def test_graph_replay_and_determinism(capi, ctx, oracle, torch_mod):
+def test_graph_replay_and_determinism(capi, oracle, torch_mod):
     from nihilus_b200 import synth
     from oracle import pyoracle as po
 
     torch = torch_mod
     N, K = 2048, 4096
     w, x = _case(synth, N, K, 1, 808)
-    h = ctx.upload(w)
-    xd = torch.from_numpy(x).cuda()
-    y = torch.zeros((1, N), device="cuda")
-    ctx.mul_mat(h, xd, y)
-    ctx.sync()
-    first = y.clone()
-    ctx.graph_begin()
-    for _ in range(3):
+    side = torch.cuda.Stream()  # the legacy default stream cannot be captured
+    with torch.cuda.stream(side):
+        ctx = capi.Context(0)
+        ctx.use_torch_stream()
+        h = ctx.upload(w)
+        xd = torch.from_numpy(x).cuda()
+        y = torch.zeros((1, N), device="cuda")
         ctx.mul_mat(h, xd, y)
-    g = ctx.graph_end()
-    y.zero_()
-    g.launch()
-    g.launch()
-    ctx.sync()
-    assert torch.equal(first, y)
-    assert _rel(y.cpu().numpy(), oracle.mul_mat(po.Q8ACT_LANES, w, x)) <= TOL
-    g.free()
-    h.free()
+        ctx.sync()
+        first = y.clone()
+        ctx.graph_begin()
+        for _ in range(3):
+            ctx.mul_mat(h, xd, y)
+        g = ctx.graph_end()
+        y.zero_()
+        g.launch()
+        g.launch()
+        ctx.sync()
+        assert torch.equal(first, y)
+        assert _rel(y.cpu().numpy(), oracle.mul_mat(po.Q8ACT_LANES, w, x)) <= TOL
+        g.free()
+        h.free()
+        ctx.close()
 
 
 def test_host_buffer_entry_point(capi, ctx, oracle):
