@@ -104,6 +104,7 @@ struct nhb_weight {
 	int8_t* q	= nullptr;
 	__half* d	= nullptr;
 	__half* w16 = nullptr;// fp16 copy of the quants for the tensor-core GEMM, made on first use
+	float* wdT	= nullptr;// f32 block-major copy of the scales [K/32][gemm_tc_pad(rows)], made with it
 	int device	= 0;
 };
 
@@ -351,19 +352,31 @@ namespace {
 			return rc;
 		int launches = 0;
 		if (!w->w16) {
-			// the tensor cores take fp16 operands: keep an exact fp16 copy of the int8 plane (2 bytes per weight)
+			// the tensor cores take fp16 operands: keep an exact fp16 copy of the int8 plane (2 bytes per weight) and the
+			// scales as f32, block-major, so that a tile's scales of one block are contiguous
 			if (ctx->capturing)
-				return fail(ctx, NHB_ERR_UNSUPPORTED, "the weight's fp16 plane must exist before graph capture; run the GEMM once first");
+				return fail(ctx, NHB_ERR_UNSUPPORTED, "the weight's GEMM planes must exist before graph capture; run the GEMM once first");
 			nhb_weight* wm = const_cast<nhb_weight*>(w);
+			const size_t sb = static_cast<size_t>(w->K / 32) * gemm_tc_pad(rows) * sizeof(float);
 			NHB_CUDA(ctx, cudaMalloc(&wm->w16, static_cast<size_t>(rows) * w->K * sizeof(__half)));
-			cudaError_t ew = launch_widen_i8_f16(w->q, wm->w16, rows, w->K, ctx->stream);
-			if (ew != cudaSuccess)
-				return fail_cuda(ctx, ew, "widen_i8_f16 launch");
+			cudaError_t ew = cudaMalloc(&wm->wdT, sb);
+			if (ew == cudaSuccess)
+				ew = cudaMemsetAsync(wm->wdT, 0, sb, ctx->stream);
+			if (ew == cudaSuccess)
+				ew = launch_weight_gemm_planes(w->q, w->d, rows, w->K, wm->w16, wm->wdT, ctx->stream);
+			if (ew != cudaSuccess) {
+				cudaFree(wm->w16);
+				wm->w16 = nullptr;
+				if (wm->wdT)
+					cudaFree(wm->wdT);
+				wm->wdT = nullptr;
+				return fail_cuda(ctx, ew, "GEMM weight planes");
+			}
 			NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));// a programmatic-dependent launch after it must not overtake it
-			++launches;
+			launches += 2;
 		}
 		std::string err;
-		cudaError_t e = launch_gemm_tc(w->w16, w->d, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
+		cudaError_t e = launch_gemm_tc(w->w16, w->wdT, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
 			cfg_of(ctx), &launches, &err);
 		ctx->launches += launches;
 		if (e != cudaSuccess)
@@ -687,6 +700,8 @@ int nhb_weight_free(nhb_ctx* ctx, nhb_weight* w) {
 		cudaFree(w->d);
 	if (w->w16)
 		cudaFree(w->w16);
+	if (w->wdT)
+		cudaFree(w->wdT);
 	delete w;
 	return NHB_OK;
 }
@@ -762,7 +777,7 @@ int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int ac
 			return fail(ctx, NHB_ERR_UNSUPPORTED, "the tensor-core GEMM implements the Q8-activation arithmetic only");
 		for (int i = 0; i < n_ops; ++i) {
 			if (ops[i].w->n1 > ops[i].w->n0 && !gemm_tc_supports(ops[i].w->n1 - ops[i].w->n0, ops[i].w->K, M))
-				return fail(ctx, NHB_ERR_UNSUPPORTED, "shape not supported by the tensor-core GEMM (needs K % 256 == 0)");
+				return fail(ctx, NHB_ERR_UNSUPPORTED, "shape not supported by the tensor-core GEMM (needs K % 64 == 0)");
 			int rc = run_gemm(ctx, ops[i]);
 			if (rc != NHB_OK)
 				return rc;

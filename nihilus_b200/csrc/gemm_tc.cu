@@ -2,22 +2,28 @@
 //
 // Arithmetic is the reference's quantize_row_q8_0 + vec_dot_q8_0_q8_0 (include/nihilus-incl/cpu/avx_2.hpp
 // :4439-4489, :4749-4780), unchanged: activations are quantised to Q8_0, every 32-wide block contributes
-// float(exact int dot) * (d_w * d_a).  The tensor cores compute the exact int dot: both operands are the int8
-// quants widened to fp16 (|q| <= 127 is exact in fp16, products and their 32-term sums are exact in the fp32
-// accumulator), one accumulator stage per Q8 block, never accumulated across blocks.  The per-block scales
-// are applied by the epilogue warps while the next block's MMA runs on the other accumulator stage.
+// fma(float(exact int dot), d_w * d_a, acc).  The tensor cores compute the exact int dot: both operands are the
+// int8 quants widened to fp16 (|q| <= 127 is exact in fp16, products and their 32-term sums are exact in the fp32
+// accumulator), one accumulator stage per Q8 block, never accumulated across blocks.  The per-block scales are
+// applied by the epilogue warps while the next block's MMA runs on the other accumulator stage.
 //
-// Layout per CTA: D[128 weight rows][N_T tokens] in TMEM (row = lane, token = column), two stages.
-//   warp 0      TMA producer: A tile [128][64] fp16 of the weight's fp16 plane, B tile [N_T][64] fp16 of the
-//               quantised activations (both K-major, 128-byte swizzle), and the activation scales of the two
-//               Q8 blocks of the K slice (plain bulk copies).  No multicast.
+// One CTA owns a tile of 128 "lane" rows x N_T "column" rows of the output, where either side may be the weight:
+//   tokens < 128:  lanes = weight rows, columns = tokens (N_T = tokens rounded up to 16)
+//   otherwise:     lanes = tokens,      columns = weight rows (N_T picked so the tile count fills whole waves)
+// D[128][N_T] sits in TMEM (lane = TMEM lane, column = TMEM column), two stages of 256 columns.
+//   warp 0      TMA producer: A tile [128][64] fp16, B tile [N_T][64] fp16 (both K-major, 128-byte swizzle) and the
+//               f32 scales of the two Q8 blocks of the K slice for both sides (plain bulk copies).  No multicast.
 //   warp 1      allocates TMEM, issues tcgen05.mma.kind::f16 (2 x K=16 per Q8 block) and the commits.
-//   warps 4-19  epilogue (4 token-column groups x 4 TMEM lane quarters): tcgen05.ld the block's int dots,
-//               acc = fma(P * d_w, d_a, acc) in registers, store Y.
+//   warps 4-19  epilogue (4 TMEM lane quarters x 4 column groups).  They read the accumulator with the 16x256b
+//               shape, which gives every thread 4 lanes x 2 adjacent columns per 8 columns: a column scale fetched
+//               from shared memory serves 4 rows (a lane-per-thread shape needs one shared-memory broadcast per
+//               element and saturates the load/store unit), the 4 row scales live in registers.
 // Every mbarrier wait is bounded; when one runs out the CTA records a code for the host, stops, frees its
 // tensor memory and returns.
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "internal.h"
@@ -34,14 +40,14 @@ namespace nhb {
 		constexpr int GM_THREADS   = (4 + GM_EPI_WARPS) * 32;// warpgroup 0: producer warp, MMA warp, two idle warps; then the epilogue warpgroups
 
 		// ---- PTX: TMA, tcgen05 ----
-		__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+		__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
 			asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-							 smem_u32(dst_smem)),
+							 dst_smem),
 				"l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
 				: "memory");
 		}
-		__device__ __forceinline__ void bulk_g2s_plain(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
-			asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)), "l"(src),
+		__device__ __forceinline__ void bulk_g2s_plain(uint32_t dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+			asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem), "l"(src),
 				"r"(bytes), "r"(smem_u32(bar))
 				: "memory");
 		}
@@ -73,37 +79,9 @@ namespace nhb {
 		__device__ __forceinline__ void umma_commit(uint64_t* bar) {
 			asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 		}
-		[[maybe_unused]] __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-			asm volatile(
-				"tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-				: "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
-				"=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-				"=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
-				"=r"(v[31])
-				: "r"(taddr)
-				: "memory");
-		}
-		__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32]) {
-			asm volatile(
-				"tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-				: "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
-				"=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-				: "r"(taddr)
-				: "memory");
-		}
-		__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[32]) {
-			asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-						 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-						 : "r"(taddr)
-						 : "memory");
-		}
-		__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&v)[32]) {
-			asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(taddr) : "memory");
-		}
 		__device__ __forceinline__ void tmem_ld_wait() {
 			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 		}
-
 		// shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 bytes apart, 8-row groups 1024 bytes apart
 		__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 			uint64_t d = 0;
@@ -120,25 +98,19 @@ namespace nhb {
 			return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(GM_ROWS >> 4) << 24);
 		}
 
+		constexpr int GM_STAGE_COLS = 256;// TMEM columns per accumulator stage
+
 		struct gemm_params {
-			const __half* wd;// [rows][K/32] weight scales
-			const float* daT;// [K/32][m_pad] activation scales, block-major
+			const float* row_scale;// [K/32][lanes_pad]  scales of the lane side, block-major
+			const float* col_scale;// [K/32][cols_pad]   scales of the column side, block-major
 			float* y;// output, already offset to this shard's first column
 			long long ldy;
-			int rows;
+			int lanes_pad, cols_pad;
+			int lane_rows;// valid rows on the lane side (weight rows, or tokens when swapped)
+			int col_rows;// valid rows on the column side
 			int K;
-			int M;
-			int m_pad;
-		};
-
-		template<int N_T> struct gemm_smem {
-			static constexpr int a_bytes	 = GM_ROWS * GM_KSLICE * 2;// 16 KiB
-			static constexpr int b_bytes	 = N_T * GM_KSLICE * 2;
-			static constexpr int da_bytes	 = 2 * N_T * 4;// two Q8 blocks
-			static constexpr int stage_bytes = a_bytes + b_bytes + ((da_bytes + 1023) / 1024) * 1024;
-			static constexpr int stages		 = (200 * 1024) / stage_bytes > 6 ? 6 : (200 * 1024) / stage_bytes;
-			static constexpr int head_bytes	 = 1024;// barriers + tmem slot
-			static constexpr int total		 = head_bytes + stages * stage_bytes + 1024;// + alignment slack
+			int swapped;// 0: lanes = weight rows, columns = tokens; 1: lanes = tokens, columns = weight rows
+			int stages;
 		};
 
 		struct gemm_head {
@@ -150,25 +122,78 @@ namespace nhb {
 			int abort_flag;
 		};
 
+		constexpr int GM_HEAD_BYTES = 1024;
+		constexpr int GM_A_BYTES	= GM_ROWS * GM_KSLICE * 2;// 16 KiB
+
+		// bytes of one pipeline stage: A tile, B tile, then [2 blocks][128 row scales + n_t column scales] floats
+		__host__ __device__ constexpr int gemm_stage_bytes(int n_t) {
+			return GM_A_BYTES + n_t * GM_KSLICE * 2 + ((2 * (GM_ROWS + n_t) * 4 + 1023) / 1024) * 1024;
+		}
+
+		// packed fp32 pairs: one issue slot, two IEEE fp32 results
+		__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+			uint64_t r;
+			asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+			return r;
+		}
+		__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+			asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+		}
+		__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+			uint64_t r;
+			asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+			return r;
+		}
+		__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+			uint64_t r;
+			asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+			return r;
+		}
+		__device__ __forceinline__ float lds_f32(uint32_t addr) {
+			float v;
+			asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+			return v;
+		}
+		__device__ __forceinline__ uint64_t lds_b64(uint32_t addr) {
+			uint64_t v;
+			asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
+			return v;
+		}
+		// 16 lanes x 16 columns as packed pairs: v[2k] = lane t/4, columns 8k + 2(t%4), +1; v[2k+1] = lane t/4 + 8, same columns
+		__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint64_t (&v)[4]) {
+			uint32_t r[8];
+			asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+						 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+						 : "r"(taddr)
+						 : "memory");
+#pragma unroll
+			for (int i = 0; i < 4; ++i)
+				asm("mov.b64 %0, {%1, %2};" : "=l"(v[i]) : "r"(r[2 * i]), "r"(r[2 * i + 1]));
+		}
+
 		template<int N_T> __global__ void __launch_bounds__(GM_THREADS, 1)
 			gemm_q8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const gemm_params p, int* __restrict__ dev_status) {
-			using L = gemm_smem<N_T>;
-			constexpr int S			= L::stages;
-			constexpr int CW		= N_T / 4;// token columns per epilogue warp
-			constexpr uint32_t TCOLS = (2 * N_T) < 32 ? 32 : (2 * N_T);
+			constexpr int STAGE_BYTES = gemm_stage_bytes(N_T);
+			constexpr int B_BYTES	  = N_T * GM_KSLICE * 2;
+			constexpr int SC_FLOATS	  = GM_ROWS + N_T;// scales of one Q8 block: lane side, then column side
+			constexpr int UNITS		  = N_T / 8;// 8-column units in the tile, dealt to the four column groups
+			constexpr int BASE		  = UNITS / 4;
+			constexpr int REM		  = UNITS % 4;
+			constexpr int MAXU		  = BASE + (REM ? 1 : 0);
+			constexpr int PAIRS		  = (MAXU + 1) / 2;
 			extern __shared__ unsigned char smem_raw[];
 			// 1024-byte alignment for the 128-byte swizzle atoms
 			unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 			gemm_head* hd		= reinterpret_cast<gemm_head*>(base);
-			unsigned char* ring = base + L::head_bytes;
+			const uint32_t ring = smem_u32(base + GM_HEAD_BYTES);
 
 			const int tid	= threadIdx.x;
 			const int warp	= tid >> 5;
 			const int lane	= tid & 31;
-			const int n0	= blockIdx.x * GM_ROWS;
-			const int m0	= blockIdx.y * N_T;
+			const int S		= p.stages;
+			const int lane0 = blockIdx.x * GM_ROWS;// first lane-side row of this tile
+			const int col0	= blockIdx.y * N_T;// first column-side row of this tile
 			const int n_kb	= p.K / GM_KSLICE;
-			const int n_blk = n_kb * 2;
 
 			if (tid == 0) {
 				for (int s = 0; s < S; ++s) {
@@ -183,7 +208,7 @@ namespace nhb {
 				fence_mbar_init();
 			}
 			if (warp == 1)
-				tmem_alloc(&hd->tmem_base, TCOLS);
+				tmem_alloc(&hd->tmem_base, 2 * GM_STAGE_COLS);
 			tc_fence_before();
 			__syncthreads();
 			tc_fence_after();
@@ -193,148 +218,196 @@ namespace nhb {
 
 			// Registers follow the work: 20 warps put five on every scheduler, which caps a uniform allocation at 96 per
 			// thread; warpgroup 0 (copy and MMA issue, a handful of registers) hands most of its share to the epilogue.
+			// The CTA can only redistribute what it was launched with: 128 threads x (96 - 32) released = 512 threads x
+			// (112 - 96) taken.  Asking for more than 112 would wait forever for registers that never come.
 			if (warp < 4) {
 				asm volatile("setmaxnreg.dec.sync.aligned.u32 32;" ::: "memory");
-			if (warp == 0) {
-				// ---------------- TMA producer ----------------
-				if (lane == 0) {
-					for (int kb = 0; kb < n_kb; ++kb) {
-						const int s = kb % S;
-						if (kb >= S && !mbar_wait(&hd->empty[s], ((kb / S) - 1) & 1)) {
-							atomicExch(dev_status, DEV_TIMEOUT_EMPTY);
-							break;
-						}
-						unsigned char* st = ring + static_cast<size_t>(s) * L::stage_bytes;
-						mbar_expect_tx(&hd->full[s], L::a_bytes + L::b_bytes + L::da_bytes);
-						tma_load_2d(st, &map_a, kb * GM_KSLICE, n0, &hd->full[s]);
-						tma_load_2d(st + L::a_bytes, &map_b, kb * GM_KSLICE, m0, &hd->full[s]);
-						float* da_s = reinterpret_cast<float*>(st + L::a_bytes + L::b_bytes);
-						bulk_g2s_plain(da_s, p.daT + static_cast<size_t>(2 * kb) * p.m_pad + m0, N_T * 4, &hd->full[s]);
-						bulk_g2s_plain(da_s + N_T, p.daT + static_cast<size_t>(2 * kb + 1) * p.m_pad + m0, N_T * 4, &hd->full[s]);
-					}
-				}
-			} else if (warp == 1) {
-				// ---------------- MMA issuer ----------------
-				if (lane == 0) {
-					constexpr uint32_t idesc = idesc_f16(N_T);
-					for (int kb = 0; kb < n_kb; ++kb) {
-						const int s = kb % S;
-						if (!mbar_wait(&hd->full[s], (kb / S) & 1)) {
-							atomicExch(dev_status, DEV_TIMEOUT_FULL);
-							break;
-						}
-						tc_fence_after();
-						const uint32_t a_addr = smem_u32(ring + static_cast<size_t>(s) * L::stage_bytes);
-						const uint32_t b_addr = a_addr + L::a_bytes;
-						bool ok				  = true;
+				if (warp == 0) {
+					// ---------------- TMA producer ----------------
+					if (lane == 0) {
+						constexpr uint32_t tx = static_cast<uint32_t>(GM_A_BYTES + B_BYTES + 2 * SC_FLOATS * 4);
+						const float* rsrc	  = p.row_scale + lane0;
+						const float* csrc	  = p.col_scale + col0;
+						int s				  = 0;
+						uint32_t ph			  = 1;// a fresh barrier reads as "phase 1 complete": the first S waits pass at once
+						for (int kb = 0; kb < n_kb; ++kb) {
+							if (!mbar_wait(&hd->empty[s], ph)) {
+								atomicExch(dev_status, DEV_TIMEOUT_EMPTY);
+								break;
+							}
+							const uint32_t st = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
+							mbar_expect_tx(&hd->full[s], tx);
+							tma_load_2d(st, &map_a, kb * GM_KSLICE, lane0, &hd->full[s]);
+							tma_load_2d(st + GM_A_BYTES, &map_b, kb * GM_KSLICE, col0, &hd->full[s]);
+							const uint32_t sc = st + GM_A_BYTES + B_BYTES;
 #pragma unroll
-						for (int j = 0; j < 2; ++j) {
-							const int t = 2 * kb + j;// Q8 block index
-							const int a = t & 1;// accumulator stage
-							const int u = t >> 1;
-							if (u >= 1 && !mbar_wait(&hd->tmem_empty[a], (u - 1) & 1)) {
-								atomicExch(dev_status, DEV_TIMEOUT_MMA);
-								ok = false;
+							for (int j = 0; j < 2; ++j) {
+								bulk_g2s_plain(sc + j * SC_FLOATS * 4, rsrc, GM_ROWS * 4, &hd->full[s]);
+								bulk_g2s_plain(sc + (j * SC_FLOATS + GM_ROWS) * 4, csrc, N_T * 4, &hd->full[s]);
+								rsrc += p.lanes_pad;
+								csrc += p.cols_pad;
+							}
+							if (++s == S) {
+								s = 0;
+								ph ^= 1;
+							}
+						}
+					}
+				} else if (warp == 1) {
+					// ---------------- MMA issuer ----------------
+					if (lane == 0) {
+						constexpr uint32_t idesc = idesc_f16(N_T);
+						int s					 = 0;
+						uint32_t ph				 = 0;
+						bool ok					 = true;
+						for (int kb = 0; kb < n_kb && ok; ++kb) {
+							if (!mbar_wait(&hd->full[s], ph)) {
+								atomicExch(dev_status, DEV_TIMEOUT_FULL);
 								break;
 							}
 							tc_fence_after();
-							const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(a * N_T);
+							const uint32_t a_addr = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
+							const uint32_t b_addr = a_addr + GM_A_BYTES;
 #pragma unroll
-							for (int k2 = 0; k2 < 2; ++k2) {
-								const uint32_t off = static_cast<uint32_t>(j * 64 + k2 * 32);// bytes inside the 128-byte row
-								umma_f16(d_tmem, smem_desc_sw128(a_addr + off), smem_desc_sw128(b_addr + off), idesc, k2);
+							for (int j = 0; j < 2; ++j) {
+								// Q8 block 2 kb + j goes to accumulator stage j; its previous user was block 2 (kb - 1) + j
+								if (!mbar_wait(&hd->tmem_empty[j], (kb & 1) ^ 1)) {
+									atomicExch(dev_status, DEV_TIMEOUT_MMA);
+									ok = false;
+									break;
+								}
+								tc_fence_after();
+								const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(j * GM_STAGE_COLS);
+#pragma unroll
+								for (int k2 = 0; k2 < 2; ++k2) {
+									const uint32_t off = static_cast<uint32_t>(j * 64 + k2 * 32);// bytes inside the 128-byte row
+									umma_f16(d_tmem, smem_desc_sw128(a_addr + off), smem_desc_sw128(b_addr + off), idesc, k2);
+								}
+								umma_commit(&hd->tmem_full[j]);
 							}
-							umma_commit(&hd->tmem_full[a]);
+							if (ok)
+								umma_commit(&hd->empty[s]);// the slot's operands are free once these MMAs have run
+							if (++s == S) {
+								s = 0;
+								ph ^= 1;
+							}
 						}
-						if (!ok)
-							break;
-						umma_commit(&hd->empty[s]);// the slot's operands are free once these MMAs have run
 					}
 				}
-			}
 			} else {
 				// ---------------- epilogue ----------------
 				asm volatile("setmaxnreg.inc.sync.aligned.u32 112;" ::: "memory");
-				const int e		   = warp - 4;// 0..15
 				const int q		   = warp & 3;// TMEM lane quarter this warp may touch
-				const int g		   = e >> 2;// which quarter of the token columns
-				const int n_local  = q * 32 + lane;
-				const int n		   = n0 + n_local;
-				const bool n_valid = n < p.rows;
-				const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-				const uint4* dw_row		 = reinterpret_cast<const uint4*>(p.wd + static_cast<size_t>(n_valid ? n : 0) * (p.K >> 5));
-				float acc[CW];
+				const int g		   = (warp - 4) >> 2;// column group
+				const int t4	   = lane & 3;
+				const int my_units = BASE + (g < REM ? 1 : 0);
+				const int my_pairs = (my_units + 1) >> 1;
+				const int col_off  = (BASE * g + (g < REM ? g : REM)) * 8;// first column of this warp inside the tile
+				const int r0	   = q * 32 + (lane >> 2);// this thread's rows inside the tile: r0 + 8j, j = 0..3
+				const uint32_t tl0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(col_off);
+				const uint32_t tl1 = tl0 + (16u << 16);
+				const uint32_t rs_off = static_cast<uint32_t>(GM_A_BYTES + B_BYTES + r0 * 4);
+				const uint32_t cs_off = static_cast<uint32_t>(GM_A_BYTES + B_BYTES + (GM_ROWS + col_off + 2 * t4) * 4);
+				uint64_t acc[4][MAXU > 0 ? MAXU : 1];
 #pragma unroll
-				for (int i = 0; i < CW; ++i)
-					acc[i] = 0.f;
-				uint4 dw8 = make_uint4(0, 0, 0, 0);
-				bool ok	  = true;
-				for (int t = 0; t < n_blk && ok; ++t) {
-					const int a	 = t & 1;
-					const int u	 = t >> 1;
-					const int kb = t >> 1;
-					const int s	 = kb % S;
-					if ((t & 7) == 0 && n_valid)
-						dw8 = __ldg(dw_row + (t >> 3));// this row's next eight block scales
-					if ((t & 1) == 0) {
-						// the activation scales of this K slice were written by the async proxy: acquire them
-						if (!mbar_wait(&hd->full[s], (kb / S) & 1)) {
-							ok = false;
-							break;
-						}
-					}
-					if (!mbar_wait(&hd->tmem_full[a], u & 1)) {
+				for (int j = 0; j < 4; ++j)
+#pragma unroll
+					for (int i = 0; i < MAXU; ++i)
+						acc[j][i] = 0ull;
+				bool ok		= true;
+				int s		= 0;
+				uint32_t ph = 0;
+				for (int kb = 0; kb < n_kb && ok; ++kb) {
+					// the scales of this K slice were written by the async proxy: acquire them
+					if (!mbar_wait(&hd->full[s], ph)) {
 						ok = false;
 						break;
 					}
-					tc_fence_after();
-					const uint32_t w32 = (t & 7) < 2 ? dw8.x : ((t & 7) < 4 ? dw8.y : ((t & 7) < 6 ? dw8.z : dw8.w));
-					const float dw	   = __half2float(__ushort_as_half(static_cast<unsigned short>((t & 1) ? (w32 >> 16) : (w32 & 0xffffu))));
-					const float* da_s  = reinterpret_cast<const float*>(ring + static_cast<size_t>(s) * L::stage_bytes + L::a_bytes + L::b_bytes) + (t & 1) * N_T + g * CW;
-					const uint32_t col = static_cast<uint32_t>(a * N_T + g * CW);
-					constexpr int CH   = CW >= 16 ? 16 : CW;// columns per tcgen05.ld
+					const uint32_t st = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
 #pragma unroll
-					for (int c0 = 0; c0 < CW; c0 += CH) {
-						uint32_t v[32];
-						if constexpr (CH == 16)
-							tmem_ld16(lane_base + col + c0, v);
-						else if constexpr (CH == 8)
-							tmem_ld8(lane_base + col + c0, v);
-						else
-							tmem_ld4(lane_base + col + c0, v);
-						tmem_ld_wait();
-						if (c0 + CH >= CW) {
-							// all of this block's dots are in registers: hand the accumulator stage back to the MMA warp
-							tc_fence_before();
+					for (int j = 0; j < 2; ++j) {
+						uint64_t rs2[4];
+#pragma unroll
+						for (int i = 0; i < 4; ++i) {
+							const float r = lds_f32(st + rs_off + (j * SC_FLOATS + 8 * i) * 4);
+							rs2[i]		  = pack2(r, r);
+						}
+						if (!mbar_wait(&hd->tmem_full[j], kb & 1)) {
+							ok = false;
+							break;
+						}
+						tc_fence_after();
+						if (MAXU == 0 || my_units == 0) {
+							// a narrow tile leaves this column group empty; the stage still counts this warp's release
 							__syncwarp();
 							if (lane == 0)
-								mbar_arrive(&hd->tmem_empty[a]);
+								mbar_arrive(&hd->tmem_empty[j]);
 						}
 #pragma unroll
-						for (int i = 0; i < CH; i += 4) {
-							const float4 d4 = *reinterpret_cast<const float4*>(da_s + c0 + i);
-							acc[c0 + i + 0] = fmaf(__uint_as_float(v[i + 0]) * dw, d4.x, acc[c0 + i + 0]);
-							acc[c0 + i + 1] = fmaf(__uint_as_float(v[i + 1]) * dw, d4.y, acc[c0 + i + 1]);
-							acc[c0 + i + 2] = fmaf(__uint_as_float(v[i + 2]) * dw, d4.z, acc[c0 + i + 2]);
-							acc[c0 + i + 3] = fmaf(__uint_as_float(v[i + 3]) * dw, d4.w, acc[c0 + i + 3]);
+						for (int pr = 0; pr < PAIRS; ++pr) {
+							if (pr < my_pairs) {
+								uint64_t va[4], vb[4], cs2[2];
+#pragma unroll
+								for (int h = 0; h < 2; ++h)
+									cs2[h] = lds_b64(st + cs_off + (j * SC_FLOATS + 8 * (2 * pr + h)) * 4);
+								tmem_ld_16x256b_x2(tl0 + j * GM_STAGE_COLS + 16 * pr, va);
+								tmem_ld_16x256b_x2(tl1 + j * GM_STAGE_COLS + 16 * pr, vb);
+								tmem_ld_wait();
+								if (pr == my_pairs - 1) {
+									// all of this block's dots are in registers: hand the accumulator stage back to the MMA warp
+									tc_fence_before();
+									__syncwarp();
+									if (lane == 0)
+										mbar_arrive(&hd->tmem_empty[j]);
+								}
+#pragma unroll
+								for (int h = 0; h < 2; ++h) {
+									const int un = 2 * pr + h;
+									const int ui = un < MAXU ? un : 0;// keeps the index in range where the unrolled body is dead
+									if (un < MAXU && un < my_units) {
+										acc[0][ui] = fma2(va[2 * h], mul2(rs2[0], cs2[h]), acc[0][ui]);
+										acc[1][ui] = fma2(va[2 * h + 1], mul2(rs2[1], cs2[h]), acc[1][ui]);
+										acc[2][ui] = fma2(vb[2 * h], mul2(rs2[2], cs2[h]), acc[2][ui]);
+										acc[3][ui] = fma2(vb[2 * h + 1], mul2(rs2[3], cs2[h]), acc[3][ui]);
+									}
+								}
+							}
 						}
 					}
-					if (t & 1) {
-						// done with the activation scales of this smem slot
-						__syncwarp();
-						if (lane == 0)
-							mbar_arrive(&hd->empty[s]);
+					// done with the scales of this smem slot
+					__syncwarp();
+					if (ok && lane == 0)
+						mbar_arrive(&hd->empty[s]);
+					if (++s == S) {
+						s = 0;
+						ph ^= 1;
 					}
 				}
 				if (!ok) {
 					if (lane == 0)
 						atomicExch(dev_status, DEV_TIMEOUT_MMA);
-				} else if (n_valid) {
+				} else {
 #pragma unroll
-					for (int i = 0; i < CW; ++i) {
-						const int m = m0 + g * CW + i;
-						if (m < p.M)
-							p.y[static_cast<size_t>(m) * p.ldy + n] = acc[i];
+					for (int j = 0; j < 4; ++j) {
+						const int lr = lane0 + r0 + 8 * j;// lane-side row
+						if (lr < p.lane_rows) {
+#pragma unroll
+							for (int un = 0; un < MAXU; ++un) {
+								if (un < my_units) {
+									float v[2];
+									unpack2(acc[j][un], v[0], v[1]);
+#pragma unroll
+									for (int c = 0; c < 2; ++c) {
+										const int cr = col0 + col_off + 8 * un + 2 * t4 + c;// column-side row
+										if (cr < p.col_rows) {
+											// swapped: lane = token, column = weight row; otherwise the other way round
+											const size_t idx = p.swapped ? static_cast<size_t>(lr) * p.ldy + cr : static_cast<size_t>(cr) * p.ldy + lr;
+											p.y[idx]		 = v[c];
+										}
+									}
+								}
+							}
+						}
 					}
 				}
 			}
@@ -342,7 +415,7 @@ namespace nhb {
 			__syncthreads();
 			if (warp == 1) {
 				tc_fence_after();
-				tmem_dealloc(tmem_base, TCOLS);
+				tmem_dealloc(tmem_base, 2 * GM_STAGE_COLS);
 			}
 		}
 
@@ -364,23 +437,33 @@ namespace nhb {
 			}
 		}
 
-		// quantize_row_q8_0 for the GEMM: quants as fp16 [m_pad][K] (rows >= M zero), scales block-major [K/32][m_pad]
+		// weight scales fp16 [rows][nb] -> f32 block-major [nb][rows_pad] through a 32 x 32 shared-memory tile
+		__global__ void scales_block_major_kernel(const __half* __restrict__ wd, int rows, int nb, int rows_pad, float* __restrict__ out) {
+			__shared__ float tile[32][33];
+			const int r_base = blockIdx.x * 32, b_base = blockIdx.y * 32;
+			for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+				const int r = r_base + i, b = b_base + threadIdx.x;
+				tile[i][threadIdx.x] = (r < rows && b < nb) ? __half2float(wd[static_cast<size_t>(r) * nb + b]) : 0.f;
+			}
+			__syncthreads();
+			for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+				const int b = b_base + i, r = r_base + threadIdx.x;
+				if (b < nb && r < rows_pad)
+					out[static_cast<size_t>(b) * rows_pad + r] = tile[threadIdx.x][i];
+			}
+		}
+
+		// quantize_row_q8_0 for the GEMM: quants as fp16 [M][K], scales block-major [K/32][m_pad]
 		__global__ void quantize_for_gemm_kernel(const float* __restrict__ x, long long ldx, int M, int m_pad, int K, __half* __restrict__ qa16,
 			float* __restrict__ daT) {
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
 			const int nb		= K >> 5;
-			const long long tot = static_cast<long long>(m_pad) * nb;
+			const long long tot = static_cast<long long>(M) * nb;
 			for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < tot; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-				const int m	  = static_cast<int>(i / nb);
-				const int blk = static_cast<int>(i - static_cast<long long>(m) * nb);
-				uint4* dst	  = reinterpret_cast<uint4*>(qa16 + static_cast<size_t>(m) * K + static_cast<size_t>(blk) * QK);
-				if (m >= M) {
-					const uint4 z = make_uint4(0, 0, 0, 0);
-					dst[0] = z, dst[1] = z, dst[2] = z, dst[3] = z;
-					daT[static_cast<size_t>(blk) * m_pad + m] = 0.f;
-					continue;
-				}
+				const int m		= static_cast<int>(i / nb);
+				const int blk	= static_cast<int>(i - static_cast<long long>(m) * nb);
+				uint4* dst		= reinterpret_cast<uint4*>(qa16 + static_cast<size_t>(m) * K + static_cast<size_t>(blk) * QK);
 				const float4* p = reinterpret_cast<const float4*>(x + static_cast<size_t>(m) * ldx + static_cast<size_t>(blk) * QK);
 				float4 v[8];
 				float amax = 0.f;
@@ -390,7 +473,6 @@ namespace nhb {
 					amax = fmaxf(fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))), amax);
 				}
 				const act_scale sc = q8_scales(amax);
-				const float d	   = sc.d;
 				__half2 o[16];
 #pragma unroll
 				for (int j = 0; j < 8; ++j) {
@@ -404,7 +486,7 @@ namespace nhb {
 #pragma unroll
 				for (int j = 0; j < 4; ++j)
 					dst[j] = *reinterpret_cast<uint4*>(&o[4 * j]);
-				daT[static_cast<size_t>(blk) * m_pad + m] = d;
+				daT[static_cast<size_t>(blk) * m_pad + m] = sc.d;
 			}
 		}
 
@@ -437,76 +519,89 @@ namespace nhb {
 					   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 		}
 
-		int pick_nt(int M) {
-			return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+		int round_up(int v, int m) {
+			return ((v + m - 1) / m) * m;
 		}
 
-		template<int N_T> cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const gemm_params& p, const launch_cfg& cfg) {
-			auto kern		  = gemm_q8_tc<N_T>;
-			const size_t smem = gemm_smem<N_T>::total;
-			cudaError_t e	  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-			if (e != cudaSuccess)
-				return e;
-			cudaLaunchConfig_t lc{};
-			lc.gridDim			= dim3((p.rows + GM_ROWS - 1) / GM_ROWS, p.m_pad / N_T);
-			lc.blockDim			= dim3(GM_THREADS);
-			lc.dynamicSmemBytes = smem;
-			lc.stream			= cfg.stream;
-			cudaLaunchAttribute attr[1];
-			attr[0].id										   = cudaLaunchAttributeProgrammaticStreamSerialization;
-			attr[0].val.programmaticStreamSerializationAllowed = 1;
-			lc.attrs										   = attr;
-			lc.numAttrs										   = cfg.pdl ? 1 : 0;
-			return cudaLaunchKernelEx(&lc, kern, ma, mb, p, cfg.dev_status);
-		}
+	}
 
+	// Tile shape for `rows` weight rows and M tokens on `sms` SMs.  Both orientations and every column count from 16
+	// to 256 are priced as waves x (columns per tile + a fixed per-tile overhead); the lane side always holds 128 rows.
+	gemm_plan gemm_tc_plan(int64_t rows, int64_t M, int sms) {
+		gemm_plan best{};
+		double best_cost = 1e300;
+		for (int swapped = 0; swapped < 2; ++swapped) {
+			const int64_t lane_rows = swapped ? M : rows;
+			const int64_t col_rows	= swapped ? rows : M;
+			const int64_t lane_tiles = (lane_rows + GM_ROWS - 1) / GM_ROWS;
+			// 240 and 256 columns per tile exceed the epilogue's register budget (their accumulators spill)
+			const int n_t_max		= static_cast<int>(std::min<int64_t>(224, ((col_rows + 15) / 16) * 16));
+			for (int n_t = 16; n_t <= n_t_max; n_t += 16) {
+				const int64_t col_tiles = (col_rows + n_t - 1) / n_t;
+				const int64_t tiles		= lane_tiles * col_tiles;
+				const int64_t waves		= (tiles + sms - 1) / sms;
+				// narrow tiles re-read the lane-side operand more often: a mild penalty keeps them for when they pay
+				const double cost = static_cast<double>(waves) * (n_t + 24.0) * (1.0 + 8.0 / n_t);
+				if (cost < best_cost - 1e-9) {
+					best_cost	   = cost;
+					best.swapped   = swapped;
+					best.n_t	   = n_t;
+					best.lane_tiles = static_cast<int>(lane_tiles);
+					best.col_tiles	= static_cast<int>(col_tiles);
+				}
+			}
+		}
+		return best;
 	}
 
 	bool gemm_tc_supports(int64_t rows, int64_t K, int64_t M) {
-		return rows >= 1 && K % 256 == 0 && K >= 256 && M >= 1 && M <= (1 << 16);
+		return rows >= 1 && K % 64 == 0 && K >= 64 && M >= 1 && M <= (1 << 16) && rows <= (int64_t(1) << 30);
 	}
 
-	int gemm_tc_m_pad(int64_t M) {
-		const int nt = pick_nt(static_cast<int>(M > 256 ? 256 : M));
-		return static_cast<int>(((M + nt - 1) / nt) * nt);
+	// padded row counts of the block-major scale planes: any tile of up to 256 rows that starts inside stays inside
+	int gemm_tc_pad(int64_t n) {
+		return round_up(static_cast<int>(n), 256) + 256;
 	}
 
-	// quantised activations: fp16 quants [m_pad][K], then block-major scales [K/32][m_pad]
+	// quantised activations: fp16 quants [M][K], then block-major scales [K/32][pad(M)]
 	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M) {
-		const int64_t m_pad = gemm_tc_m_pad(M);
-		return static_cast<size_t>(((m_pad * K * 2 + 255) & ~int64_t(255)) + (K / 32) * m_pad * 4);
+		return static_cast<size_t>(((M * K * 2 + 255) & ~int64_t(255)) + (K / 32) * gemm_tc_pad(M) * 4);
 	}
 
-	cudaError_t launch_widen_i8_f16(const int8_t* q, __half* out, int64_t rows, int64_t K, cudaStream_t s) {
+	// fp16 copy of the quants and block-major f32 copy of the scales, made once per weight
+	cudaError_t launch_weight_gemm_planes(const int8_t* q, const __half* d, int64_t rows, int64_t K, __half* w16, float* wdT, cudaStream_t s) {
 		const long long n16 = rows * K / 16;
 		if (n16 == 0)
 			return cudaSuccess;
 		long long grid = (n16 + 255) / 256;
 		grid		   = grid > 148 * 16 ? 148 * 16 : grid;
-		widen_i8_f16_kernel<<<static_cast<int>(grid), 256, 0, s>>>(q, out, n16);
+		widen_i8_f16_kernel<<<static_cast<int>(grid), 256, 0, s>>>(q, w16, n16);
+		const int nb	   = static_cast<int>(K / 32);
+		const int rows_pad = gemm_tc_pad(rows);
+		dim3 g((rows_pad + 31) / 32, (nb + 31) / 32);
+		scales_block_major_kernel<<<g, dim3(32, 8), 0, s>>>(d, static_cast<int>(rows), nb, rows_pad, wdT);
 		return cudaGetLastError();
 	}
 
-	cudaError_t launch_gemm_tc(const __half* w16, const __half* wd, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
+	cudaError_t launch_gemm_tc(const __half* w16, const float* wdT, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
 		void* scratch, const launch_cfg& cfg, int* launches, std::string* err) {
-		const int nt	= pick_nt(M);
-		const int m_pad = gemm_tc_m_pad(M);
+		const int m_pad = gemm_tc_pad(M);
 		__half* qa16	= static_cast<__half*>(scratch);
-		float* daT		= reinterpret_cast<float*>(static_cast<char*>(scratch) + ((static_cast<size_t>(m_pad) * K * 2 + 255) & ~size_t(255)));
+		float* daT		= reinterpret_cast<float*>(static_cast<char*>(scratch) + ((static_cast<size_t>(M) * K * 2 + 255) & ~size_t(255)));
+		cudaLaunchAttribute attr[1];
+		attr[0].id										   = cudaLaunchAttributeProgrammaticStreamSerialization;
+		attr[0].val.programmaticStreamSerializationAllowed = 1;
 		// 1. quantise the activations (fp16-widened quants + block-major scales)
 		{
-			const long long tot = static_cast<long long>(m_pad) * (K / 32);
+			const long long tot = static_cast<long long>(M) * (K / 32);
 			long long grid		= (tot + 127) / 128;
 			grid				= grid > 148 * 16 ? 148 * 16 : grid;
 			cudaLaunchConfig_t lc{};
 			lc.gridDim	= dim3(static_cast<unsigned>(grid));
 			lc.blockDim = dim3(128);
 			lc.stream	= cfg.stream;
-			cudaLaunchAttribute attr[1];
-			attr[0].id										   = cudaLaunchAttributeProgrammaticStreamSerialization;
-			attr[0].val.programmaticStreamSerializationAllowed = 1;
-			lc.attrs										   = attr;
-			lc.numAttrs										   = cfg.pdl ? 1 : 0;
+			lc.attrs	= attr;
+			lc.numAttrs = cfg.pdl ? 1 : 0;
 			cudaError_t e = cudaLaunchKernelEx(&lc, quantize_for_gemm_kernel, x, ldx, M, m_pad, K, qa16, daT);
 			if (e != cudaSuccess) {
 				if (err)
@@ -516,41 +611,74 @@ namespace nhb {
 			if (launches)
 				*launches += 1;
 		}
-		// 2. tensor maps + the GEMM
+		// 2. tile shape, tensor maps, the GEMM
+		const gemm_plan plan = gemm_tc_plan(rows, M, cfg.sm_count);
 		CUtensorMap ma, mb;
-		if (!make_map(&ma, w16, static_cast<uint64_t>(rows), static_cast<uint64_t>(K), GM_ROWS) ||
-			!make_map(&mb, qa16, static_cast<uint64_t>(m_pad), static_cast<uint64_t>(K), static_cast<uint32_t>(nt))) {
+		const void* a_base	  = plan.swapped ? static_cast<const void*>(qa16) : static_cast<const void*>(w16);
+		const void* b_base	  = plan.swapped ? static_cast<const void*>(w16) : static_cast<const void*>(qa16);
+		const uint64_t a_rows = plan.swapped ? M : rows;
+		const uint64_t b_rows = plan.swapped ? rows : M;
+		if (!make_map(&ma, a_base, a_rows, static_cast<uint64_t>(K), GM_ROWS) || !make_map(&mb, b_base, b_rows, static_cast<uint64_t>(K), static_cast<uint32_t>(plan.n_t))) {
 			if (err)
 				*err = "cuTensorMapEncodeTiled failed";
 			return cudaErrorInvalidValue;
 		}
 		gemm_params p{};
-		p.wd	= wd;
-		p.daT	= daT;
-		p.y		= y;
-		p.ldy	= ldy;
-		p.rows	= rows;
-		p.K		= K;
-		p.M		= M;
-		p.m_pad = m_pad;
-		cudaError_t e;
-		switch (nt) {
-			case 16:
-				e = launch_t<16>(ma, mb, p, cfg);
-				break;
-			case 32:
-				e = launch_t<32>(ma, mb, p, cfg);
-				break;
-			case 64:
-				e = launch_t<64>(ma, mb, p, cfg);
-				break;
-			case 128:
-				e = launch_t<128>(ma, mb, p, cfg);
-				break;
+		p.row_scale	  = plan.swapped ? daT : wdT;
+		p.col_scale	  = plan.swapped ? wdT : daT;
+		p.lanes_pad	  = plan.swapped ? m_pad : gemm_tc_pad(rows);
+		p.cols_pad	  = plan.swapped ? gemm_tc_pad(rows) : m_pad;
+		p.y			  = y;
+		p.ldy		  = ldy;
+		p.lane_rows	  = static_cast<int>(a_rows);
+		p.col_rows	  = static_cast<int>(b_rows);
+		p.K			  = K;
+		p.swapped		  = plan.swapped;
+		const int stage_b = gemm_stage_bytes(plan.n_t);
+		p.stages		  = std::min(8, (200 * 1024) / stage_b);
+		const size_t smem = static_cast<size_t>(GM_HEAD_BYTES) + static_cast<size_t>(p.stages) * stage_b + 1024;
+		void (*kern)(const CUtensorMap, const CUtensorMap, const gemm_params, int*) = nullptr;
+		switch (plan.n_t) {
+#define NHB_GEMM_CASE(n) \
+	case n: \
+		kern = gemm_q8_tc<n>; \
+		break;
+			NHB_GEMM_CASE(16)
+			NHB_GEMM_CASE(32)
+			NHB_GEMM_CASE(48)
+			NHB_GEMM_CASE(64)
+			NHB_GEMM_CASE(80)
+			NHB_GEMM_CASE(96)
+			NHB_GEMM_CASE(112)
+			NHB_GEMM_CASE(128)
+			NHB_GEMM_CASE(144)
+			NHB_GEMM_CASE(160)
+			NHB_GEMM_CASE(176)
+			NHB_GEMM_CASE(192)
+			NHB_GEMM_CASE(208)
+			NHB_GEMM_CASE(224)
+			NHB_GEMM_CASE(240)
+			NHB_GEMM_CASE(256)
+#undef NHB_GEMM_CASE
 			default:
-				e = launch_t<256>(ma, mb, p, cfg);
-				break;
+				if (err)
+					*err = "no GEMM kernel for this tile width";
+				return cudaErrorInvalidValue;
 		}
+		const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+		if (attr_err != cudaSuccess) {
+			if (err)
+				*err = "cudaFuncSetAttribute(gemm_q8_tc)";
+			return attr_err;
+		}
+		cudaLaunchConfig_t lc{};
+		lc.gridDim			= dim3(plan.lane_tiles, plan.col_tiles);
+		lc.blockDim			= dim3(GM_THREADS);
+		lc.dynamicSmemBytes = smem;
+		lc.stream			= cfg.stream;
+		lc.attrs			= attr;
+		lc.numAttrs			= cfg.pdl ? 1 : 0;
+		cudaError_t e		= cudaLaunchKernelEx(&lc, kern, ma, mb, p, cfg.dev_status);
 		if (e != cudaSuccess) {
 			if (err)
 				*err = "gemm_q8_tc launch";

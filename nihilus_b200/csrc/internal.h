@@ -90,10 +90,17 @@ namespace nhb {
 	cudaError_t launch_unpack(const int8_t* q, const __half* d, int64_t rows, int64_t K, uint8_t* blocks34, cudaStream_t s);
 
 	// gemm_tc.cu
+	struct gemm_plan {
+		int swapped;// 0: lanes = weight rows, columns = tokens; 1: lanes = tokens, columns = weight rows
+		int n_t;// columns per tile
+		int lane_tiles, col_tiles;
+	};
+	gemm_plan gemm_tc_plan(int64_t rows, int64_t M, int sms);
 	bool gemm_tc_supports(int64_t rows, int64_t K, int64_t M);
+	int gemm_tc_pad(int64_t n);
 	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M);
-	cudaError_t launch_widen_i8_f16(const int8_t* q, __half* out, int64_t rows, int64_t K, cudaStream_t s);
-	cudaError_t launch_gemm_tc(const __half* w16, const __half* wd, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
+	cudaError_t launch_weight_gemm_planes(const int8_t* q, const __half* d, int64_t rows, int64_t K, __half* w16, float* wdT, cudaStream_t s);
+	cudaError_t launch_gemm_tc(const __half* w16, const float* wdT, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
 		void* scratch, const launch_cfg& cfg, int* launches, std::string* err);
 
 }

@@ -139,7 +139,8 @@ def test_multi_row_stream_and_ldg_agree(capi, ctx, oracle, torch_mod, M):
 
 
 @pytest.mark.parametrize("N,K,M", [(128, 256, 9), (128, 256, 16), (300, 512, 17), (130, 1024, 33), (256, 4096, 64), (1000, 4096, 100),
-                                   (384, 4096, 128), (512, 4096, 200), (256, 14336, 257), (640, 4096, 512)])
+                                   (384, 4096, 128), (512, 4096, 200), (256, 14336, 257), (640, 4096, 512), (130, 64, 20), (1000, 192, 130),
+                                   (4100, 256, 300), (37, 128, 1000)])
 def test_tensor_core_gemm_prefill(capi, ctx, oracle, torch_mod, N, K, M):
     """tcgen05 GEMM: exact int block dots on the tensor cores, f32 outputs within 1e-4 of the oracle; AUTO picks it for M > 8."""
     from nihilus_b200 import synth
