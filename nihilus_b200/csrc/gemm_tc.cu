@@ -79,9 +79,6 @@ namespace nhb {
 		__device__ __forceinline__ void umma_commit(uint64_t* bar) {
 			asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 		}
-		__device__ __forceinline__ void tmem_ld_wait() {
-			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-		}
 		// shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 bytes apart, 8-row groups 1024 bytes apart
 		__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 			uint64_t d = 0;
@@ -159,16 +156,27 @@ namespace nhb {
 			asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
 			return v;
 		}
-		// 16 lanes x 16 columns as packed pairs: v[2k] = lane t/4, columns 8k + 2(t%4), +1; v[2k+1] = lane t/4 + 8, same columns
-		__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint64_t (&v)[4]) {
-			uint32_t r[8];
+		// 16 lanes x 16 columns: thread t receives, for k = 0, 1: r[4k], r[4k+1] = lane t/4, columns 8k + 2(t%4), +1 and
+		// r[4k+2], r[4k+3] = lane t/4 + 8, same columns (lanes relative to the lane in taddr)
+		__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
 			asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
 						 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
 						 : "r"(taddr)
 						 : "memory");
-#pragma unroll
-			for (int i = 0; i < 4; ++i)
-				asm("mov.b64 %0, {%1, %2};" : "=l"(v[i]) : "r"(r[2 * i]), "r"(r[2 * i + 1]));
+		}
+		// Waits for the loads in flight.  The registers pass through the statement so that no use of them can be
+		// scheduled ahead of the wait.
+		__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&a)[8], uint32_t (&b)[8]) {
+			asm volatile("tcgen05.wait::ld.sync.aligned;"
+						 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]),
+						 "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7])
+						 :
+						 : "memory");
+		}
+		__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+			uint64_t r;
+			asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+			return r;
 		}
 
 		template<int N_T> __global__ void __launch_bounds__(GM_THREADS, 1)
@@ -346,13 +354,19 @@ namespace nhb {
 #pragma unroll
 						for (int pr = 0; pr < PAIRS; ++pr) {
 							if (pr < my_pairs) {
+								uint32_t ra[8], rb[8];
 								uint64_t va[4], vb[4], cs2[2];
 #pragma unroll
 								for (int h = 0; h < 2; ++h)
 									cs2[h] = lds_b64(st + cs_off + (j * SC_FLOATS + 8 * (2 * pr + h)) * 4);
-								tmem_ld_16x256b_x2(tl0 + j * GM_STAGE_COLS + 16 * pr, va);
-								tmem_ld_16x256b_x2(tl1 + j * GM_STAGE_COLS + 16 * pr, vb);
-								tmem_ld_wait();
+								tmem_ld_16x256b_x2(tl0 + j * GM_STAGE_COLS + 16 * pr, ra);
+								tmem_ld_16x256b_x2(tl1 + j * GM_STAGE_COLS + 16 * pr, rb);
+								tmem_ld_wait16(ra, rb);
+#pragma unroll
+								for (int i = 0; i < 4; ++i) {
+									va[i] = pack2u(ra[2 * i], ra[2 * i + 1]);
+									vb[i] = pack2u(rb[2 * i], rb[2 * i + 1]);
+								}
 								if (pr == my_pairs - 1) {
 									// all of this block's dots are in registers: hand the accumulator stage back to the MMA warp
 									tc_fence_before();
