@@ -11,7 +11,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libnihilus_b200.so")
+# NHB_LIB names another build of the same library (experiments with compile-time knobs)
+LIB_PATH = os.environ.get("NHB_LIB") or os.path.join(_HERE, "lib", "libnihilus_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(

@@ -93,6 +93,7 @@ struct nhb_ctx {
 	int preq		   = 0;// warp-per-row GEMV: quantise activations in a separate kernel
 	int rows_db		   = 0;// warp-per-row GEMV: two items in flight per warp
 	int rows_cluster   = 1;// warp-per-row GEMV: CTAs per cluster sharing the activation quantisation
+	int rows_fat	   = 1;// warp-per-row GEMV: one 24-warp CTA per SM for launches with enough rows
 	int gemv_default   = NHB_KERNEL_GEMV_ROWS;
 	bool capturing	   = false;
 	long long launches = 0;
@@ -272,7 +273,7 @@ namespace {
 							++launches;
 						}
 					}
-					cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, ctx->rows_db != 0, ctx->rows_cluster);
+					cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, ctx->rows_db != 0, ctx->rows_cluster, ctx->rows_fat != 0);
 					if (e != cudaSuccess)
 						return fail_cuda(ctx, e, "gemv_q8_rows launch");
 				}
@@ -495,6 +496,7 @@ int nhb_ctx_create(nhb_ctx** out, int device, int rank, int world) {
 	ctx->preq		 = env_int("NHB_PREQ", 0);
 	ctx->rows_db	 = env_int("NHB_ROWS_DB", 0);
 	ctx->rows_cluster = env_int("NHB_ROWS_CLUSTER", 1);
+	ctx->rows_fat	  = env_int("NHB_ROWS_FAT", 1);
 	{
 		const int k = env_int("NHB_GEMV_KERNEL", NHB_KERNEL_GEMV_ROWS);
 		if (k == NHB_KERNEL_GEMV_LDG || k == NHB_KERNEL_GEMV_STREAM || k == NHB_KERNEL_GEMV_ROWS)
@@ -556,6 +558,8 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 		ctx->rows_db = value != 0;
 	else if (!std::strcmp(name, "rows_cluster"))
 		ctx->rows_cluster = value < 1 ? 1 : value;
+	else if (!std::strcmp(name, "rows_fat_ctas"))
+		ctx->rows_fat = value != 0;
 	else if (!std::strcmp(name, "gemv_kernel")) {
 		if (value != NHB_KERNEL_GEMV_LDG && value != NHB_KERNEL_GEMV_STREAM && value != NHB_KERNEL_GEMV_ROWS)
 			return fail(ctx, NHB_ERR_ARG, "gemv_kernel must be 1, 2 or 4");

@@ -17,8 +17,12 @@ namespace nhb {
 
 	namespace {
 
-		constexpr int ROWS_WARPS = 8;
-		constexpr int ROWS_TPB	 = ROWS_WARPS * 32;
+		// Two CTA shapes.  Wide launches use one CTA of 24 warps per SM: the activations are quantised once per SM
+		// instead of three times.  Launches with too few rows for that keep 8-warp CTAs, several per SM.
+		constexpr int ROWS_WARPS	 = 8;
+		constexpr int ROWS_TPB		 = ROWS_WARPS * 32;
+		constexpr int ROWS_WARPS_FAT = 24;
+		constexpr int ROWS_TPB_FAT	 = ROWS_WARPS_FAT * 32;
 		constexpr int ITEM		 = 4;// 32-byte Q8 blocks per lane per step: 4 KB of a row per warp
 
 		__device__ __forceinline__ int rows_find_op(const rows_batch& b, int row, int cur) {
@@ -109,14 +113,14 @@ namespace nhb {
 			if (b.preq) {
 				// quantised by quantize_q8_kernel into global scratch: int8 [MT][K] then f32 [MT][nb]
 				const unsigned char* src = b.preq_base + op->preq_off;
-				for (int i = tid; i < MT * nb * 2; i += ROWS_TPB) {
+				for (int i = tid; i < MT * nb * 2; i += static_cast<int>(blockDim.x)) {
 					const int hb  = i >> 1;
 					const int m	  = hb / nb;
 					const int blk = hb - m * nb;
 					reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] = __ldg(reinterpret_cast<const uint4*>(src) + i);
 				}
 				const float* sd = reinterpret_cast<const float*>(src + static_cast<size_t>(MT) * K);
-				for (int i = tid; i < MT * nb; i += ROWS_TPB)
+				for (int i = tid; i < MT * nb; i += static_cast<int>(blockDim.x))
 					sda[i] = __ldg(sd + i);
 			} else {
 				// two threads per 32-wide block (16 floats each); the pair shares its absmax by shuffle.  In a cluster
@@ -127,7 +131,7 @@ namespace nhb {
 				const int per		= ((n / 2 + static_cast<int>(cn) - 1) / static_cast<int>(cn)) * 2;
 				const int i_begin	= static_cast<int>(cr) * per;
 				const int i_end		= min(n, i_begin + per);
-				for (int i = i_begin + tid; i < i_end; i += ROWS_TPB) {
+				for (int i = i_begin + tid; i < i_end; i += static_cast<int>(blockDim.x)) {
 					const int hb	= i >> 1;
 					const int m		= hb / nb;
 					const int blk	= hb - m * nb;
@@ -162,13 +166,14 @@ namespace nhb {
 			cluster_barrier();
 		}
 
-		template<int MT, int OCC> __global__ void __launch_bounds__(ROWS_TPB, OCC) gemv_q8_rows(const __grid_constant__ rows_batch b) {
+		template<int MT, int OCC, int TPB = ROWS_TPB> __global__ void __launch_bounds__(TPB, OCC) gemv_q8_rows(const __grid_constant__ rows_batch b) {
+			constexpr int WARPS = TPB / 32;
 			extern __shared__ __align__(128) unsigned char act_smem[];
 			const int tid		 = threadIdx.x;
 			const int lane		 = tid & 31;
 			const int warp		 = tid >> 5;
-			const int W			 = gridDim.x * ROWS_WARPS;
-			const int row0		 = blockIdx.x * ROWS_WARPS + warp;
+			const int W			 = gridDim.x * WARPS;
+			const int row0		 = blockIdx.x * WARPS + warp;
 			const int total_rows = b.total_rows;
 			const int n_ops		 = b.n_ops;
 			int cur				 = 0;
@@ -324,7 +329,7 @@ namespace nhb {
 	}
 
 	// `b` arrives with op pointers/shapes, act_off/slot tables and preq fields filled by the caller.
-	cudaError_t launch_gemv_rows(const rows_batch& b_in, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer, int cluster) {
+	cudaError_t launch_gemv_rows(const rows_batch& b_in, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer, int cluster, bool fat_ctas) {
 		rows_batch b = b_in;
 		int rows	 = 0;
 		for (int i = 0; i < b.n_ops; ++i) {
@@ -336,18 +341,23 @@ namespace nhb {
 			return cudaSuccess;
 		if (ctas_per_sm < 1)
 			ctas_per_sm = 1;
-		int grid	  = (rows + ROWS_WARPS - 1) / ROWS_WARPS;
+		// one 24-warp CTA per SM when every one of those warps gets a row, else 8-warp CTAs
+		const bool fat	= fat_ctas && !double_buffer && cluster <= 1 && rows >= cfg.sm_count * ROWS_WARPS_FAT;
+		const int warps = fat ? ROWS_WARPS_FAT : ROWS_WARPS;
+		if (fat)
+			ctas_per_sm = 1;
+		int grid	  = (rows + warps - 1) / warps;
 		const int cap = cfg.sm_count * ctas_per_sm;
 		if (grid > cap) {
 			// even split: every warp gets ceil(rows / W) or one fewer rows, with as few short warps as possible
-			const int per_warp = (rows + cap * ROWS_WARPS - 1) / (cap * ROWS_WARPS);
-			grid			   = (rows + per_warp * ROWS_WARPS - 1) / (per_warp * ROWS_WARPS);
+			const int per_warp = (rows + cap * warps - 1) / (cap * warps);
+			grid			   = (rows + per_warp * warps - 1) / (per_warp * warps);
 		}
 		const size_t smem = static_cast<size_t>(b.act_bytes);
 		cudaError_t e	  = cudaErrorInvalidValue;
 		cudaLaunchConfig_t lc{};
 		lc.gridDim			= dim3(grid);
-		lc.blockDim			= dim3(ROWS_TPB);
+		lc.blockDim			= dim3(warps * 32);
 		lc.dynamicSmemBytes = smem;
 		lc.stream			= cfg.stream;
 		cudaLaunchAttribute attr[2];
@@ -371,8 +381,22 @@ namespace nhb {
 		lc.numAttrs = n_attr;
 		// registers per thread are capped by the occupancy the grid was sized for (2, 3 or 4 CTAs per SM)
 		const int occ = double_buffer ? 0 : (ctas_per_sm >= 4 ? 4 : (ctas_per_sm == 3 ? 3 : 2));
+#define NHB_ROWS_FAT_CASE(MT) \
+	if (fat && M == MT) { \
+		auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT>; \
+		e		  = cudaSuccess; \
+		if (smem > 48 * 1024) \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+		if (e == cudaSuccess) \
+			e = cudaLaunchKernelEx(&lc, kern, b); \
+	}
+		NHB_ROWS_FAT_CASE(1)
+		NHB_ROWS_FAT_CASE(2)
+		NHB_ROWS_FAT_CASE(3)
+		NHB_ROWS_FAT_CASE(4)
+#undef NHB_ROWS_FAT_CASE
 #define NHB_ROWS_CASE(MT, OCC) \
-	if (M == MT && occ == OCC) { \
+	if (!fat && M == MT && occ == OCC) { \
 		auto kern = gemv_q8_rows<MT, OCC>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \

@@ -316,6 +316,37 @@ def test_rows_kernel_options_do_not_change_results(capi, oracle, torch_mod):
     assert _rel(base[2], oracle.mul_mat(po.Q8ACT_LANES, w3, x3.cpu().numpy())) <= TOL
 
 
+def test_wide_launch_cta_shape_is_bit_identical(capi, oracle, torch_mod):
+    """Launches with at least 24 rows per SM use one 24-warp CTA per SM; the result must not depend on that choice."""
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    torch = torch_mod
+    w1, w2 = synth.make_weight(4100, 512, 71), synth.make_weight(1333, 512, 72)
+    outs = []
+    for M in (1, 3):
+        x = torch.from_numpy(synth.make_activation(M, 512, 73 + M)).cuda()
+        per_shape = []
+        for fat in (0, 1):
+            c = capi.Context(0)
+            c.use_torch_stream()
+            c.set_option("rows_fat_ctas", fat)
+            hs = [c.upload(w1), c.upload(w2)]
+            ys = [torch.zeros((M, 4100), device="cuda"), torch.zeros((M, 1333), device="cuda")]
+            for _ in range(2):
+                c.mul_mat_batch([(hs[0], x, ys[0]), (hs[1], x, ys[1])])
+            c.sync()
+            per_shape.append([y.cpu().numpy().copy() for y in ys])
+            for h in hs:
+                h.free()
+            c.close()
+        for a, b in zip(*per_shape):
+            assert (a.view(np.uint32) == b.view(np.uint32)).all()
+        assert _rel(per_shape[1][0], oracle.mul_mat(po.Q8ACT_LANES, w1, x.cpu().numpy())) <= TOL
+        assert _rel(per_shape[1][1], oracle.mul_mat(po.Q8ACT_LANES, w2, x.cpu().numpy())) <= TOL
+        outs.append(per_shape)
+
+
 def test_emulated_row_shards_are_bit_identical_to_one_gpu(capi, ctx, oracle, torch_mod):
     """world = 2, 4 and 3 (uneven) emulated as several contexts on this GPU: concatenated slices == unsharded."""
     from nihilus_b200 import synth
