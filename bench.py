@@ -28,6 +28,9 @@ from nihilus_b200 import shapes, synth  # noqa: E402
 METRIC = "q8_0_mul_mat_decode_set_hbm_gbs"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one full step (129 GEMV launches), from an ncu capture of one layer +
+# lm_head scaled to 32 layers (every layer repeats the captured shapes): profiles/gemv_q8_rows_decode_set.md
+NCU_DRAM_BYTES_PER_STEP = 8144.6e6
 
 
 def measured_peaks():
@@ -380,7 +383,8 @@ def main():
             "clocks": clocks,
             "roofline": {
                 "bound": "hbm", "kernel": "gemv_q8_rows", "achieved": per_launch_bytes / (per_launch_ms * 1e-3) / 1e9, "peak": hbm_peak,
-                "unit": "GB/s", "frac": per_launch_bytes / (per_launch_ms * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                "unit": "GB/s", "frac": per_launch_bytes / (per_launch_ms * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind,
+                "traffic": (NCU_DRAM_BYTES_PER_STEP / world / gemv_launches) if args.layers == shapes.L else None,
                 "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms,
                 "note": "per GPU; launch gaps inside the graph are included in the duration",
             },
