@@ -199,6 +199,8 @@ def main():
     ap.add_argument("--layers", type=int, default=shapes.L, help="debug: fewer layers (the reported workload is 32)")
     ap.add_argument("--group", default="stage", choices=["stage", "op"], help="ops launched together: independent ops of a stage, or one by one")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
+                    help="N > 1: outputs completed by the GEMV's own peer stores (fused) or by a grouped NCCL all-gather per stage")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 512-token GEMM figures that ride along in the JSON line")
@@ -260,7 +262,8 @@ def main():
     y_host = torch.empty(yo, dtype=torch.float32).pin_memory()
     with torch.cuda.stream(stream):
         x_dev = x_host.to("cuda", non_blocking=True)
-        y_dev = torch.zeros(yo, dtype=torch.float32, device="cuda")
+        # with several ranks the outputs live in symmetric memory and the GEMV delivers every rank's columns itself
+        y_dev = ctx.symm_empty((yo,)) if (world > 1 and args.gather == "fused") else torch.zeros(yo, dtype=torch.float32, device="cuda")
     stream.synchronize()
     xs = [x_dev[x_off[i]:x_off[i] + ops[i][3]].view(1, -1) for i in range(len(ops))]
     ys = [y_dev[y_off[i]:y_off[i] + ops[i][2]].view(1, -1) for i in range(len(ops))]
@@ -279,7 +282,7 @@ def main():
     def enqueue_step():
         for g in groups:
             ctx.mul_mat_batch([(weights[j], xs[j], ys[j]) for j in g])
-            if world > 1:
+            if world > 1 and args.gather != "none":  # "none" leaves the rows incomplete: timing experiments only
                 ctx.all_gather_batch([ys[j] for j in g])
 
     l0 = ctx.launches
@@ -372,7 +375,7 @@ def main():
                 "workload": "configs[2]: LLaMA-3-8B full decode matmul set, batch 1: %d layers x (q,k,v,o,gate,up,down) + lm_head = %d Q8_0 mul_mats, "
                             "%.3f GB of Q8_0 weights per step" % (args.layers, len(ops), weight_bytes / 1e9),
                 "act_mode": "q8_0 activations (reference quantiser), exact int8 block dots",
-                "launch_grouping": args.group, "cuda_graph": graph is not None, "parallelism": "row-shard x%d + NCCL all-gather" % world,
+                "launch_grouping": args.group, "cuda_graph": graph is not None, "parallelism": "row-shard x%d" % world + ("" if world == 1 else (" + all-gather fused into the GEMV (peer stores over NVLink)" if args.gather == "fused" else " + NCCL all-gather per stage")),
                 "l2": "inputs larger than L2 (%.2f GB of weights per GPU per step vs 126 MB)" % (weight_bytes / world / 1e9),
             },
             "tokens_per_s_equiv": 1e3 / ms_step,

@@ -105,7 +105,8 @@ int nhb_sync(nhb_ctx* ctx);
 /* largest M served by the GEMV family under NHB_KERNEL_AUTO (default 8) */
 int nhb_ctx_set_gemv_max_m(nhb_ctx* ctx, int max_m);
 /* tuning knobs: "pdl" (programmatic dependent launch, default 1), "gemv_kernel" (1, 2 or 4: what AUTO uses for
- * small M), "rows_ctas_per_sm", "prequantize", "ctas_per_sm" (streaming GEMV, 1 or 2), "gemv_max_m" */
+ * small M), "rows_ctas_per_sm", "prequantize", "ctas_per_sm" (streaming GEMV, 1 or 2), "gemv_max_m", "rows_fat_ctas",
+ * "fused_gather" */
 int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value);
 /* kernels this context has launched so far (upload, mul_mat, gather ...) */
 long long nhb_ctx_launch_count(const nhb_ctx* ctx);
@@ -171,6 +172,15 @@ int nhb_graph_free(nhb_ctx* ctx, nhb_graph* g);
 /* 128-byte NCCL unique id made by rank 0 and handed to every rank by the caller's own transport */
 int nhb_comm_unique_id(void* id128);
 int nhb_comm_init(nhb_ctx* ctx, const void* id128);
+/* Output memory for the fused all-gather of the decode GEMV.  Collective: every rank calls it after nhb_comm_init, with
+ * the same size, in the same order; each rank gets its own allocation and a mapping of every other rank's (CUDA IPC, so
+ * one process per GPU and peer access between the GPUs are required).  When every output of a GEMV launch (M <= 8) lies
+ * in such memory at the same offset on every rank, the kernel stores each value into all ranks' copies and trades
+ * completion flags with the peers before it finishes -- the output row is whole on every rank when the kernel is, and
+ * nhb_all_gather on it is a no-op.  All ranks must then issue the same sequence of such launches.  A peer that never
+ * shows up ends the bounded wait with NHB_ERR_TIMEOUT from nhb_sync.  Option "fused_gather" = 0 keeps NCCL. */
+int nhb_symm_alloc(nhb_ctx* ctx, size_t bytes, void** out_dev);
+int nhb_symm_free(nhb_ctx* ctx, void* dev);
 /* complete Y[M][N] (ldy) on every rank from the column slices each rank wrote */
 int nhb_all_gather(nhb_ctx* ctx, float* y_dev, int64_t ldy, int64_t M, int64_t N);
 /* several outputs in one grouped collective (q/k/v, gate/up) */

@@ -34,7 +34,7 @@ EXPORTS = (
     "nhb_weight_upload_q8_0", "nhb_weight_free", "nhb_weight_info_get", "nhb_weight_download_q8_0", "nhb_mul_mat",
     "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
-    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free",
+    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free",
 )
 
 
@@ -75,6 +75,8 @@ _sig("nhb_memcpy_h2d", _i, _vp, _vp, _vp, C.c_size_t)
 _sig("nhb_memcpy_d2h", _i, _vp, _vp, _vp, C.c_size_t)
 _sig("nhb_device_alloc", _i, _vp, C.c_size_t, C.POINTER(_vp))
 _sig("nhb_device_free", _i, _vp, _vp)
+_sig("nhb_symm_alloc", _i, _vp, C.c_size_t, C.POINTER(_vp))
+_sig("nhb_symm_free", _i, _vp, _vp)
 _sig("nhb_weight_upload_q8_0", _i, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("nhb_weight_free", _i, _vp, _vp)
 _sig("nhb_weight_info_get", _i, _vp, C.POINTER(WeightInfo))
@@ -95,6 +97,17 @@ _sig("nhb_mul_mat_q8_0_noalloc", _i, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _i64,
 _sig("nhb_noalloc_max_bytes", _i64)
 _sig("nhb_noalloc_last_error", C.c_char_p)
 _sig("nhb_all_gather_batch", _i, _vp, C.POINTER(_vp), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), _i)
+
+
+def _tensor_from_ptr(ptr: int, nbytes: int, device: int, dtype):
+    """A torch view of device memory this library owns (no copy; the caller keeps the allocation alive)."""
+    import torch
+
+    class _Cai:
+        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+    t = torch.as_tensor(_Cai(), device=f"cuda:{device}")
+    return t.view(dtype)
 
 
 class NhbError(RuntimeError):
@@ -296,6 +309,19 @@ class Context:
     def comm_init(self, uid: bytes):
         buf = C.create_string_buffer(uid, 128)
         _check(lib.nhb_comm_init(self.handle, buf), self.handle)
+
+    def symm_empty(self, shape, dtype=None):
+        """A zeroed torch tensor in symmetric memory (collective: same call, same order, on every rank)."""
+        import torch
+
+        dtype = dtype or torch.float32
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = max(n, 1) * torch.empty((), dtype=dtype).element_size()
+        p = _vp()
+        _check(lib.nhb_symm_alloc(self.handle, nbytes, C.byref(p)), self.handle)
+        return _tensor_from_ptr(p.value, nbytes, self.device, dtype).view(*shape) if n else torch.empty(shape, dtype=dtype, device=f"cuda:{self.device}")
 
     def all_gather(self, y):
         M, N = y.shape

@@ -98,6 +98,16 @@ struct nhb_ctx {
 	bool capturing	   = false;
 	long long launches = 0;
 	std::string err;
+	// fused all-gather (decode GEMV): peer-mapped output regions, the flag array every rank can write, local counters
+	struct symm_region {
+		char* local	 = nullptr;
+		size_t bytes = 0;
+		char* peer[NHB_MAX_WORLD] = {};// this rank's own entry is `local`
+		bool complete = false;// the last kernel that wrote into it delivered every rank's columns itself
+	};
+	std::vector<symm_region> regions;
+	unsigned* push_local = nullptr;// [0] CTAs done in the running launch, [1] fused launches completed
+	int fused_gather	 = 1;
 };
 
 struct nhb_weight {
@@ -201,6 +211,113 @@ namespace {
 		return NHB_OK;
 	}
 
+	nhb_ctx::symm_region* find_region(nhb_ctx* ctx, const void* p, size_t bytes) {
+		const char* c = static_cast<const char*>(p);
+		for (auto& r: ctx->regions)
+			if (c >= r.local && c + bytes <= r.local + r.bytes)
+				return &r;
+		return nullptr;
+	}
+
+	// Allocates `bytes` on this rank and maps the matching allocation of every other rank (CUDA IPC; the 64-byte
+	// handles travel through an NCCL all-gather).  Collective: every rank calls it with the same size, in the same order.
+	int symm_alloc_impl(nhb_ctx* ctx, size_t bytes, nhb_ctx::symm_region* out) {
+		if (ctx->world > NHB_MAX_WORLD)
+			return fail(ctx, NHB_ERR_UNSUPPORTED, "symmetric memory supports at most 8 ranks");
+		nhb_ctx::symm_region reg;
+		reg.bytes = bytes;
+		void* p	  = nullptr;
+		NHB_CUDA(ctx, cudaMalloc(&p, bytes));
+		reg.local			= static_cast<char*>(p);
+		reg.peer[ctx->rank] = reg.local;
+		cudaError_t e		= cudaMemsetAsync(p, 0, bytes, ctx->stream);
+		if (e == cudaSuccess && ctx->world > 1) {
+			if (!ctx->comm) {
+				cudaFree(p);
+				return fail(ctx, NHB_ERR_NCCL, "symmetric memory needs nhb_comm_init first (the handles travel over NCCL)");
+			}
+			cudaIpcMemHandle_t mine;
+			e = cudaIpcGetMemHandle(&mine, p);
+			unsigned char* stage = nullptr;
+			const size_t hb		 = sizeof(cudaIpcMemHandle_t);
+			if (e == cudaSuccess)
+				e = cudaMalloc(&stage, hb * ctx->world);
+			if (e == cudaSuccess)
+				e = cudaMemcpyAsync(stage + hb * ctx->rank, &mine, hb, cudaMemcpyHostToDevice, ctx->stream);
+			int nrc = nccl_success;
+			if (e == cudaSuccess)
+				nrc = nccl().AllGather(stage + hb * ctx->rank, stage, hb, /*ncclUint8*/ 1, ctx->comm, ctx->stream);
+			std::vector<cudaIpcMemHandle_t> all(ctx->world);
+			if (e == cudaSuccess && nrc == nccl_success)
+				e = cudaMemcpyAsync(all.data(), stage, hb * ctx->world, cudaMemcpyDeviceToHost, ctx->stream);
+			if (e == cudaSuccess)
+				e = cudaStreamSynchronize(ctx->stream);
+			if (stage)
+				cudaFree(stage);
+			if (nrc != nccl_success) {
+				cudaFree(p);
+				return fail(ctx, NHB_ERR_NCCL, "exchange of memory handles failed");
+			}
+			for (int r = 0; r < ctx->world && e == cudaSuccess; ++r) {
+				if (r == ctx->rank)
+					continue;
+				void* q = nullptr;
+				e		= cudaIpcOpenMemHandle(&q, all[r], cudaIpcMemLazyEnablePeerAccess);
+				reg.peer[r] = static_cast<char*>(q);
+			}
+		}
+		if (e != cudaSuccess) {
+			for (int r = 0; r < ctx->world; ++r)
+				if (r != ctx->rank && reg.peer[r])
+					cudaIpcCloseMemHandle(reg.peer[r]);
+			cudaFree(p);
+			return fail_cuda(ctx, e, "symmetric allocation (one process per GPU with peer access is required)");
+		}
+		*out = reg;
+		return NHB_OK;
+	}
+
+	void symm_release(nhb_ctx* ctx, nhb_ctx::symm_region& reg) {
+		for (int r = 0; r < ctx->world; ++r)
+			if (r != ctx->rank && reg.peer[r])
+				cudaIpcCloseMemHandle(reg.peer[r]);
+		if (reg.local)
+			cudaFree(reg.local);
+		reg = nhb_ctx::symm_region();
+	}
+
+	// Fills the fused all-gather part of a warp-per-row launch when every output of the batch lies in symmetric memory.
+	// regions[0] is the control region holding the flag array.
+	bool setup_push(nhb_ctx* ctx, rows_batch& b, const nhb_mul_mat_op* const* src_ops, int mt, int64_t m0) {
+		if (ctx->world <= 1 || !ctx->fused_gather || ctx->regions.empty() || !ctx->push_local || b.n_ops == 0)
+			return false;
+		nhb_ctx::symm_region* regs[NHB_MAX_BATCH];
+		for (int i = 0; i < b.n_ops; ++i) {
+			const nhb_mul_mat_op* op = src_ops[i];
+			// the whole row range this launch completes must be inside one region
+			float* first = op->y + m0 * op->ldy;
+			regs[i]		 = find_region(ctx, first, (static_cast<size_t>(mt - 1) * op->ldy + op->w->N) * sizeof(float));
+			if (!regs[i] || regs[i] == &ctx->regions[0])
+				return false;
+		}
+		for (int i = 0; i < b.n_ops; ++i) {
+			const char* y_local = reinterpret_cast<const char*>(b.op[i].y);
+			const size_t off	= static_cast<size_t>(y_local - regs[i]->local);
+			for (int r = 0; r < ctx->world; ++r)
+				b.y_peer[i][r] = reinterpret_cast<float*>(regs[i]->peer[r] + off);
+			regs[i]->complete = true;
+		}
+		b.push.world	   = ctx->world;
+		b.push.rank		   = ctx->rank;
+		b.push.done_ctas   = ctx->push_local;
+		b.push.epoch	   = ctx->push_local + 1;
+		b.push.flags_local = reinterpret_cast<unsigned*>(ctx->regions[0].local);
+		for (int r = 0; r < ctx->world; ++r)
+			b.push.flags_peer[r] = reinterpret_cast<unsigned*>(ctx->regions[0].peer[r]);
+		b.push.status = ctx->dev_status;
+		return true;
+	}
+
 	// GEMV family over M rows (looping over row groups the kernels support)
 	int run_gemv(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int act_mode, int kernel) {
 		const int64_t M = ops[0].M;
@@ -223,12 +340,14 @@ namespace {
 				for (int64_t m0 = 0; m0 < M; m0 += mt_max) {
 					const int mt = static_cast<int>(std::min<int64_t>(mt_max, M - m0));
 					rows_batch b{};
+					const nhb_mul_mat_op* src_ops[NHB_MAX_BATCH];
 					size_t off = 0;
 					for (int i = 0; i < n_ops; ++i) {
 						const nhb_weight* w = ops[i].w;
 						if (w->n1 == w->n0)
 							continue;
-						rows_op& ro = b.op[b.n_ops];
+						src_ops[b.n_ops] = &ops[i];
+						rows_op& ro		 = b.op[b.n_ops];
 						ro.wq		= w->q;
 						ro.wd		= w->d;
 						ro.x		= ops[i].x + m0 * ops[i].ldx;
@@ -273,6 +392,12 @@ namespace {
 							++launches;
 						}
 					}
+					// a batch in which some rank owns no rows of some op would leave the ranks with different launch counts
+					bool all_ranks_have_rows = true;
+					for (int i = 0; i < n_ops; ++i)
+						all_ranks_have_rows = all_ranks_have_rows && ops[i].w->N >= ctx->world;
+					if (!ctx->rows_db && ctx->rows_cluster <= 1 && all_ranks_have_rows)
+						setup_push(ctx, b, src_ops, mt, m0);
 					cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, ctx->rows_db != 0, ctx->rows_cluster, ctx->rows_fat != 0);
 					if (e != cudaSuccess)
 						return fail_cuda(ctx, e, "gemv_q8_rows launch");
@@ -513,6 +638,10 @@ int nhb_ctx_destroy(nhb_ctx* ctx) {
 	cudaStreamSynchronize(ctx->stream);
 	if (ctx->comm && nccl().ok)
 		nccl().CommDestroy(ctx->comm);
+	for (auto& r: ctx->regions)
+		symm_release(ctx, r);
+	if (ctx->push_local)
+		cudaFree(ctx->push_local);
 	if (ctx->scratch)
 		cudaFree(ctx->scratch);
 	if (ctx->io)
@@ -558,6 +687,8 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 		ctx->rows_db = value != 0;
 	else if (!std::strcmp(name, "rows_cluster"))
 		ctx->rows_cluster = value < 1 ? 1 : value;
+	else if (!std::strcmp(name, "fused_gather"))
+		ctx->fused_gather = value != 0;
 	else if (!std::strcmp(name, "rows_fat_ctas"))
 		ctx->rows_fat = value != 0;
 	else if (!std::strcmp(name, "gemv_kernel")) {
@@ -765,6 +896,10 @@ int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int ac
 	if (M == 0)
 		return NHB_OK;
 	device_guard g(ctx->device);
+	// whatever this call writes is this rank's slice only, until a fused launch below says otherwise
+	for (int i = 0; i < n_ops && !ctx->regions.empty(); ++i)
+		if (nhb_ctx::symm_region* r = find_region(ctx, ops[i].y, sizeof(float)))
+			r->complete = false;
 	const int forced = env_int("NHB_FORCE_KERNEL", 0);
 	if (kernel == NHB_KERNEL_AUTO && forced >= 1 && forced <= 4)
 		kernel = forced;
@@ -950,6 +1085,55 @@ int nhb_comm_init(nhb_ctx* ctx, const void* id128) {
 	return NHB_OK;
 }
 
+int nhb_symm_alloc(nhb_ctx* ctx, size_t bytes, void** out_dev) {
+	if (!ctx || !out_dev || bytes == 0)
+		return fail(ctx, NHB_ERR_ARG, "nhb_symm_alloc: bad arguments");
+	*out_dev = nullptr;
+	if (ctx->capturing)
+		return fail(ctx, NHB_ERR_UNSUPPORTED, "allocation during graph capture");
+	device_guard g(ctx->device);
+	if (ctx->regions.empty()) {
+		// first use: the flag array every rank writes into (region 0) and this rank's two counters
+		nhb_ctx::symm_region ctl;
+		int rc = symm_alloc_impl(ctx, 256, &ctl);
+		if (rc != NHB_OK)
+			return rc;
+		cudaError_t e = cudaMalloc(&ctx->push_local, 256);
+		if (e == cudaSuccess)
+			e = cudaMemset(ctx->push_local, 0, 256);
+		if (e != cudaSuccess) {
+			symm_release(ctx, ctl);
+			return fail_cuda(ctx, e, "nhb_symm_alloc: control block");
+		}
+		ctx->regions.reserve(64);
+		ctx->regions.push_back(ctl);
+	}
+	nhb_ctx::symm_region reg;
+	int rc = symm_alloc_impl(ctx, (bytes + 255) & ~size_t(255), &reg);
+	if (rc != NHB_OK)
+		return rc;
+	ctx->regions.push_back(reg);
+	*out_dev = reg.local;
+	return NHB_OK;
+}
+
+int nhb_symm_free(nhb_ctx* ctx, void* dev) {
+	if (!ctx)
+		return fail(nullptr, NHB_ERR_ARG, "null context");
+	if (!dev)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	for (size_t i = 1; i < ctx->regions.size(); ++i) {
+		if (ctx->regions[i].local == dev) {
+			NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+			symm_release(ctx, ctx->regions[i]);
+			ctx->regions.erase(ctx->regions.begin() + static_cast<long>(i));
+			return NHB_OK;
+		}
+	}
+	return fail(ctx, NHB_ERR_ARG, "nhb_symm_free: not a pointer nhb_symm_alloc returned");
+}
+
 int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, const int64_t* M, const int64_t* N, int n) {
 	if (!ctx || n < 0 || (n > 0 && (!y_dev || !ldy || !M || !N)))
 		return fail(ctx, NHB_ERR_ARG, "nhb_all_gather_batch: bad arguments");
@@ -958,6 +1142,14 @@ int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, 
 	if (!ctx->comm)
 		return fail(ctx, NHB_ERR_NCCL, "nhb_comm_init has not been called");
 	device_guard g(ctx->device);
+	// outputs a fused GEMV launch has already completed on every rank need no collective
+	bool any_left = false;
+	for (int i = 0; i < n; ++i) {
+		nhb_ctx::symm_region* r = (y_dev[i] && !ctx->regions.empty()) ? find_region(ctx, y_dev[i], sizeof(float)) : nullptr;
+		any_left				= any_left || !(r && r->complete);
+	}
+	if (!any_left)
+		return NHB_OK;
 	nccl_api& nc = nccl();
 	int rc		 = nc.GroupStart();
 	for (int i = 0; i < n && rc == nccl_success; ++i) {
@@ -965,6 +1157,9 @@ int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, 
 			nc.GroupEnd();
 			return fail(ctx, NHB_ERR_ARG, "nhb_all_gather_batch: bad entry");
 		}
+		if (nhb_ctx::symm_region* r = ctx->regions.empty() ? nullptr : find_region(ctx, y_dev[i], sizeof(float)))
+			if (r->complete)
+				continue;
 		const bool even = N[i] % ctx->world == 0;
 		for (int64_t m = 0; m < M[i] && rc == nccl_success; ++m) {
 			float* row = y_dev[i] + m * ldy[i];

@@ -166,6 +166,57 @@ namespace nhb {
 			cluster_barrier();
 		}
 
+		__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+			asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+		}
+		__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p) {
+			unsigned v;
+			asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+			return v;
+		}
+		__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+			unsigned v;
+			asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+			return v;
+		}
+
+		// End of a fused launch.  Every CTA orders its stores (CTA barrier, then a device-scope fence by thread 0) and
+		// counts itself done; the last one issues the launch's single system-scope fence, tells every rank "this rank
+		// has finished launch number e" and then waits, for a bounded time, until all ranks have said the same.
+		// System-scope fences wait for the stores that crossed NVLink to be acknowledged, so there is exactly one on the
+		// critical path; the polls are relaxed loads and one acquire load closes the wait.  Nothing here waits on a CTA
+		// of this grid that has not run yet, and a peer's flag only depends on that peer's own kernel, so ranks cannot
+		// wait on each other in a cycle.
+		__device__ __forceinline__ void push_finish(const push_ctl& pc, int tid) {
+			__syncthreads();
+			if (tid != 0)
+				return;
+			asm volatile("fence.acq_rel.gpu;" ::: "memory");
+			const unsigned prev = atomicAdd(pc.done_ctas, 1u);
+			if (prev != gridDim.x - 1)
+				return;
+			asm volatile("fence.acq_rel.sys;" ::: "memory");
+			const unsigned e = *reinterpret_cast<volatile unsigned*>(pc.epoch) + 1u;
+			for (int r = 0; r < pc.world; ++r)
+				st_relaxed_sys(pc.flags_peer[r] + pc.rank, e);
+			bool ok = true;
+			for (int r = 0; r < pc.world && ok; ++r) {
+				ok = false;
+				for (uint32_t i = 0; i < NHB_SPIN_LIMIT; ++i) {
+					if (static_cast<int>(ld_relaxed_sys(pc.flags_local + r) - e) >= 0) {
+						ok = static_cast<int>(ld_acquire_sys(pc.flags_local + r) - e) >= 0;
+						break;
+					}
+					if (i > 4096)
+						__nanosleep(20);
+				}
+			}
+			*reinterpret_cast<volatile unsigned*>(pc.done_ctas) = 0u;
+			*reinterpret_cast<volatile unsigned*>(pc.epoch)	   = e;
+			if (!ok)
+				atomicExch(pc.status, DEV_TIMEOUT_PEER);
+		}
+
 		template<int MT, int OCC, int TPB = ROWS_TPB> __global__ void __launch_bounds__(TPB, OCC) gemv_q8_rows(const __grid_constant__ rows_batch b) {
 			constexpr int WARPS = TPB / 32;
 			extern __shared__ __align__(128) unsigned char act_smem[];
@@ -214,6 +265,30 @@ namespace nhb {
 					if (lane == 0)
 						yrow[static_cast<size_t>(m) * ldy] = v;
 				}
+			}
+			if (b.push.world > 1) {
+				// Fused all-gather.  In pass i the warps of this CTA finished WARPS consecutive rows; once they are all
+				// written (CTA barrier) one warp per pass copies that run to every other rank in one coalesced store per
+				// rank and token, instead of one 4-byte store across NVLink per row.
+				__syncthreads();
+				int pcur = 0;
+				for (int base = blockIdx.x * WARPS + warp * W; base < total_rows; base += WARPS * W) {
+					const int row = base + lane;
+					if (lane < WARPS && row < total_rows) {
+						pcur			   = rows_find_op(b, row, pcur);
+						const rows_op* op  = &b.op[pcur];
+						const int lrow	   = row - op->row_begin;
+						const long long ld = op->ldy;
+#pragma unroll
+						for (int m = 0; m < MT; ++m) {
+							const float v = __ldcg(op->y + static_cast<size_t>(m) * ld + lrow);
+							for (int r = 0; r < b.push.world; ++r)
+								if (r != b.push.rank)
+									b.y_peer[pcur][r][static_cast<size_t>(m) * ld + lrow] = v;
+						}
+					}
+				}
+				push_finish(b.push, tid);
 			}
 		}
 

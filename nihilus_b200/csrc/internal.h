@@ -10,11 +10,12 @@
 
 #define NHB_MAX_BATCH 8
 #define NHB_STATUS_WORDS 8
+#define NHB_MAX_WORLD 8
 
 namespace nhb {
 
 	// device status word values (written by kernels whose bounded waits ran out)
-	enum : int { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_DRAIN = 3, DEV_TIMEOUT_MMA = 4 };
+	enum : int { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_DRAIN = 3, DEV_TIMEOUT_MMA = 4, DEV_TIMEOUT_PEER = 5 };
 
 	// one mul_mat as the streaming GEMV sees it: this context's row shard of the two planes
 	struct stream_op {
@@ -52,6 +53,19 @@ namespace nhb {
 		int pad;
 	};
 
+	// Fused all-gather of the decode GEMV: every rank stores its output values straight into all ranks' copies of
+	// the output (peer-mapped memory) and the last CTA of the grid trades "done" flags with the peers before it exits,
+	// so the kernel's completion means the whole row is there on this rank.
+	struct push_ctl {
+		int world;// 0 or 1: not a fused launch
+		int rank;
+		unsigned* done_ctas;// local: CTAs of this grid that have stored everything
+		unsigned* epoch;// local: number of fused launches completed on this rank
+		unsigned* flags_local;// [world], written by the peers: their epoch after their matching launch
+		unsigned* flags_peer[NHB_MAX_WORLD];// the same array on every rank (this rank's own included)
+		int* status;// the context's device status word
+	};
+
 	struct rows_batch {
 		int n_ops;
 		int total_rows;
@@ -62,6 +76,8 @@ namespace nhb {
 		int pad;
 		const unsigned char* preq_base;
 		rows_op op[NHB_MAX_BATCH];
+		push_ctl push;
+		float* y_peer[NHB_MAX_BATCH][NHB_MAX_WORLD];// per op: the output on every rank, offset like rows_op::y
 	};
 
 	struct launch_cfg {

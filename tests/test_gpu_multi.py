@@ -54,6 +54,46 @@ def _worker(rank, world, uid_path, q):
     ctx.all_gather_batch([ya, yb])
     ctx.sync()
     out["batch_a"], out["batch_b"] = ya.cpu().numpy(), yb.cpu().numpy()
+    # ---- fused all-gather: outputs in symmetric memory, the GEMV itself delivers every rank's columns ----
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ctx.use_torch_stream()
+        cases = {"f_even": (4096, 4096, 1), "f_ragged": (1031, 4096, 3), "f_m8": (300, 512, 8)}
+        ys, hs, xs = {}, {}, {}
+        for name, (N, K, M) in cases.items():  # same allocations, same order, on every rank
+            ys[name] = ctx.symm_empty((M, N))
+        yq, yk = ctx.symm_empty((1, 512)), ctx.symm_empty((1, 256))
+        for name, (N, K, M) in cases.items():
+            hs[name] = ctx.upload(synth.make_weight(N, K, 900 + N))
+            xs[name] = torch.from_numpy(synth.make_activation(M, K, 901 + N)).cuda()
+        launches0 = ctx.launches
+        for rep in range(3):  # repeated launches walk the epoch counter
+            for name in cases:
+                ctx.mul_mat(hs[name], xs[name], ys[name])
+                ctx.all_gather(ys[name])  # nothing left to do: no collective is enqueued
+            ctx.mul_mat_batch([(ha, x, yq), (hb, x, yk)])
+            ctx.all_gather_batch([yq, yk])
+        ctx.sync()
+        out["fused_launches_per_rep"] = (ctx.launches - launches0) / 3
+        for name in cases:
+            out[name] = ys[name].cpu().numpy()
+        out["f_batch_a"], out["f_batch_b"] = yq.cpu().numpy(), yk.cpu().numpy()
+        # the same sequence replayed from a CUDA graph
+        for name in cases:
+            ys[name].zero_()
+        ctx.sync()
+        ctx.graph_begin()
+        for name in cases:
+            ctx.mul_mat(hs[name], xs[name], ys[name])
+        g = ctx.graph_end()
+        g.launch()
+        g.launch()
+        ctx.sync()
+        for name in cases:
+            out["g_" + name[2:]] = ys[name].cpu().numpy()
+        g.free()
+        for h in hs.values():
+            h.free()
     q.put((rank, out))
     ha.free()
     hb.free()
@@ -93,3 +133,16 @@ def test_two_gpu_shards_all_gathered_match_oracle(capi, oracle, tmp_path):
         ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, 4096, seed), x)
         for r in range(world):
             assert np.abs(results[r][key] - ref).max() <= 1e-4 * np.abs(ref).max()
+            # fused delivery gives the very same bits as compute + NCCL
+            assert (results[r]["f_" + key].view(np.uint32) == results[r][key].view(np.uint32)).all()
+    for name, (N, K, M) in {"even": (4096, 4096, 1), "ragged": (1031, 4096, 3), "m8": (300, 512, 8)}.items():
+        ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, K, 900 + N), synth.make_activation(M, K, 901 + N))
+        for r in range(world):
+            for prefix in ("f_", "g_"):
+                y = results[r][prefix + name]
+                assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max(), (prefix, name, r)
+            assert (results[r]["f_" + name].view(np.uint32) == results[0]["g_" + name].view(np.uint32)).all()
+        if name in ("even", "ragged"):
+            assert (results[0]["f_" + name].view(np.uint32) == results[0][name].view(np.uint32)).all()
+    # 3 single mul_mats (m8 takes two GEMV launches) + 1 batch per repetition, and no NCCL launch at all
+    assert results[0]["fused_launches_per_rep"] == 5
