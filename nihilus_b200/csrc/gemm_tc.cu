@@ -64,38 +64,102 @@ namespace nhb {
 		__device__ __forceinline__ void tc_fence_after() {
 			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 		}
-		// D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate = 0 overwrites D
-		__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+		// mbarrier operations on a 32-bit shared address (the hot loops keep barrier addresses in registers)
+		__device__ __forceinline__ bool mbar_try_a(uint32_t bar, uint32_t parity) {
+			uint32_t ok;
 			asm volatile(
 				"{\n"
 				".reg .pred p;\n"
-				"setp.ne.b32 p, %4, 0;\n"
-				"tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+				"mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+				"selp.u32 %0, 1, 0, p;\n"
+				"}\n"
+				: "=r"(ok)
+				: "r"(bar), "r"(parity)
+				: "memory");
+			return ok != 0;
+		}
+		// bounded wait; false = gave up.  The first poll usually succeeds, the loop is kept out of line of sight.
+		__device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity) {
+			if (mbar_try_a(bar, parity))
+				return true;
+			for (uint32_t i = 0; i < NHB_SPIN_LIMIT; ++i) {
+				if (mbar_try_a(bar, parity))
+					return true;
+				if (i > 32)
+					__nanosleep(40);
+			}
+			return false;
+		}
+		__device__ __forceinline__ void mbar_arrive_a(uint32_t bar) {
+			asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+		}
+		__device__ __forceinline__ void umma_commit_a(uint32_t bar) {
+			asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+		}
+		// D[tmem] = A * B (overwrite) and D[tmem] += A * B, descriptors given as (low word, constant high word)
+		__device__ __forceinline__ void umma_f16_set(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
+			asm volatile(
+				"{\n"
+				".reg .pred p;\n"
+				".reg .b64 da, db;\n"
+				"setp.ne.b32 p, 0, 0;\n"
+				"mov.b64 da, {%1, %3};\n"
+				"mov.b64 db, {%2, %3};\n"
+				"tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
 				"}\n" ::"r"(d_tmem),
-				"l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+				"r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc)
 				: "memory");
 		}
-		// arrive on `bar` once every tcgen05 operation this thread issued so far has completed
-		__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-			asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+		__device__ __forceinline__ void umma_f16_acc(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
+			asm volatile(
+				"{\n"
+				".reg .pred p;\n"
+				".reg .b64 da, db;\n"
+				"setp.eq.b32 p, 0, 0;\n"
+				"mov.b64 da, {%1, %3};\n"
+				"mov.b64 db, {%2, %3};\n"
+				"tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
+				"}\n" ::"r"(d_tmem),
+				"r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc)
+				: "memory");
 		}
-		// shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 bytes apart, 8-row groups 1024 bytes apart
-		__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-			uint64_t d = 0;
-			d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);// start address
-			d |= static_cast<uint64_t>(1) << 16;// leading byte offset (unused for swizzled K-major; canonical value 1)
-			d |= static_cast<uint64_t>(1024 >> 4) << 32;// stride byte offset
-			d |= static_cast<uint64_t>(1) << 46;// descriptor version (Blackwell)
-			d |= static_cast<uint64_t>(2) << 61;// SWIZZLE_128B
-			return d;
+		// the two words of the shared-memory matrix descriptor below: only the 14-bit address field in the low word
+		// changes from tile to tile (shared addresses stay below 256 KiB, so adding (bytes >> 4) never carries out of it)
+		constexpr uint32_t GM_DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);// stride 1024 B, version 1, 128-byte swizzle
+		__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) {
+			return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16);
 		}
+
 
 		// instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, M = 128, N = n
 		__host__ __device__ constexpr uint32_t idesc_f16(int n) {
 			return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(GM_ROWS >> 4) << 24);
 		}
 
-		constexpr int GM_STAGE_COLS = 256;// TMEM columns per accumulator stage
+#ifdef NHB_GEMM_PROF
+		// debug builds only: cycles CTA (0,0) spent waiting, per role.  [0..3] epilogue warp 4: full, tmem_full, total;
+		// [8..11] MMA warp: full, tmem_empty, total; [16..18] producer: empty, total
+		__device__ long long g_prof[32];
+#define PROF_T(var) const long long var = clock64()
+#define PROF_ACC(slot, a, b) prof_acc[slot] += (b) - (a)
+#define PROF_DECL long long prof_acc[4] = {}
+#define PROF_FLUSH(base_slot) \
+	if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) { \
+		for (int i_ = 0; i_ < 4; ++i_) \
+			g_prof[(base_slot) + i_] = prof_acc[i_]; \
+	}
+#else
+#define PROF_T(var)
+#define PROF_ACC(slot, a, b)
+#define PROF_DECL
+#define PROF_FLUSH(base_slot)
+#endif
+		constexpr int GM_TMEM_COLS = 512;// the whole tensor memory of the SM: one CTA per SM
+		// accumulator stages: as many as fit, so the MMA warp can run several Q8 blocks ahead of the epilogue (narrow
+		// tiles are bound by the latency of the MMA -> epilogue -> MMA hand-over, which more stages overlap)
+		__host__ __device__ constexpr int gemm_stage_cols(int n_t) {
+			return n_t <= 64 ? 64 : (n_t <= 128 ? 128 : 256);
+		}
 
 		struct gemm_params {
 			const float* row_scale;// [K/32][lanes_pad]  scales of the lane side, block-major
@@ -113,8 +177,8 @@ namespace nhb {
 		struct gemm_head {
 			uint64_t full[8];
 			uint64_t empty[8];
-			uint64_t tmem_full[2];
-			uint64_t tmem_empty[2];
+			uint64_t tmem_full[8];
+			uint64_t tmem_empty[8];
 			uint32_t tmem_base;
 			int abort_flag;
 		};
@@ -188,6 +252,8 @@ namespace nhb {
 			constexpr int BASE		  = UNITS / 4;
 			constexpr int REM		  = UNITS % 4;
 			constexpr int MAXU		  = BASE + (REM ? 1 : 0);
+			constexpr int STAGE_COLS  = gemm_stage_cols(N_T);
+			constexpr int NS		  = GM_TMEM_COLS / STAGE_COLS;// 2, 4 or 8 accumulator stages
 			constexpr int PAIRS		  = (MAXU + 1) / 2;
 			extern __shared__ unsigned char smem_raw[];
 			// 1024-byte alignment for the 128-byte swizzle atoms
@@ -208,7 +274,7 @@ namespace nhb {
 					mbar_init(&hd->full[s], 1);
 					mbar_init(&hd->empty[s], 1 + GM_EPI_WARPS);
 				}
-				for (int a = 0; a < 2; ++a) {
+				for (int a = 0; a < NS; ++a) {
 					mbar_init(&hd->tmem_full[a], 1);
 					mbar_init(&hd->tmem_empty[a], GM_EPI_WARPS);
 				}
@@ -216,7 +282,7 @@ namespace nhb {
 				fence_mbar_init();
 			}
 			if (warp == 1)
-				tmem_alloc(&hd->tmem_base, 2 * GM_STAGE_COLS);
+				tmem_alloc(&hd->tmem_base, GM_TMEM_COLS);
 			tc_fence_before();
 			__syncthreads();
 			tc_fence_after();
@@ -236,13 +302,20 @@ namespace nhb {
 						constexpr uint32_t tx = static_cast<uint32_t>(GM_A_BYTES + B_BYTES + 2 * SC_FLOATS * 4);
 						const float* rsrc	  = p.row_scale + lane0;
 						const float* csrc	  = p.col_scale + col0;
+						const uint32_t full0  = smem_u32(&hd->full[0]);
+						const uint32_t empty0 = smem_u32(&hd->empty[0]);
 						int s				  = 0;
 						uint32_t ph			  = 1;// a fresh barrier reads as "phase 1 complete": the first S waits pass at once
+						PROF_DECL;
+						PROF_T(pt0);
 						for (int kb = 0; kb < n_kb; ++kb) {
-							if (!mbar_wait(&hd->empty[s], ph)) {
+							PROF_T(p0);
+							if (!mbar_wait_a(empty0 + 8 * s, ph)) {
 								atomicExch(dev_status, DEV_TIMEOUT_EMPTY);
 								break;
 							}
+							PROF_T(p1);
+							PROF_ACC(0, p0, p1);
 							const uint32_t st = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
 							mbar_expect_tx(&hd->full[s], tx);
 							tma_load_2d(st, &map_a, kb * GM_KSLICE, lane0, &hd->full[s]);
@@ -260,45 +333,80 @@ namespace nhb {
 								ph ^= 1;
 							}
 						}
+						PROF_T(pt1);
+						PROF_ACC(2, pt0, pt1);
+						PROF_FLUSH(16);
 					}
-				} else if (warp == 1) {
-					// ---------------- MMA issuer ----------------
-					if (lane == 0) {
-						constexpr uint32_t idesc = idesc_f16(N_T);
-						int s					 = 0;
-						uint32_t ph				 = 0;
-						bool ok					 = true;
-						for (int kb = 0; kb < n_kb && ok; ++kb) {
-							if (!mbar_wait(&hd->full[s], ph)) {
+				} else if (warp == 1 || (NS >= 8 && warp == 2)) {
+					// ---------------- MMA issuers ----------------
+					// A thread that issues every MMA and commit of a K slice is the critical path of narrow tiles (about 370
+					// cycles per Q8 block, all of it issue latency).  For tiles of up to 64 columns (eight accumulator stages) two
+					// warps take alternate K slices: they then own disjoint accumulator stages and (the ring depth is even)
+					// disjoint ring slots, so each barrier still has a single waiter that is never more than one phase ahead of
+					// it.  Wider tiles are bound by the epilogue, where a second polling warp only costs issue slots (measured:
+					// 2048 tokens x 4096 rows 163 -> 181 us), and with two stages both issuers would share them and a parity wait
+					// could pass a phase early; there one warp issues everything.
+					// Barrier addresses and descriptor words live in registers and only get incremented.
+					constexpr uint32_t ISSUERS = NS >= 8 ? 2 : 1;
+					if (lane == 0 && static_cast<uint32_t>(warp - 1) < ISSUERS) {
+						const uint32_t first = static_cast<uint32_t>(warp - 1);// 0 or 1
+						constexpr uint32_t idesc   = idesc_f16(N_T);
+						const uint32_t full0	   = smem_u32(&hd->full[0]);
+						const uint32_t empty0	   = smem_u32(&hd->empty[0]);
+						const uint32_t tmem_full0  = smem_u32(&hd->tmem_full[0]);
+						const uint32_t tmem_empty0 = smem_u32(&hd->tmem_empty[0]);
+						uint32_t s = first, ph = 0;
+						if (s >= static_cast<uint32_t>(S)) {// a one-slot ring: slice 1 is the second use of slot 0
+							s -= S;
+							ph ^= 1;
+						}
+						bool ok = true;
+						PROF_DECL;
+						PROF_T(mt0);
+						for (int kb = static_cast<int>(first); kb < n_kb && ok; kb += ISSUERS) {
+							const uint32_t a_lo = smem_desc_lo(ring + s * STAGE_BYTES);// descriptor low word of this slot's A tile
+							PROF_T(m0);
+							if (!mbar_wait_a(full0 + 8 * s, ph)) {
 								atomicExch(dev_status, DEV_TIMEOUT_FULL);
 								break;
 							}
 							tc_fence_after();
-							const uint32_t a_addr = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
-							const uint32_t b_addr = a_addr + GM_A_BYTES;
+							PROF_T(m1);
+							PROF_ACC(0, m0, m1);
+							const uint32_t b_lo = a_lo + (GM_A_BYTES >> 4);
+							// Q8 block t = 2 kb + j goes to accumulator stage t % NS, in its (t / NS)-th use
+							const uint32_t a0	  = static_cast<uint32_t>(2 * kb) & (NS - 1);
+							const uint32_t use_ph = (static_cast<uint32_t>(2 * kb) / NS) & 1u;
 #pragma unroll
-							for (int j = 0; j < 2; ++j) {
-								// Q8 block 2 kb + j goes to accumulator stage j; its previous user was block 2 (kb - 1) + j
-								if (!mbar_wait(&hd->tmem_empty[j], (kb & 1) ^ 1)) {
+							for (uint32_t j = 0; j < 2; ++j) {
+								const uint32_t a = a0 + j;
+								PROF_T(m2);
+								if (!mbar_wait_a(tmem_empty0 + 8 * a, use_ph ^ 1u)) {
 									atomicExch(dev_status, DEV_TIMEOUT_MMA);
 									ok = false;
 									break;
 								}
 								tc_fence_after();
-								const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(j * GM_STAGE_COLS);
-#pragma unroll
-								for (int k2 = 0; k2 < 2; ++k2) {
-									const uint32_t off = static_cast<uint32_t>(j * 64 + k2 * 32);// bytes inside the 128-byte row
-									umma_f16(d_tmem, smem_desc_sw128(a_addr + off), smem_desc_sw128(b_addr + off), idesc, k2);
-								}
-								umma_commit(&hd->tmem_full[j]);
+								PROF_T(m3);
+								PROF_ACC(1, m2, m3);
+								const uint32_t d_tmem = tmem_base + a * STAGE_COLS;
+								// the block's two K = 16 steps sit 32 bytes apart inside the 128-byte rows: (j * 64 + k2 * 32) >> 4
+								umma_f16_set(d_tmem, a_lo + 4 * j, b_lo + 4 * j, GM_DESC_HI, idesc);
+								umma_f16_acc(d_tmem, a_lo + 4 * j + 2, b_lo + 4 * j + 2, GM_DESC_HI, idesc);
+								umma_commit_a(tmem_full0 + 8 * a);
 							}
 							if (ok)
-								umma_commit(&hd->empty[s]);// the slot's operands are free once these MMAs have run
-							if (++s == S) {
-								s = 0;
+								umma_commit_a(empty0 + 8 * s);// the slot's operands are free once these MMAs have run
+							s += ISSUERS;
+							while (s >= static_cast<uint32_t>(S)) {
+								s -= S;
 								ph ^= 1;
 							}
+						}
+						PROF_T(mt1);
+						PROF_ACC(2, mt0, mt1);
+						if (warp == 1) {
+							PROF_FLUSH(8);
 						}
 					}
 				}
@@ -322,34 +430,49 @@ namespace nhb {
 #pragma unroll
 					for (int i = 0; i < MAXU; ++i)
 						acc[j][i] = 0ull;
+				const uint32_t full0	   = smem_u32(&hd->full[0]);
+				const uint32_t empty0	   = smem_u32(&hd->empty[0]);
+				const uint32_t tmem_full0  = smem_u32(&hd->tmem_full[0]);
+				const uint32_t tmem_empty0 = smem_u32(&hd->tmem_empty[0]);
 				bool ok		= true;
 				int s		= 0;
 				uint32_t ph = 0;
+				PROF_DECL;
+				PROF_T(et0);
 				for (int kb = 0; kb < n_kb && ok; ++kb) {
 					// the scales of this K slice were written by the async proxy: acquire them
-					if (!mbar_wait(&hd->full[s], ph)) {
+					PROF_T(e0);
+					if (!mbar_wait_a(full0 + 8 * s, ph)) {
 						ok = false;
 						break;
 					}
-					const uint32_t st = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
+					PROF_T(e1);
+					PROF_ACC(0, e0, e1);
+					const uint32_t st	  = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
+					const int a0		  = (2 * kb) & (NS - 1);
+					const uint32_t use_ph = static_cast<uint32_t>((2 * kb) / NS) & 1u;
 #pragma unroll
 					for (int j = 0; j < 2; ++j) {
+						const int a = a0 + j;
 						uint64_t rs2[4];
 #pragma unroll
 						for (int i = 0; i < 4; ++i) {
 							const float r = lds_f32(st + rs_off + (j * SC_FLOATS + 8 * i) * 4);
 							rs2[i]		  = pack2(r, r);
 						}
-						if (!mbar_wait(&hd->tmem_full[j], kb & 1)) {
+						PROF_T(e2);
+						if (!mbar_wait_a(tmem_full0 + 8 * a, use_ph)) {
 							ok = false;
 							break;
 						}
 						tc_fence_after();
+						PROF_T(e3);
+						PROF_ACC(1, e2, e3);
 						if (MAXU == 0 || my_units == 0) {
 							// a narrow tile leaves this column group empty; the stage still counts this warp's release
 							__syncwarp();
 							if (lane == 0)
-								mbar_arrive(&hd->tmem_empty[j]);
+								mbar_arrive_a(tmem_empty0 + 8 * a);
 						}
 #pragma unroll
 						for (int pr = 0; pr < PAIRS; ++pr) {
@@ -359,8 +482,8 @@ namespace nhb {
 #pragma unroll
 								for (int h = 0; h < 2; ++h)
 									cs2[h] = lds_b64(st + cs_off + (j * SC_FLOATS + 8 * (2 * pr + h)) * 4);
-								tmem_ld_16x256b_x2(tl0 + j * GM_STAGE_COLS + 16 * pr, ra);
-								tmem_ld_16x256b_x2(tl1 + j * GM_STAGE_COLS + 16 * pr, rb);
+								tmem_ld_16x256b_x2(tl0 + a * STAGE_COLS + 16 * pr, ra);
+								tmem_ld_16x256b_x2(tl1 + a * STAGE_COLS + 16 * pr, rb);
 								tmem_ld_wait16(ra, rb);
 #pragma unroll
 								for (int i = 0; i < 4; ++i) {
@@ -372,7 +495,7 @@ namespace nhb {
 									tc_fence_before();
 									__syncwarp();
 									if (lane == 0)
-										mbar_arrive(&hd->tmem_empty[j]);
+										mbar_arrive_a(tmem_empty0 + 8 * a);
 								}
 #pragma unroll
 								for (int h = 0; h < 2; ++h) {
@@ -391,12 +514,21 @@ namespace nhb {
 					// done with the scales of this smem slot
 					__syncwarp();
 					if (ok && lane == 0)
-						mbar_arrive(&hd->empty[s]);
+						mbar_arrive_a(empty0 + 8 * s);
 					if (++s == S) {
 						s = 0;
 						ph ^= 1;
 					}
 				}
+#ifdef NHB_GEMM_PROF
+				{
+					PROF_T(et1);
+					PROF_ACC(2, et0, et1);
+					if (warp == 4) {
+						PROF_FLUSH(0);
+					}
+				}
+#endif
 				if (!ok) {
 					if (lane == 0)
 						atomicExch(dev_status, DEV_TIMEOUT_MMA);
@@ -429,7 +561,7 @@ namespace nhb {
 			__syncthreads();
 			if (warp == 1) {
 				tc_fence_after();
-				tmem_dealloc(tmem_base, 2 * GM_STAGE_COLS);
+				tmem_dealloc(tmem_base, GM_TMEM_COLS);
 			}
 		}
 
@@ -650,6 +782,8 @@ namespace nhb {
 		p.swapped		  = plan.swapped;
 		const int stage_b = gemm_stage_bytes(plan.n_t);
 		p.stages		  = std::min(8, (200 * 1024) / stage_b);
+		if (gemm_stage_cols(plan.n_t) <= 64 && p.stages >= 2)
+			p.stages &= ~1;// two issuer warps alternate over the ring: an even depth gives each its own slots
 		const size_t smem = static_cast<size_t>(GM_HEAD_BYTES) + static_cast<size_t>(p.stages) * stage_b + 1024;
 		void (*kern)(const CUtensorMap, const CUtensorMap, const gemm_params, int*) = nullptr;
 		switch (plan.n_t) {
@@ -704,3 +838,14 @@ namespace nhb {
 	}
 
 }
+
+#ifdef NHB_GEMM_PROF
+extern "C" int nhb_debug_gemm_prof(long long* out32, int reset) {
+	cudaError_t e = cudaMemcpyFromSymbol(out32, nhb::g_prof, sizeof(long long) * 32);
+	if (e == cudaSuccess && reset) {
+		long long z[32] = {};
+		e = cudaMemcpyToSymbol(nhb::g_prof, z, sizeof(z));
+	}
+	return e == cudaSuccess ? 0 : -2;
+}
+#endif
