@@ -94,6 +94,7 @@ struct nhb_ctx {
 	int rows_db		   = 0;// warp-per-row GEMV: two items in flight per warp
 	int rows_cluster   = 1;// warp-per-row GEMV: CTAs per cluster sharing the activation quantisation
 	int rows_fat	   = 1;// warp-per-row GEMV: one 24-warp CTA per SM for launches with enough rows
+	int rows_split	   = 1;// ... and within those, the item-parallel kernel for rows longer than 4096
 	int gemv_default   = NHB_KERNEL_GEMV_ROWS;
 	bool capturing	   = false;
 	long long launches = 0;
@@ -398,7 +399,7 @@ namespace {
 						all_ranks_have_rows = all_ranks_have_rows && ops[i].w->N >= ctx->world;
 					if (!ctx->rows_db && ctx->rows_cluster <= 1 && all_ranks_have_rows)
 						setup_push(ctx, b, src_ops, mt, m0);
-					cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, ctx->rows_db != 0, ctx->rows_cluster, ctx->rows_fat != 0);
+					cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, ctx->rows_db != 0, ctx->rows_cluster, ctx->rows_fat != 0, ctx->rows_split != 0);
 					if (e != cudaSuccess)
 						return fail_cuda(ctx, e, "gemv_q8_rows launch");
 				}
@@ -622,6 +623,7 @@ int nhb_ctx_create(nhb_ctx** out, int device, int rank, int world) {
 	ctx->rows_db	 = env_int("NHB_ROWS_DB", 0);
 	ctx->rows_cluster = env_int("NHB_ROWS_CLUSTER", 1);
 	ctx->rows_fat	  = env_int("NHB_ROWS_FAT", 1);
+	ctx->rows_split	  = env_int("NHB_ROWS_SPLIT", 1);
 	{
 		const int k = env_int("NHB_GEMV_KERNEL", NHB_KERNEL_GEMV_ROWS);
 		if (k == NHB_KERNEL_GEMV_LDG || k == NHB_KERNEL_GEMV_STREAM || k == NHB_KERNEL_GEMV_ROWS)
@@ -689,6 +691,8 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 		ctx->rows_cluster = value < 1 ? 1 : value;
 	else if (!std::strcmp(name, "fused_gather"))
 		ctx->fused_gather = value != 0;
+	else if (!std::strcmp(name, "rows_split_long"))
+		ctx->rows_split = value != 0;
 	else if (!std::strcmp(name, "rows_fat_ctas"))
 		ctx->rows_fat = value != 0;
 	else if (!std::strcmp(name, "gemv_kernel")) {

@@ -9,6 +9,8 @@
 // Arithmetic: quantize_row_q8_0 + vec_dot_q8_0_q8_0 of the reference (include/nihilus-incl/cpu/avx_2.hpp
 // :4439-4489, :4749-4780); per 32-wide block  acc = fma(float(exact int32 block dot), d_w * d_a, acc).  The
 // summation order depends on K only, so any row sharding gives bit-identical outputs.
+#include <algorithm>
+
 #include "internal.h"
 #include "ptx.cuh"
 #include "q8_device.cuh"
@@ -249,21 +251,30 @@ namespace nhb {
 				const unsigned char* act = act_smem + op->act_off;
 				float* const yrow		 = op->y + lrow;
 				const long long ldy		 = op->ldy;
-				float acc[MT];
+				// A row's value is the sum, in ascending order, of its 4 KB items' totals; an item's total is the warp
+				// reduction of the lanes' partial sums.  (One item per row for K = 4096.)  Every kernel of this file sums
+				// in this order, so which warp computes which item never shows in the result.
+				float rowacc[MT];
 #pragma unroll
 				for (int m = 0; m < MT; ++m)
-					acc[m] = 0.f;
+					rowacc[m] = 0.f;
 				for (int b0 = 0; b0 < rd.nb; b0 += 32 * ITEM) {
 					if (!pre)
 						load_item(regs, rd, b0, lane);
 					pre = false;
-					compute_item<MT>(regs, acc, act, rd.nb, b0, lane);
-				}
+					float acc[MT];
 #pragma unroll
-				for (int m = 0; m < MT; ++m) {
-					const float v = warp_sum(acc[m]);
-					if (lane == 0)
-						yrow[static_cast<size_t>(m) * ldy] = v;
+					for (int m = 0; m < MT; ++m)
+						acc[m] = 0.f;
+					compute_item<MT>(regs, acc, act, rd.nb, b0, lane);
+#pragma unroll
+					for (int m = 0; m < MT; ++m)
+						rowacc[m] += warp_sum(acc[m]);
+				}
+				if (lane == 0) {
+#pragma unroll
+					for (int m = 0; m < MT; ++m)
+						yrow[static_cast<size_t>(m) * ldy] = rowacc[m];
 				}
 			}
 			if (b.push.world > 1) {
@@ -292,6 +303,86 @@ namespace nhb {
 			}
 		}
 
+
+		// ---- item-parallel variant for long rows (K > 4096) ----
+		// With one warp per row a 14336-wide row is four 4 KB items fetched one after the other, and 4096 such rows leave
+		// most warps with one or two of these chains: the kernel is bound by that chain, not by bandwidth.  Here a CTA
+		// owns a contiguous run of rows (every SM gets the same share) and deals their items to its 24 warps, so the
+		// items of one row are in flight in different warps at the same time; item totals meet in shared memory and are
+		// added per row in ascending order -- the same order, hence the same bits, as the one-warp-per-row kernels.
+		// All ops of the launch must share K.
+		constexpr int SPLIT_MAX_ROWS = 64;// rows per CTA the partial-sum array is sized for
+		template<int MT> __global__ void __launch_bounds__(ROWS_TPB_FAT, 1) gemv_q8_rows_split(const __grid_constant__ rows_batch b) {
+			constexpr int WARPS = ROWS_WARPS_FAT;
+			extern __shared__ __align__(128) unsigned char act_smem[];
+			__shared__ float part[SPLIT_MAX_ROWS * 8 * MT];// [row][item][m]
+			const int tid		 = threadIdx.x;
+			const int lane		 = tid & 31;
+			const int warp		 = tid >> 5;
+			const int total_rows = b.total_rows;
+			const int nb		 = b.op[0].K >> 5;
+			const int ipr		 = (nb + 32 * ITEM - 1) / (32 * ITEM);// items per row
+			// this CTA's rows: an even contiguous split of the batch-wide row list
+			const int r_lo	  = static_cast<int>(static_cast<long long>(total_rows) * blockIdx.x / gridDim.x);
+			const int r_hi	  = static_cast<int>(static_cast<long long>(total_rows) * (blockIdx.x + 1) / gridDim.x);
+			const int n_items = (r_hi - r_lo) * ipr;
+			item_regs regs;
+			bool pre = false;
+			int cur	 = 0;
+			// ---- weights first: they never depend on the previous kernel ----
+			if (warp < n_items) {
+				const int row = r_lo + warp / ipr;
+				cur			  = rows_find_op(b, row, 0);
+				load_item(regs, make_row(&b.op[cur], row - b.op[cur].row_begin), (warp % ipr) * 32 * ITEM, lane);
+				pre = true;
+			}
+			pdl_launch_dependents();
+			pdl_wait_prior_grids();
+			quantize_inputs<MT>(b, act_smem, tid);
+			for (int it = warp; it < n_items; it += WARPS) {
+				const int rl  = it / ipr;
+				const int b0  = (it - rl * ipr) * 32 * ITEM;
+				const int row = r_lo + rl;
+				cur			  = rows_find_op(b, row, cur);
+				const rows_op* op = &b.op[cur];
+				const row_desc rd = make_row(op, row - op->row_begin);
+				if (!pre)
+					load_item(regs, rd, b0, lane);
+				pre = false;
+				float acc[MT];
+#pragma unroll
+				for (int m = 0; m < MT; ++m)
+					acc[m] = 0.f;
+				compute_item<MT>(regs, acc, act_smem + op->act_off, rd.nb, b0, lane);
+#pragma unroll
+				for (int m = 0; m < MT; ++m) {
+					const float v = warp_sum(acc[m]);
+					if (lane == 0)
+						part[(rl * 8 + (it - rl * ipr)) * MT + m] = v;
+				}
+			}
+			__syncthreads();
+			// one thread per (row, token): item totals in ascending order, store, and in a fused launch the peers' copies
+			int ocur = 0;
+			for (int i = tid; i < (r_hi - r_lo) * MT; i += ROWS_TPB_FAT) {
+				const int m	 = i / (r_hi - r_lo);
+				const int rl = i - m * (r_hi - r_lo);// consecutive threads -> consecutive rows: coalesced stores
+				float v		 = 0.f;
+				for (int k = 0; k < ipr; ++k)
+					v += part[(rl * 8 + k) * MT + m];
+				const int row	  = r_lo + rl;
+				ocur			  = rows_find_op(b, row, 0);
+				const rows_op* op = &b.op[ocur];
+				const size_t off  = static_cast<size_t>(m) * op->ldy + (row - op->row_begin);
+				op->y[off]		  = v;
+				if (b.push.world > 1)
+					for (int r = 0; r < b.push.world; ++r)
+						if (r != b.push.rank)
+							b.y_peer[ocur][r][off] = v;
+			}
+			if (b.push.world > 1)
+				push_finish(b.push, tid);
+		}
 
 		// ---- double-buffered variant: two 4 KB items in flight per warp ----
 		// A position in a warp's work list: one item (32*ITEM blocks) of one row, with everything needed to stream it.
@@ -353,23 +444,31 @@ namespace nhb {
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
 			quantize_inputs<MT>(b, act_smem, tid);
-			float acc[MT];
+			float acc[MT], rowacc[MT];
 #pragma unroll
 			for (int m = 0; m < MT; ++m)
-				acc[m] = 0.f;
+				acc[m] = rowacc[m] = 0.f;
+			// same summation order as gemv_q8_rows: item totals added in ascending order
+			auto finish_item = [&]() {
+#pragma unroll
+				for (int m = 0; m < MT; ++m) {
+					rowacc[m] += warp_sum(acc[m]);
+					acc[m] = 0.f;
+				}
+			};
 			auto finish_row = [&](const item_pos& p) {
 #pragma unroll
 				for (int m = 0; m < MT; ++m) {
-					const float v = warp_sum(acc[m]);
 					if (lane == 0)
-						p.yrow[static_cast<size_t>(m) * p.ldy] = v;
-					acc[m] = 0.f;
+						p.yrow[static_cast<size_t>(m) * p.ldy] = rowacc[m];
+					rowacc[m] = 0.f;
 				}
 			};
 			while (true) {
 				if (pa.row >= total_rows)
 					break;
 				compute_item<MT>(ra, acc, pa.act, pa.rd.nb, pa.b0, lane);
+				finish_item();
 				{
 					const bool row_end = pa.b0 + 32 * ITEM >= pa.rd.nb;
 					const item_pos done = pa;
@@ -382,6 +481,7 @@ namespace nhb {
 				if (pb.row >= total_rows)
 					break;
 				compute_item<MT>(rb, acc, pb.act, pb.rd.nb, pb.b0, lane);
+				finish_item();
 				{
 					const bool row_end = pb.b0 + 32 * ITEM >= pb.rd.nb;
 					const item_pos done = pb;
@@ -404,7 +504,8 @@ namespace nhb {
 	}
 
 	// `b` arrives with op pointers/shapes, act_off/slot tables and preq fields filled by the caller.
-	cudaError_t launch_gemv_rows(const rows_batch& b_in, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer, int cluster, bool fat_ctas) {
+	cudaError_t launch_gemv_rows(const rows_batch& b_in, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer, int cluster, bool fat_ctas,
+		bool split_long_rows) {
 		rows_batch b = b_in;
 		int rows	 = 0;
 		for (int i = 0; i < b.n_ops; ++i) {
@@ -428,6 +529,13 @@ namespace nhb {
 			const int per_warp = (rows + cap * warps - 1) / (cap * warps);
 			grid			   = (rows + per_warp * warps - 1) / (per_warp * warps);
 		}
+		// long rows: the item-parallel kernel, one CTA per SM, when all ops share K and a CTA's rows fit its partial-sum array
+		bool split = fat && split_long_rows && (b.op[0].K >> 5) > 32 * ITEM && (b.op[0].K >> 5) <= 8 * 32 * ITEM &&
+			(rows + cfg.sm_count - 1) / cfg.sm_count <= SPLIT_MAX_ROWS;
+		for (int i = 1; i < b.n_ops && split; ++i)
+			split = b.op[i].K == b.op[0].K;
+		if (split)
+			grid = cfg.sm_count;
 		const size_t smem = static_cast<size_t>(b.act_bytes);
 		cudaError_t e	  = cudaErrorInvalidValue;
 		cudaLaunchConfig_t lc{};
@@ -456,8 +564,22 @@ namespace nhb {
 		lc.numAttrs = n_attr;
 		// registers per thread are capped by the occupancy the grid was sized for (2, 3 or 4 CTAs per SM)
 		const int occ = double_buffer ? 0 : (ctas_per_sm >= 4 ? 4 : (ctas_per_sm == 3 ? 3 : 2));
+#define NHB_ROWS_SPLIT_CASE(MT) \
+	if (split && M == MT) { \
+		auto kern = gemv_q8_rows_split<MT>; \
+		e		  = cudaSuccess; \
+		if (smem > 40 * 1024) \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+		if (e == cudaSuccess) \
+			e = cudaLaunchKernelEx(&lc, kern, b); \
+	}
+		NHB_ROWS_SPLIT_CASE(1)
+		NHB_ROWS_SPLIT_CASE(2)
+		NHB_ROWS_SPLIT_CASE(3)
+		NHB_ROWS_SPLIT_CASE(4)
+#undef NHB_ROWS_SPLIT_CASE
 #define NHB_ROWS_FAT_CASE(MT) \
-	if (fat && M == MT) { \
+	if (fat && !split && M == MT) { \
 		auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \

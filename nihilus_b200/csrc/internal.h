@@ -99,7 +99,7 @@ namespace nhb {
 	size_t gemv_rows_act_bytes(int64_t K, int M);
 	bool gemv_rows_supports(int64_t K, int64_t M);
 	cudaError_t launch_gemv_rows(const rows_batch& b, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer = false, int cluster = 1,
-		bool fat_ctas = false);
+		bool fat_ctas = false, bool split_long_rows = false);
 	cudaError_t launch_block_dots(const int8_t* wq, const int8_t* qa, int rows, int K, int M, int32_t* dots, cudaStream_t s);
 
 	// repack.cu

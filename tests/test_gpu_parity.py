@@ -347,6 +347,36 @@ def test_wide_launch_cta_shape_is_bit_identical(capi, oracle, torch_mod):
         outs.append(per_shape)
 
 
+def test_long_rows_item_parallel_kernel_is_bit_identical(capi, oracle, torch_mod):
+    """Rows longer than 4096 in a wide launch are split into 4 KB items over the warps of a CTA; item totals are
+    added in the same order as in the one-warp-per-row kernels, so the three kernels agree bit for bit."""
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    torch = torch_mod
+    N, K = 3700, 14336
+    w = synth.make_weight(N, K, 81)
+    for M in (1, 4):
+        x = torch.from_numpy(synth.make_activation(M, K, 82 + M)).cuda()
+        got = []
+        for fat, split in ((0, 0), (1, 0), (1, 1)):
+            c = capi.Context(0)
+            c.use_torch_stream()
+            c.set_option("rows_fat_ctas", fat)
+            c.set_option("rows_split_long", split)
+            h = c.upload(w)
+            y = torch.zeros((M, N), device="cuda")
+            for _ in range(2):
+                c.mul_mat(h, x, y)
+            c.sync()
+            got.append(y.cpu().numpy().copy())
+            h.free()
+            c.close()
+        assert (got[0].view(np.uint32) == got[1].view(np.uint32)).all()
+        assert (got[0].view(np.uint32) == got[2].view(np.uint32)).all()
+        assert _rel(got[2], oracle.mul_mat(po.Q8ACT_LANES, w, x.cpu().numpy())) <= TOL
+
+
 def test_emulated_row_shards_are_bit_identical_to_one_gpu(capi, ctx, oracle, torch_mod):
     """world = 2, 4 and 3 (uneven) emulated as several contexts on this GPU: concatenated slices == unsharded."""
     from nihilus_b200 import synth
