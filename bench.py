@@ -199,6 +199,8 @@ def main():
     ap.add_argument("--layers", type=int, default=shapes.L, help="debug: fewer layers (the reported workload is 32)")
     ap.add_argument("--group", default="stage", choices=["stage", "op"], help="ops launched together: independent ops of a stage, or one by one")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--replicate-mb", type=int, default=48,
+                    help="N > 1 placement policy: weights smaller than this many MiB stay whole on every rank (no exchange); 0 shards all")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
                     help="N > 1: outputs completed by the GEMV's own peer stores (fused) or by a grouped NCCL all-gather per stage")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
@@ -233,6 +235,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     ctx = capi.Context(local, rank, world)
+    if world > 1:
+        ctx.set_option("replicate_below_mb", args.replicate_mb)
     stream = torch.cuda.Stream()
     ctx.set_stream(stream.cuda_stream)
     if world > 1:
@@ -375,7 +379,7 @@ def main():
                 "workload": "configs[2]: LLaMA-3-8B full decode matmul set, batch 1: %d layers x (q,k,v,o,gate,up,down) + lm_head = %d Q8_0 mul_mats, "
                             "%.3f GB of Q8_0 weights per step" % (args.layers, len(ops), weight_bytes / 1e9),
                 "act_mode": "q8_0 activations (reference quantiser), exact int8 block dots",
-                "launch_grouping": args.group, "cuda_graph": graph is not None, "parallelism": "row-shard x%d" % world + ("" if world == 1 else (" + all-gather fused into the GEMV (peer stores over NVLink)" if args.gather == "fused" else " + NCCL all-gather per stage")),
+                "launch_grouping": args.group, "cuda_graph": graph is not None, "parallelism": "row-shard x%d" % world + ("" if world == 1 or not args.replicate_mb else " (weights under %d MiB replicated)" % args.replicate_mb) + ("" if world == 1 else (" + all-gather fused into the GEMV (peer stores over NVLink)" if args.gather == "fused" else " + NCCL all-gather per stage")),
                 "l2": "inputs larger than L2 (%.2f GB of weights per GPU per step vs 126 MB)" % (weight_bytes / world / 1e9),
             },
             "tokens_per_s_equiv": 1e3 / ms_step,

@@ -106,7 +106,9 @@ int nhb_sync(nhb_ctx* ctx);
 int nhb_ctx_set_gemv_max_m(nhb_ctx* ctx, int max_m);
 /* tuning knobs: "pdl" (programmatic dependent launch, default 1), "gemv_kernel" (1, 2 or 4: what AUTO uses for
  * small M), "rows_ctas_per_sm", "prequantize", "ctas_per_sm" (streaming GEMV, 1 or 2), "gemv_max_m", "rows_fat_ctas",
- * "fused_gather" */
+ * "rows_split_long", "fused_gather", and the placement policy "replicate_below_mb": with world > 1, a weight smaller
+ * than that many MiB is kept whole on every rank (n0 = 0, n1 = N; every rank computes every row, no exchange) instead of
+ * row-sharded -- set it before uploading; 0 (default) shards everything */
 int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value);
 /* kernels this context has launched so far (upload, mul_mat, gather ...) */
 long long nhb_ctx_launch_count(const nhb_ctx* ctx);

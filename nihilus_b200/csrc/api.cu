@@ -104,8 +104,11 @@ struct nhb_ctx {
 		char* local	 = nullptr;
 		size_t bytes = 0;
 		char* peer[NHB_MAX_WORLD] = {};// this rank's own entry is `local`
-		bool complete = false;// the last kernel that wrote into it delivered every rank's columns itself
 	};
+	// outputs whose rows are already whole on every rank (delivered by a fused launch, or computed from a replicated
+	// weight): nhb_all_gather has nothing to do for them.  Keyed by the output pointer the caller passes.
+	std::vector<const void*> complete;
+	int64_t replicate_below = 0;// bytes: smaller weights are kept whole on every rank instead of row-sharded
 	std::vector<symm_region> regions;
 	unsigned* push_local = nullptr;// [0] CTAs done in the running launch, [1] fused launches completed
 	int fused_gather	 = 1;
@@ -295,19 +298,28 @@ namespace {
 		nhb_ctx::symm_region* regs[NHB_MAX_BATCH];
 		for (int i = 0; i < b.n_ops; ++i) {
 			const nhb_mul_mat_op* op = src_ops[i];
+			regs[i]					 = nullptr;
+			if (op->w->n1 - op->w->n0 == op->w->N)
+				continue;// replicated: nothing to deliver, the output may live anywhere
 			// the whole row range this launch completes must be inside one region
 			float* first = op->y + m0 * op->ldy;
 			regs[i]		 = find_region(ctx, first, (static_cast<size_t>(mt - 1) * op->ldy + op->w->N) * sizeof(float));
 			if (!regs[i] || regs[i] == &ctx->regions[0])
 				return false;
 		}
+		bool any = false;
 		for (int i = 0; i < b.n_ops; ++i) {
+			const nhb_weight* w = src_ops[i]->w;
+			if (w->n1 - w->n0 == w->N)
+				continue;// replicated weight: every rank computes every row, nothing to deliver (y_peer stays null)
 			const char* y_local = reinterpret_cast<const char*>(b.op[i].y);
 			const size_t off	= static_cast<size_t>(y_local - regs[i]->local);
 			for (int r = 0; r < ctx->world; ++r)
 				b.y_peer[i][r] = reinterpret_cast<float*>(regs[i]->peer[r] + off);
-			regs[i]->complete = true;
+			any = true;
 		}
+		if (!any)
+			return false;
 		b.push.world	   = ctx->world;
 		b.push.rank		   = ctx->rank;
 		b.push.done_ctas   = ctx->push_local;
@@ -397,8 +409,11 @@ namespace {
 					bool all_ranks_have_rows = true;
 					for (int i = 0; i < n_ops; ++i)
 						all_ranks_have_rows = all_ranks_have_rows && ops[i].w->N >= ctx->world;
-					if (!ctx->rows_db && ctx->rows_cluster <= 1 && all_ranks_have_rows)
-						setup_push(ctx, b, src_ops, mt, m0);
+					const bool pushed = !ctx->rows_db && ctx->rows_cluster <= 1 && all_ranks_have_rows && setup_push(ctx, b, src_ops, mt, m0);
+					if (pushed && m0 + mt >= M)
+						for (int i = 0; i < b.n_ops; ++i)
+							if (b.y_peer[i][0])
+								ctx->complete.push_back(src_ops[i]->y);
 					cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, ctx->rows_db != 0, ctx->rows_cluster, ctx->rows_fat != 0, ctx->rows_split != 0);
 					if (e != cudaSuccess)
 						return fail_cuda(ctx, e, "gemv_q8_rows launch");
@@ -622,6 +637,7 @@ int nhb_ctx_create(nhb_ctx** out, int device, int rank, int world) {
 	ctx->preq		 = env_int("NHB_PREQ", 0);
 	ctx->rows_db	 = env_int("NHB_ROWS_DB", 0);
 	ctx->rows_cluster = env_int("NHB_ROWS_CLUSTER", 1);
+	ctx->replicate_below = static_cast<int64_t>(std::max(0, env_int("NHB_REPLICATE_MB", 0))) << 20;
 	ctx->rows_fat	  = env_int("NHB_ROWS_FAT", 1);
 	ctx->rows_split	  = env_int("NHB_ROWS_SPLIT", 1);
 	{
@@ -689,6 +705,8 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 		ctx->rows_db = value != 0;
 	else if (!std::strcmp(name, "rows_cluster"))
 		ctx->rows_cluster = value < 1 ? 1 : value;
+	else if (!std::strcmp(name, "replicate_below_mb"))
+		ctx->replicate_below = static_cast<int64_t>(value < 0 ? 0 : value) << 20;
 	else if (!std::strcmp(name, "fused_gather"))
 		ctx->fused_gather = value != 0;
 	else if (!std::strcmp(name, "rows_split_long"))
@@ -786,6 +804,11 @@ int nhb_weight_upload_q8_0(nhb_ctx* ctx, const void* host_blocks34, int64_t N, i
 	w->K		  = K;
 	w->device	  = ctx->device;
 	nhb_shard_rows(N, ctx->world, ctx->rank, &w->n0, &w->n1);
+	if (ctx->world > 1 && N * (K / 32) * 34 < ctx->replicate_below) {
+		// placement policy: a weight this small costs less to stream whole on every rank than to shard and exchange
+		w->n0 = 0;
+		w->n1 = N;
+	}
 	const int64_t rows = w->n1 - w->n0;
 	const int64_t nb   = K / 32;
 	if (rows > 0) {
@@ -901,9 +924,12 @@ int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int ac
 		return NHB_OK;
 	device_guard g(ctx->device);
 	// whatever this call writes is this rank's slice only, until a fused launch below says otherwise
-	for (int i = 0; i < n_ops && !ctx->regions.empty(); ++i)
-		if (nhb_ctx::symm_region* r = find_region(ctx, ops[i].y, sizeof(float)))
-			r->complete = false;
+	for (int i = 0; i < n_ops && ctx->world > 1; ++i) {
+		auto& c = ctx->complete;
+		c.erase(std::remove(c.begin(), c.end(), static_cast<const void*>(ops[i].y)), c.end());
+		if (ops[i].w->n1 - ops[i].w->n0 == ops[i].w->N)
+			c.push_back(ops[i].y);// replicated weight: this rank writes the whole row itself
+	}
 	const int forced = env_int("NHB_FORCE_KERNEL", 0);
 	if (kernel == NHB_KERNEL_AUTO && forced >= 1 && forced <= 4)
 		kernel = forced;
@@ -1147,11 +1173,10 @@ int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, 
 		return fail(ctx, NHB_ERR_NCCL, "nhb_comm_init has not been called");
 	device_guard g(ctx->device);
 	// outputs a fused GEMV launch has already completed on every rank need no collective
-	bool any_left = false;
-	for (int i = 0; i < n; ++i) {
-		nhb_ctx::symm_region* r = (y_dev[i] && !ctx->regions.empty()) ? find_region(ctx, y_dev[i], sizeof(float)) : nullptr;
-		any_left				= any_left || !(r && r->complete);
-	}
+	auto is_complete = [&](const void* y) { return std::find(ctx->complete.begin(), ctx->complete.end(), y) != ctx->complete.end(); };
+	bool any_left	 = false;
+	for (int i = 0; i < n; ++i)
+		any_left = any_left || !is_complete(y_dev[i]);
 	if (!any_left)
 		return NHB_OK;
 	nccl_api& nc = nccl();
@@ -1161,9 +1186,8 @@ int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, 
 			nc.GroupEnd();
 			return fail(ctx, NHB_ERR_ARG, "nhb_all_gather_batch: bad entry");
 		}
-		if (nhb_ctx::symm_region* r = ctx->regions.empty() ? nullptr : find_region(ctx, y_dev[i], sizeof(float)))
-			if (r->complete)
-				continue;
+		if (is_complete(y_dev[i]))
+			continue;
 		const bool even = N[i] % ctx->world == 0;
 		for (int64_t m = 0; m < M[i] && rc == nccl_success; ++m) {
 			float* row = y_dev[i] + m * ldy[i];

@@ -294,7 +294,7 @@ namespace nhb {
 						for (int m = 0; m < MT; ++m) {
 							const float v = __ldcg(op->y + static_cast<size_t>(m) * ld + lrow);
 							for (int r = 0; r < b.push.world; ++r)
-								if (r != b.push.rank)
+								if (r != b.push.rank && b.y_peer[pcur][r])
 									b.y_peer[pcur][r][static_cast<size_t>(m) * ld + lrow] = v;
 						}
 					}
@@ -377,7 +377,7 @@ namespace nhb {
 				op->y[off]		  = v;
 				if (b.push.world > 1)
 					for (int r = 0; r < b.push.world; ++r)
-						if (r != b.push.rank)
+						if (r != b.push.rank && b.y_peer[ocur][r])
 							b.y_peer[ocur][r][off] = v;
 			}
 			if (b.push.world > 1)

@@ -94,6 +94,26 @@ def _worker(rank, world, uid_path, q):
         g.free()
         for h in hs.values():
             h.free()
+        # ---- placement policy: small weights stay whole on every rank, large ones are sharded; one batch mixes both ----
+        ctx.set_option("replicate_below_mb", 4)
+        w_small, w_big = synth.make_weight(700, 4096, 61), synth.make_weight(2048, 4096, 62)  # 3.0 MB and 8.9 MB
+        hs_small, hs_big = ctx.upload(w_small), ctx.upload(w_big)
+        out["small_rows"] = (hs_small.n0, hs_small.n1)
+        out["big_rows"] = (hs_big.n0, hs_big.n1)
+        xr = torch.from_numpy(synth.make_activation(2, 4096, 63)).cuda()
+        ys_small, ys_big = ctx.symm_empty((2, 700)), ctx.symm_empty((2, 2048))
+        l0 = ctx.launches
+        for _ in range(2):
+            ctx.mul_mat_batch([(hs_small, xr, ys_small), (hs_big, xr, ys_big)])
+            ctx.all_gather_batch([ys_small, ys_big])
+            ctx.mul_mat(hs_small, xr, ys_small)  # all ops replicated: no exchange at all
+            ctx.all_gather(ys_small)
+        ctx.sync()
+        out["policy_launches"] = ctx.launches - l0
+        out["p_small"], out["p_big"] = ys_small.cpu().numpy(), ys_big.cpu().numpy()
+        hs_small.free()
+        hs_big.free()
+        ctx.set_option("replicate_below_mb", 0)
     q.put((rank, out))
     ha.free()
     hb.free()
@@ -144,5 +164,15 @@ def test_two_gpu_shards_all_gathered_match_oracle(capi, oracle, tmp_path):
             assert (results[r]["f_" + name].view(np.uint32) == results[0]["g_" + name].view(np.uint32)).all()
         if name in ("even", "ragged"):
             assert (results[0]["f_" + name].view(np.uint32) == results[0][name].view(np.uint32)).all()
+    xr = synth.make_activation(2, 4096, 63)
+    for key, seed, N in (("p_small", 61, 700), ("p_big", 62, 2048)):
+        ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, 4096, seed), xr)
+        for r in range(world):
+            assert np.abs(results[r][key] - ref).max() <= 1e-4 * np.abs(ref).max(), (key, r)
+        assert (results[0][key].view(np.uint32) == results[1][key].view(np.uint32)).all()
+    for r in range(world):
+        assert results[r]["small_rows"] == (0, 700)  # whole on every rank
+        assert results[r]["big_rows"] == ((0, 1024), (1024, 2048))[r]
+        assert results[r]["policy_launches"] == 4  # two kernels per repetition, never a collective
     # 3 single mul_mats (m8 takes two GEMV launches) + 1 batch per repetition, and no NCCL launch at all
     assert results[0]["fused_launches_per_rep"] == 5
