@@ -84,6 +84,9 @@ const char* nhb_last_error(const nhb_ctx* ctx);
 /* rows [n0, n1) of an N-row weight owned by `rank` of `world`; the remainder goes to the lowest ranks.
  * No counterpart in the reference (device 0 is hard-wired, cuda/common.hpp:36-40). */
 int nhb_shard_rows(int64_t N, int world, int rank, int64_t* n0, int64_t* n1);
+/* the rows nhb_weight_upload_q8_0 gives `rank`: the shard above, or all N rows when the weight's Q8_0 size,
+ * N * (K/32) * 34 bytes, is below `replicate_below_bytes` (the "replicate_below_mb" option of a context) */
+int nhb_place_rows(int64_t N, int64_t K, int world, int rank, int64_t replicate_below_bytes, int64_t* n0, int64_t* n1);
 /* 34-byte blocks -> int8 plane + fp16 plane for rows [n0, n1); the layout nhb_weight_upload_q8_0 builds on the GPU */
 int nhb_repack_q8_0_host(const void* blocks34, int64_t N, int64_t K, int64_t n0, int64_t n1, int8_t* q_plane, uint16_t* d_plane);
 int nhb_unpack_q8_0_host(const int8_t* q_plane, const uint16_t* d_plane, int64_t rows, int64_t K, void* blocks34);

@@ -553,6 +553,19 @@ int nhb_shard_rows(int64_t N, int world, int rank, int64_t* n0, int64_t* n1) {
 	return NHB_OK;
 }
 
+int nhb_place_rows(int64_t N, int64_t K, int world, int rank, int64_t replicate_below_bytes, int64_t* n0, int64_t* n1) {
+	if (K <= 0 || K % 32 != 0)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_place_rows: K must be a positive multiple of 32");
+	int rc = nhb_shard_rows(N, world, rank, n0, n1);
+	if (rc != NHB_OK)
+		return rc;
+	if (world > 1 && N * (K / 32) * 34 < replicate_below_bytes) {
+		*n0 = 0;
+		*n1 = N;
+	}
+	return NHB_OK;
+}
+
 int nhb_repack_q8_0_host(const void* blocks34, int64_t N, int64_t K, int64_t n0, int64_t n1, int8_t* q_plane, uint16_t* d_plane) {
 	if (!blocks34 || !q_plane || !d_plane || N < 0 || K <= 0 || K % 32 != 0 || n0 < 0 || n1 > N || n0 > n1)
 		return fail(nullptr, NHB_ERR_ARG, "nhb_repack_q8_0_host: bad arguments");
@@ -803,12 +816,8 @@ int nhb_weight_upload_q8_0(nhb_ctx* ctx, const void* host_blocks34, int64_t N, i
 	w->N		  = N;
 	w->K		  = K;
 	w->device	  = ctx->device;
-	nhb_shard_rows(N, ctx->world, ctx->rank, &w->n0, &w->n1);
-	if (ctx->world > 1 && N * (K / 32) * 34 < ctx->replicate_below) {
-		// placement policy: a weight this small costs less to stream whole on every rank than to shard and exchange
-		w->n0 = 0;
-		w->n1 = N;
-	}
+	// placement policy: a weight under the threshold costs less to stream whole on every rank than to shard and exchange
+	nhb_place_rows(N, K, ctx->world, ctx->rank, ctx->replicate_below, &w->n0, &w->n1);
 	const int64_t rows = w->n1 - w->n0;
 	const int64_t nb   = K / 32;
 	if (rows > 0) {

@@ -106,3 +106,24 @@ def test_product_does_not_touch_the_oracle():
         p = os.path.join(ROOT, "include", f)
         if os.path.isfile(p):
             assert "oracle" not in open(p).read()
+
+
+def test_placement_policy_replicates_small_weights_only(capi):
+    """LLaMA-3-8B at 8 ranks with a 48 MiB threshold: q, k, v, attn_output whole on every rank, the FFN and lm_head sharded."""
+    from nihilus_b200 import shapes
+
+    thr = 48 << 20
+    for name, (n, k) in shapes.LLAMA3_8B.items():
+        covered = []
+        for r in range(8):
+            n0, n1 = capi.place_rows(n, k, 8, r, thr)
+            if name in ("attn_q", "attn_k", "attn_v", "attn_output"):
+                assert (n0, n1) == (0, n)
+            else:
+                assert (n0, n1) == capi.shard_rows(n, 8, r)
+                covered.append((n0, n1))
+        if covered:
+            assert covered[0][0] == 0 and covered[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+        assert capi.place_rows(n, k, 1, 0, thr) == (0, n)  # one rank: nothing to decide
+        assert capi.place_rows(n, k, 8, 3, 0) == capi.shard_rows(n, 8, 3)  # policy off
