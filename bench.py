@@ -199,6 +199,8 @@ def main():
     ap.add_argument("--layers", type=int, default=shapes.L, help="debug: fewer layers (the reported workload is 32)")
     ap.add_argument("--group", default="stage", choices=["stage", "op"], help="ops launched together: independent ops of a stage, or one by one")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--act-mode", default="q8", choices=["q8", "f32"],
+                    help="q8: activations quantised to Q8_0, exact int8 block dots (the reported metric); f32: f32 activations x dequantised weights")
     ap.add_argument("--replicate-mb", type=int, default=48,
                     help="N > 1 placement policy: weights smaller than this many MiB stay whole on every rank (no exchange); 0 shards all")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
@@ -283,9 +285,11 @@ def main():
     else:
         groups = [[j] for j in range(len(ops))]
 
+    act_mode = capi.ACT_Q8 if args.act_mode == "q8" else capi.ACT_F32
+
     def enqueue_step():
         for g in groups:
-            ctx.mul_mat_batch([(weights[j], xs[j], ys[j]) for j in g])
+            ctx.mul_mat_batch([(weights[j], xs[j], ys[j]) for j in g], act_mode=act_mode)
             if world > 1 and args.gather != "none":  # "none" leaves the rows incomplete: timing experiments only
                 ctx.all_gather_batch([ys[j] for j in g])
 
@@ -378,7 +382,7 @@ def main():
             "config": {
                 "workload": "configs[2]: LLaMA-3-8B full decode matmul set, batch 1: %d layers x (q,k,v,o,gate,up,down) + lm_head = %d Q8_0 mul_mats, "
                             "%.3f GB of Q8_0 weights per step" % (args.layers, len(ops), weight_bytes / 1e9),
-                "act_mode": "q8_0 activations (reference quantiser), exact int8 block dots",
+                "act_mode": "q8_0 activations (reference quantiser), exact int8 block dots" if args.act_mode == "q8" else "f32 activations x dequantised weights",
                 "launch_grouping": args.group, "cuda_graph": graph is not None, "parallelism": "row-shard x%d" % world + ("" if world == 1 or not args.replicate_mb else " (weights under %d MiB replicated)" % args.replicate_mb) + ("" if world == 1 else (" + all-gather fused into the GEMV (peer stores over NVLink)" if args.gather == "fused" else " + NCCL all-gather per stage")),
                 "l2": "inputs larger than L2 (%.2f GB of weights per GPU per step vs 126 MB)" % (weight_bytes / world / 1e9),
             },

@@ -339,14 +339,21 @@ namespace {
 		if (kernel == NHB_KERNEL_AUTO)
 			kernel = ctx->gemv_default;
 		// ---- warp-per-row GEMV: the default ----
-		if (act_mode == NHB_ACT_Q8 && kernel == NHB_KERNEL_GEMV_ROWS) {
+		const bool f32act = act_mode == NHB_ACT_F32;
+		if (kernel == NHB_KERNEL_GEMV_ROWS) {
 			int mt_max = 4;
 			for (int i = 0; i < n_ops; ++i)
-				while (mt_max > 0 && !gemv_rows_supports(ops[i].w->K, mt_max))
+				while (mt_max > 0 && !gemv_rows_supports(ops[i].w->K, mt_max, f32act))
 					--mt_max;
+			// the shared-memory budget counts every distinct input once
 			size_t act_total = 0;
-			for (int i = 0; i < n_ops && mt_max > 0; ++i)
-				act_total += gemv_rows_act_bytes(ops[i].w->K, 1);
+			for (int i = 0; i < n_ops && mt_max > 0; ++i) {
+				bool seen = false;
+				for (int j = 0; j < i; ++j)
+					seen = seen || (ops[j].x == ops[i].x && ops[j].ldx == ops[i].ldx && ops[j].w->K == ops[i].w->K);
+				if (!seen)
+					act_total += gemv_rows_act_bytes(ops[i].w->K, 1, f32act);
+			}
 			while (mt_max > 1 && act_total * mt_max > 96 * 1024)
 				--mt_max;
 			if (mt_max >= 1 && act_total <= 96 * 1024) {
@@ -379,7 +386,7 @@ namespace {
 							b.slot_op[b.n_slots++] = b.n_ops;
 							ro.act_off			   = static_cast<int>(off);
 							ro.preq_off			   = static_cast<int>(off);
-							off += gemv_rows_act_bytes(ro.K, mt);
+							off += gemv_rows_act_bytes(ro.K, mt, f32act);
 						} else {
 							ro.act_off	= b.op[b.slot_op[slot]].act_off;
 							ro.preq_off = ro.act_off;
@@ -389,7 +396,8 @@ namespace {
 					if (b.n_ops == 0)
 						break;
 					b.act_bytes = static_cast<int>(off);
-					if (ctx->preq) {
+					b.f32act	= f32act ? 1 : 0;
+					if (ctx->preq && !f32act) {
 						int rc = ensure(ctx, &ctx->scratch, &ctx->scratch_cap, off, "activation scratch");
 						if (rc != NHB_OK)
 							return rc;
@@ -592,7 +600,7 @@ int nhb_unpack_q8_0_host(const int8_t* q_plane, const uint16_t* d_plane, int64_t
 int nhb_choose_kernel(int64_t N, int64_t K, int64_t M, int act_mode) {
 	(void)N;
 	if (act_mode == NHB_ACT_F32)
-		return NHB_KERNEL_GEMV_LDG;
+		return gemv_rows_supports(K, M > 4 ? 4 : (M < 1 ? 1 : M), true) ? NHB_KERNEL_GEMV_ROWS : NHB_KERNEL_GEMV_LDG;
 	if (M <= 8)
 		return gemv_rows_supports(K, 1) ? NHB_KERNEL_GEMV_ROWS : NHB_KERNEL_GEMV_LDG;
 	return NHB_KERNEL_GEMM_TC;

@@ -102,6 +102,52 @@ namespace nhb {
 			}
 		}
 
+		// f32-activation arithmetic (vec_dot_q8_f32, include/nihilus-incl/cpu/avx_2.hpp:4782-4852): per block
+		// s = sum_j x_j * float(q_j), acc += s * d_w.  Activations sit in shared memory as float4 [MT][8][nb]: chunk c of
+		// block blk at (c * nb + blk), so a warp reading one block per lane touches consecutive 16-byte words.
+		template<int MT> __device__ __forceinline__ void compute_item_f32(const item_regs& r, float (&acc)[MT], const unsigned char* act, int nb, int b0, int lane) {
+#pragma unroll
+			for (int i = 0; i < ITEM; ++i) {
+				const int blk = b0 + lane + 32 * i;
+				if (blk < nb) {
+					const float dw		= __half2float(__ushort_as_half(r.d[i]));
+					const uint32_t w[8] = { r.w[i].lo.x, r.w[i].lo.y, r.w[i].lo.z, r.w[i].lo.w, r.w[i].hi.x, r.w[i].hi.y, r.w[i].hi.z, r.w[i].hi.w };
+#pragma unroll
+					for (int m = 0; m < MT; ++m) {
+						const float4* xs = reinterpret_cast<const float4*>(act) + static_cast<size_t>(m) * 8 * nb;
+						float s0 = 0.f, s1 = 0.f;// two chains: the 32 fmas of a block would otherwise be one dependent run
+#pragma unroll
+						for (int c = 0; c < 8; ++c) {
+							const float4 xv = xs[c * nb + blk];
+							const int q0 = static_cast<int8_t>(w[c] & 0xff), q1 = static_cast<int8_t>((w[c] >> 8) & 0xff);
+							const int q2 = static_cast<int8_t>((w[c] >> 16) & 0xff), q3 = static_cast<int8_t>(w[c] >> 24);
+							s0 = fmaf(xv.x, static_cast<float>(q0), s0);
+							s1 = fmaf(xv.y, static_cast<float>(q1), s1);
+							s0 = fmaf(xv.z, static_cast<float>(q2), s0);
+							s1 = fmaf(xv.w, static_cast<float>(q3), s1);
+						}
+						acc[m] = fmaf(s0 + s1, dw, acc[m]);
+					}
+				}
+			}
+		}
+
+		// Prologue of the f32-activation mode: copy every distinct input into shared memory in the chunk-major layout above.
+		template<int MT> __device__ __forceinline__ void stage_inputs_f32(const rows_batch& b, unsigned char* act_smem, int tid) {
+			for (int s = 0; s < b.n_slots; ++s) {
+				const rows_op* op = &b.op[b.slot_op[s]];
+				float4* dst		  = reinterpret_cast<float4*>(act_smem + op->act_off);
+				const int nb	  = op->K >> 5;
+				for (int i = tid; i < MT * nb * 8; i += static_cast<int>(blockDim.x)) {
+					const int m	  = i / (nb * 8);
+					const int j	  = i - m * nb * 8;// float4 index inside the row: block j / 8, chunk j % 8
+					const float4 v = __ldg(reinterpret_cast<const float4*>(op->x + static_cast<size_t>(m) * op->ldx) + j);
+					dst[static_cast<size_t>(m) * 8 * nb + (j & 7) * nb + (j >> 3)] = v;
+				}
+			}
+			__syncthreads();
+		}
+
 		// Prologue of both GEMV variants: quantise every distinct input of the batch into shared memory.
 		template<int MT> __device__ __forceinline__ void quantize_inputs(const rows_batch& b, unsigned char* act_smem, int tid) {
 		const uint32_t cn = cluster_size();
@@ -219,7 +265,7 @@ namespace nhb {
 				atomicExch(pc.status, DEV_TIMEOUT_PEER);
 		}
 
-		template<int MT, int OCC, int TPB = ROWS_TPB> __global__ void __launch_bounds__(TPB, OCC) gemv_q8_rows(const __grid_constant__ rows_batch b) {
+		template<int MT, int OCC, int TPB = ROWS_TPB, bool F32 = false> __global__ void __launch_bounds__(TPB, OCC) gemv_q8_rows(const __grid_constant__ rows_batch b) {
 			constexpr int WARPS = TPB / 32;
 			extern __shared__ __align__(128) unsigned char act_smem[];
 			const int tid		 = threadIdx.x;
@@ -240,7 +286,10 @@ namespace nhb {
 			}
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
-			quantize_inputs<MT>(b, act_smem, tid);
+			if constexpr (F32)
+				stage_inputs_f32<MT>(b, act_smem, tid);
+			else
+				quantize_inputs<MT>(b, act_smem, tid);
 			// ---- rows ----
 			for (int row = row0; row < total_rows; row += W) {
 				while (cur + 1 < n_ops && row >= b.op[cur + 1].row_begin)
@@ -266,7 +315,10 @@ namespace nhb {
 #pragma unroll
 					for (int m = 0; m < MT; ++m)
 						acc[m] = 0.f;
-					compute_item<MT>(regs, acc, act, rd.nb, b0, lane);
+					if constexpr (F32)
+						compute_item_f32<MT>(regs, acc, act, rd.nb, b0, lane);
+					else
+						compute_item<MT>(regs, acc, act, rd.nb, b0, lane);
 #pragma unroll
 					for (int m = 0; m < MT; ++m)
 						rowacc[m] += warp_sum(acc[m]);
@@ -312,7 +364,7 @@ namespace nhb {
 		// added per row in ascending order -- the same order, hence the same bits, as the one-warp-per-row kernels.
 		// All ops of the launch must share K.
 		constexpr int SPLIT_MAX_ROWS = 64;// rows per CTA the partial-sum array is sized for
-		template<int MT> __global__ void __launch_bounds__(ROWS_TPB_FAT, 1) gemv_q8_rows_split(const __grid_constant__ rows_batch b) {
+		template<int MT, bool F32 = false> __global__ void __launch_bounds__(ROWS_TPB_FAT, 1) gemv_q8_rows_split(const __grid_constant__ rows_batch b) {
 			constexpr int WARPS = ROWS_WARPS_FAT;
 			extern __shared__ __align__(128) unsigned char act_smem[];
 			__shared__ float part[SPLIT_MAX_ROWS * 8 * MT];// [row][item][m]
@@ -338,7 +390,10 @@ namespace nhb {
 			}
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
-			quantize_inputs<MT>(b, act_smem, tid);
+			if constexpr (F32)
+				stage_inputs_f32<MT>(b, act_smem, tid);
+			else
+				quantize_inputs<MT>(b, act_smem, tid);
 			for (int it = warp; it < n_items; it += WARPS) {
 				const int rl  = it / ipr;
 				const int b0  = (it - rl * ipr) * 32 * ITEM;
@@ -353,7 +408,10 @@ namespace nhb {
 #pragma unroll
 				for (int m = 0; m < MT; ++m)
 					acc[m] = 0.f;
-				compute_item<MT>(regs, acc, act_smem + op->act_off, rd.nb, b0, lane);
+				if constexpr (F32)
+					compute_item_f32<MT>(regs, acc, act_smem + op->act_off, rd.nb, b0, lane);
+				else
+					compute_item<MT>(regs, acc, act_smem + op->act_off, rd.nb, b0, lane);
 #pragma unroll
 				for (int m = 0; m < MT; ++m) {
 					const float v = warp_sum(acc[m]);
@@ -495,12 +553,13 @@ namespace nhb {
 		}
 	}
 
-	size_t gemv_rows_act_bytes(int64_t K, int M) {
-		return static_cast<size_t>(((M * (K + (K / 32) * 4)) + 127) & ~int64_t(127));
+	size_t gemv_rows_act_bytes(int64_t K, int M, bool f32act) {
+		const int64_t per_row = f32act ? K * 4 : K + (K / 32) * 4;
+		return static_cast<size_t>((M * per_row + 127) & ~int64_t(127));
 	}
 
-	bool gemv_rows_supports(int64_t K, int64_t M) {
-		return K % 32 == 0 && M >= 1 && M <= 4 && gemv_rows_act_bytes(K, static_cast<int>(M)) <= 96 * 1024;
+	bool gemv_rows_supports(int64_t K, int64_t M, bool f32act) {
+		return K % 32 == 0 && M >= 1 && M <= 4 && gemv_rows_act_bytes(K, static_cast<int>(M), f32act) <= 96 * 1024;
 	}
 
 	// `b` arrives with op pointers/shapes, act_off/slot tables and preq fields filled by the caller.
@@ -518,6 +577,11 @@ namespace nhb {
 		if (ctas_per_sm < 1)
 			ctas_per_sm = 1;
 		// one 24-warp CTA per SM when every one of those warps gets a row, else 8-warp CTAs
+		if (b.f32act) {// one shape family for the f32 mode: no double buffering, no clusters, 2 CTAs per SM when not fat
+			double_buffer = false;
+			cluster		  = 1;
+			ctas_per_sm	  = 2;
+		}
 		const bool fat	= fat_ctas && !double_buffer && cluster <= 1 && rows >= cfg.sm_count * ROWS_WARPS_FAT;
 		const int warps = fat ? ROWS_WARPS_FAT : ROWS_WARPS;
 		if (fat)
@@ -564,8 +628,33 @@ namespace nhb {
 		lc.numAttrs = n_attr;
 		// registers per thread are capped by the occupancy the grid was sized for (2, 3 or 4 CTAs per SM)
 		const int occ = double_buffer ? 0 : (ctas_per_sm >= 4 ? 4 : (ctas_per_sm == 3 ? 3 : 2));
+#define NHB_ROWS_F32_CASE(MT) \
+	if (b.f32act && M == MT) { \
+		e = cudaSuccess; \
+		if (split) { \
+			auto kern = gemv_q8_rows_split<MT, true>; \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			if (e == cudaSuccess) \
+				e = cudaLaunchKernelEx(&lc, kern, b); \
+		} else if (fat) { \
+			auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT, true>; \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			if (e == cudaSuccess) \
+				e = cudaLaunchKernelEx(&lc, kern, b); \
+		} else { \
+			auto kern = gemv_q8_rows<MT, 2, ROWS_TPB, true>; \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			if (e == cudaSuccess) \
+				e = cudaLaunchKernelEx(&lc, kern, b); \
+		} \
+	}
+		NHB_ROWS_F32_CASE(1)
+		NHB_ROWS_F32_CASE(2)
+		NHB_ROWS_F32_CASE(3)
+		NHB_ROWS_F32_CASE(4)
+#undef NHB_ROWS_F32_CASE
 #define NHB_ROWS_SPLIT_CASE(MT) \
-	if (split && M == MT) { \
+	if (!b.f32act && split && M == MT) { \
 		auto kern = gemv_q8_rows_split<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 40 * 1024) \
@@ -579,7 +668,7 @@ namespace nhb {
 		NHB_ROWS_SPLIT_CASE(4)
 #undef NHB_ROWS_SPLIT_CASE
 #define NHB_ROWS_FAT_CASE(MT) \
-	if (fat && !split && M == MT) { \
+	if (!b.f32act && fat && !split && M == MT) { \
 		auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
@@ -593,7 +682,7 @@ namespace nhb {
 		NHB_ROWS_FAT_CASE(4)
 #undef NHB_ROWS_FAT_CASE
 #define NHB_ROWS_CASE(MT, OCC) \
-	if (!fat && M == MT && occ == OCC) { \
+	if (!b.f32act && !fat && M == MT && occ == OCC) { \
 		auto kern = gemv_q8_rows<MT, OCC>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
@@ -615,7 +704,7 @@ namespace nhb {
 		NHB_ROWS_CASE(4, 4)
 #undef NHB_ROWS_CASE
 #define NHB_ROWS_DB_CASE(MT) \
-	if (double_buffer && M == MT) { \
+	if (!b.f32act && double_buffer && M == MT) { \
 		auto kern = gemv_q8_rows_db<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \

@@ -73,7 +73,7 @@ namespace nhb {
 		int n_slots;// distinct activation inputs
 		int slot_op[NHB_MAX_BATCH];// a representative op per slot
 		int preq;// 1: activations were quantised by a separate kernel into preq_base
-		int pad;
+		int f32act;// 1: f32 activations x dequantised weights instead of the Q8 arithmetic
 		const unsigned char* preq_base;
 		rows_op op[NHB_MAX_BATCH];
 		push_ctl push;
@@ -96,8 +96,8 @@ namespace nhb {
 	cudaError_t launch_quantize(const float* x, long long ldx, int M, int K, int8_t* q, float* d, cudaStream_t s, bool pdl = false);
 
 	// gemv_rows.cu
-	size_t gemv_rows_act_bytes(int64_t K, int M);
-	bool gemv_rows_supports(int64_t K, int64_t M);
+	size_t gemv_rows_act_bytes(int64_t K, int M, bool f32act = false);
+	bool gemv_rows_supports(int64_t K, int64_t M, bool f32act = false);
 	cudaError_t launch_gemv_rows(const rows_batch& b, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer = false, int cluster = 1,
 		bool fat_ctas = false, bool split_long_rows = false);
 	cudaError_t launch_block_dots(const int8_t* wq, const int8_t* qa, int rows, int K, int M, int32_t* dots, cudaStream_t s);

@@ -65,7 +65,8 @@ def test_choose_kernel_and_work_formulas(capi):
     assert capi.lib.nhb_choose_kernel(4096, 4096, 8, capi.ACT_Q8) == capi.KERNEL_GEMV_ROWS
     assert capi.lib.nhb_choose_kernel(4096, 96, 1, capi.ACT_Q8) == capi.KERNEL_GEMV_ROWS
     assert capi.lib.nhb_choose_kernel(4096, 4096, 512, capi.ACT_Q8) == capi.KERNEL_GEMM_TC
-    assert capi.lib.nhb_choose_kernel(4096, 4096, 1, capi.ACT_F32) == capi.KERNEL_GEMV_LDG
+    assert capi.lib.nhb_choose_kernel(4096, 4096, 1, capi.ACT_F32) == capi.KERNEL_GEMV_ROWS
+    assert capi.lib.nhb_choose_kernel(4096, 65536, 1, capi.ACT_F32) == capi.KERNEL_GEMV_LDG
     assert capi.lib.nhb_mul_mat_bytes(4096, 4096, 1) == 17825792 + 16384 + 16384 == shapes.mul_mat_bytes(4096, 4096, 1)
     assert capi.lib.nhb_mul_mat_flops(14336, 4096, 512) == 2 * 512 * 14336 * 4096 == shapes.mul_mat_flops(14336, 4096, 512)
     total = sum(n * (k // 32) * 34 for _, _, n, k in shapes.decode_set())

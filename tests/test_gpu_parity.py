@@ -188,7 +188,7 @@ def test_tensor_core_gemm_ragged_output_and_sharding(capi, ctx, oracle, torch_mo
         assert (yy.view(np.uint32) == full.view(np.uint32)).all()  # row shards are bit-identical to one GPU
 
 
-@pytest.mark.parametrize("N,K,M", [(64, 256, 1), (100, 4096, 3), (32, 14336, 2), (9, 96, 5)])
+@pytest.mark.parametrize("N,K,M", [(64, 256, 1), (100, 4096, 3), (32, 14336, 2), (9, 96, 5), (3700, 4096, 2), (3600, 14336, 1), (5000, 512, 7)])
 def test_f32_activation_mode(capi, ctx, oracle, torch_mod, N, K, M):
     from nihilus_b200 import synth
     from oracle import pyoracle as po
