@@ -30,7 +30,7 @@ UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one full step (129 GEMV launches), from an ncu capture of one layer +
 # lm_head scaled to 32 layers (every layer repeats the captured shapes): profiles/gemv_q8_rows_decode_set.md
-NCU_DRAM_BYTES_PER_STEP = 8144.6e6
+NCU_DRAM_BYTES_PER_STEP = 8094.8e6
 
 
 def measured_peaks():
