@@ -110,6 +110,11 @@ struct nhb_ctx {
 	std::vector<const void*> complete;
 	int64_t replicate_below = 0;// bytes: smaller weights are kept whole on every rank instead of row-sharded
 	std::vector<symm_region> regions;
+	// upload staging: two pinned host buffers, two device buffers, an event each (kept for the next upload)
+	void* up_pinned[2]	   = { nullptr, nullptr };
+	void* up_dev[2]		   = { nullptr, nullptr };
+	cudaEvent_t up_done[2] = { nullptr, nullptr };
+	size_t up_cap		   = 0;
 	unsigned* push_local = nullptr;// [0] CTAs done in the running launch, [1] fused launches completed
 	int fused_gather	 = 1;
 };
@@ -679,6 +684,14 @@ int nhb_ctx_destroy(nhb_ctx* ctx) {
 		nccl().CommDestroy(ctx->comm);
 	for (auto& r: ctx->regions)
 		symm_release(ctx, r);
+	for (int i = 0; i < 2; ++i) {
+		if (ctx->up_pinned[i])
+			cudaFreeHost(ctx->up_pinned[i]);
+		if (ctx->up_dev[i])
+			cudaFree(ctx->up_dev[i]);
+		if (ctx->up_done[i])
+			cudaEventDestroy(ctx->up_done[i]);
+	}
 	if (ctx->push_local)
 		cudaFree(ctx->push_local);
 	if (ctx->scratch)
@@ -838,23 +851,51 @@ int nhb_weight_upload_q8_0(nhb_ctx* ctx, const void* host_blocks34, int64_t N, i
 			delete w;
 			return fail_cuda(ctx, e, "weight plane allocation");
 		}
-		// stage raw blocks in row chunks of <= 64 MiB and split them on the device
+		// Raw blocks travel in row chunks of <= 32 MiB through two pinned host buffers and two device buffers, and are
+		// split on the device.  The caller's memory is usually pageable (a mapped GGUF file): copying it into pinned
+		// memory on this thread while the previous chunk is on the bus and in the repack kernel roughly triples the
+		// rate of handing pageable memory to cudaMemcpyAsync chunk by chunk.
 		const int64_t row_bytes	 = nb * 34;
-		const int64_t chunk_rows = std::max<int64_t>(1, (int64_t(64) << 20) / row_bytes);
-		void* stage				 = nullptr;
+		const int64_t chunk_rows = std::max<int64_t>(1, (int64_t(32) << 20) / row_bytes);
 		const size_t stage_bytes = static_cast<size_t>(std::min(chunk_rows, rows) * row_bytes);
-		e						 = cudaMalloc(&stage, stage_bytes);
 		const uint8_t* src		 = static_cast<const uint8_t*>(host_blocks34) + w->n0 * row_bytes;
-		for (int64_t r0 = 0; r0 < rows && e == cudaSuccess; r0 += chunk_rows) {
-			const int64_t rr = std::min(chunk_rows, rows - r0);
-			e				 = cudaMemcpyAsync(stage, src + r0 * row_bytes, static_cast<size_t>(rr * row_bytes), cudaMemcpyHostToDevice, ctx->stream);
-			if (e == cudaSuccess)
-				e = launch_repack(static_cast<const uint8_t*>(stage), rr, K, w->q + r0 * K, w->d + r0 * nb, ctx->stream);
-			if (e == cudaSuccess)
-				e = cudaStreamSynchronize(ctx->stream);// the next chunk reuses the staging buffer
+		e						 = cudaSuccess;
+		for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+			if (ctx->up_cap < stage_bytes || !ctx->up_pinned[i]) {
+				if (ctx->up_pinned[i])
+					cudaFreeHost(ctx->up_pinned[i]);
+				if (ctx->up_dev[i])
+					cudaFree(ctx->up_dev[i]);
+				ctx->up_pinned[i] = nullptr;
+				ctx->up_dev[i]	  = nullptr;
+				e				  = cudaMallocHost(&ctx->up_pinned[i], stage_bytes);
+				if (e == cudaSuccess)
+					e = cudaMalloc(&ctx->up_dev[i], stage_bytes);
+			}
+			if (e == cudaSuccess && !ctx->up_done[i])
+				e = cudaEventCreateWithFlags(&ctx->up_done[i], cudaEventDisableTiming);
 		}
-		if (stage)
-			cudaFree(stage);
+		if (e == cudaSuccess && ctx->up_cap < stage_bytes)
+			ctx->up_cap = stage_bytes;
+		int slot = 0;
+		bool used[2] = { false, false };
+		for (int64_t r0 = 0; r0 < rows && e == cudaSuccess; r0 += chunk_rows, slot ^= 1) {
+			const int64_t rr   = std::min(chunk_rows, rows - r0);
+			const size_t bytes = static_cast<size_t>(rr * row_bytes);
+			if (used[slot])
+				e = cudaEventSynchronize(ctx->up_done[slot]);// the chunk that used this pair two steps ago has left it
+			if (e != cudaSuccess)
+				break;
+			std::memcpy(ctx->up_pinned[slot], src + r0 * row_bytes, bytes);
+			e = cudaMemcpyAsync(ctx->up_dev[slot], ctx->up_pinned[slot], bytes, cudaMemcpyHostToDevice, ctx->stream);
+			if (e == cudaSuccess)
+				e = launch_repack(static_cast<const uint8_t*>(ctx->up_dev[slot]), rr, K, w->q + r0 * K, w->d + r0 * nb, ctx->stream);
+			if (e == cudaSuccess)
+				e = cudaEventRecord(ctx->up_done[slot], ctx->stream);
+			used[slot] = true;
+		}
+		if (e == cudaSuccess)
+			e = cudaStreamSynchronize(ctx->stream);// the weight is usable, and the caller's buffer released, on return
 		if (e != cudaSuccess) {
 			cudaFree(w->q);
 			cudaFree(w->d);
