@@ -395,7 +395,7 @@ def main():
             "roofline": {
                 "bound": "hbm", "kernel": "gemv_q8_rows", "achieved": per_launch_bytes / (per_launch_ms * 1e-3) / 1e9, "peak": hbm_peak,
                 "unit": "GB/s", "frac": per_launch_bytes / (per_launch_ms * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind,
-                "traffic": (NCU_DRAM_BYTES_PER_STEP / world / gemv_launches) if args.layers == shapes.L else None,
+                "traffic": (NCU_DRAM_BYTES_PER_STEP / gemv_launches) if (args.layers == shapes.L and world == 1) else None,
                 "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms,
                 "note": "per GPU; launch gaps inside the graph are included in the duration",
             },
