@@ -36,7 +36,18 @@ namespace nhb {
 
 		constexpr int GM_ROWS	 = 128;// weight rows per CTA = MMA M
 		constexpr int GM_KSLICE	 = 64;// fp16 elements per smem stage row = 128 bytes = two Q8 blocks
-		constexpr int GM_EPI_WARPS = 16;// four per scheduler: their TMEM loads and FMAs overlap without manual pipelining
+#ifndef NHB_GEMM_EPI_WARPS
+#define NHB_GEMM_EPI_WARPS 16
+#endif
+#ifndef NHB_GEMM_LDU
+#define NHB_GEMM_LDU 2
+#endif
+		constexpr int GM_EPI_WARPS = NHB_GEMM_EPI_WARPS;// 4 TMEM lane quarters x (GM_EPI_WARPS / 4) column groups
+		constexpr int GM_NG		   = GM_EPI_WARPS / 4;
+		constexpr int GM_LDU	   = NHB_GEMM_LDU;// 8-column units fetched per TMEM load (2 or 4)
+		// registers: the CTA redistributes what it was launched with (see the kernel): 20 warps -> 96 at launch, 112 for
+		// the epilogue; 16 warps -> 128 at launch, 160 for the epilogue
+		constexpr int GM_EPI_REGS = GM_EPI_WARPS == 16 ? 112 : 160;
 		constexpr int GM_THREADS   = (4 + GM_EPI_WARPS) * 32;// warpgroup 0: producer warp, MMA warp, two idle warps; then the epilogue warpgroups
 
 		// ---- PTX: TMA, tcgen05 ----
@@ -220,20 +231,35 @@ namespace nhb {
 			asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
 			return v;
 		}
-		// 16 lanes x 16 columns: thread t receives, for k = 0, 1: r[4k], r[4k+1] = lane t/4, columns 8k + 2(t%4), +1 and
-		// r[4k+2], r[4k+3] = lane t/4 + 8, same columns (lanes relative to the lane in taddr)
-		__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+		// 16 lanes x (16 or 32) columns: thread t receives, for k = 0, 1, ...: r[4k], r[4k+1] = lane t/4, columns
+		// 8k + 2(t%4), +1 and r[4k+2], r[4k+3] = lane t/4 + 8, same columns (lanes relative to the lane in taddr)
+		__device__ __forceinline__ void tmem_ld_16x256b(uint32_t taddr, uint32_t (&r)[8]) {
 			asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
 						 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
 						 : "r"(taddr)
 						 : "memory");
 		}
+		__device__ __forceinline__ void tmem_ld_16x256b(uint32_t taddr, uint32_t (&r)[16]) {
+			asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+						 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+						 "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+						 : "r"(taddr)
+						 : "memory");
+		}
 		// Waits for the loads in flight.  The registers pass through the statement so that no use of them can be
 		// scheduled ahead of the wait.
-		__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&a)[8], uint32_t (&b)[8]) {
+		__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&a)[8], uint32_t (&b)[8]) {
 			asm volatile("tcgen05.wait::ld.sync.aligned;"
 						 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]),
 						 "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7])
+						 :
+						 : "memory");
+		}
+		__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&a)[16], uint32_t (&b)[16]) {
+			asm volatile("tcgen05.wait::ld.sync.aligned;"
+						 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]),
+						 "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]),
+						 "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15])
 						 :
 						 : "memory");
 		}
@@ -249,12 +275,12 @@ namespace nhb {
 			constexpr int B_BYTES	  = N_T * GM_KSLICE * 2;
 			constexpr int SC_FLOATS	  = GM_ROWS + N_T;// scales of one Q8 block: lane side, then column side
 			constexpr int UNITS		  = N_T / 8;// 8-column units in the tile, dealt to the four column groups
-			constexpr int BASE		  = UNITS / 4;
-			constexpr int REM		  = UNITS % 4;
+			constexpr int BASE		  = UNITS / GM_NG;
+			constexpr int REM		  = UNITS % GM_NG;
 			constexpr int MAXU		  = BASE + (REM ? 1 : 0);
 			constexpr int STAGE_COLS  = gemm_stage_cols(N_T);
 			constexpr int NS		  = GM_TMEM_COLS / STAGE_COLS;// 2, 4 or 8 accumulator stages
-			constexpr int PAIRS		  = (MAXU + 1) / 2;
+			constexpr int PAIRS		  = (MAXU + GM_LDU - 1) / GM_LDU;// load groups of GM_LDU units
 			extern __shared__ unsigned char smem_raw[];
 			// 1024-byte alignment for the 128-byte swizzle atoms
 			unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -412,12 +438,15 @@ namespace nhb {
 				}
 			} else {
 				// ---------------- epilogue ----------------
-				asm volatile("setmaxnreg.inc.sync.aligned.u32 112;" ::: "memory");
+				if constexpr (GM_EPI_REGS == 112)
+					asm volatile("setmaxnreg.inc.sync.aligned.u32 112;" ::: "memory");
+				else
+					asm volatile("setmaxnreg.inc.sync.aligned.u32 160;" ::: "memory");
 				const int q		   = warp & 3;// TMEM lane quarter this warp may touch
 				const int g		   = (warp - 4) >> 2;// column group
 				const int t4	   = lane & 3;
 				const int my_units = BASE + (g < REM ? 1 : 0);
-				const int my_pairs = (my_units + 1) >> 1;
+				const int my_pairs = (my_units + GM_LDU - 1) / GM_LDU;
 				const int col_off  = (BASE * g + (g < REM ? g : REM)) * 8;// first column of this warp inside the tile
 				const int r0	   = q * 32 + (lane >> 2);// this thread's rows inside the tile: r0 + 8j, j = 0..3
 				const uint32_t tl0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(col_off);
@@ -477,16 +506,16 @@ namespace nhb {
 #pragma unroll
 						for (int pr = 0; pr < PAIRS; ++pr) {
 							if (pr < my_pairs) {
-								uint32_t ra[8], rb[8];
-								uint64_t va[4], vb[4], cs2[2];
+								uint32_t ra[4 * GM_LDU], rb[4 * GM_LDU];
+								uint64_t va[2 * GM_LDU], vb[2 * GM_LDU], cs2[GM_LDU];
 #pragma unroll
-								for (int h = 0; h < 2; ++h)
-									cs2[h] = lds_b64(st + cs_off + (j * SC_FLOATS + 8 * (2 * pr + h)) * 4);
-								tmem_ld_16x256b_x2(tl0 + a * STAGE_COLS + 16 * pr, ra);
-								tmem_ld_16x256b_x2(tl1 + a * STAGE_COLS + 16 * pr, rb);
-								tmem_ld_wait16(ra, rb);
+								for (int h = 0; h < GM_LDU; ++h)
+									cs2[h] = lds_b64(st + cs_off + (j * SC_FLOATS + 8 * (GM_LDU * pr + h)) * 4);
+								tmem_ld_16x256b(tl0 + a * STAGE_COLS + 8 * GM_LDU * pr, ra);
+								tmem_ld_16x256b(tl1 + a * STAGE_COLS + 8 * GM_LDU * pr, rb);
+								tmem_ld_wait_regs(ra, rb);
 #pragma unroll
-								for (int i = 0; i < 4; ++i) {
+								for (int i = 0; i < 2 * GM_LDU; ++i) {
 									va[i] = pack2u(ra[2 * i], ra[2 * i + 1]);
 									vb[i] = pack2u(rb[2 * i], rb[2 * i + 1]);
 								}
@@ -498,8 +527,8 @@ namespace nhb {
 										mbar_arrive_a(tmem_empty0 + 8 * a);
 								}
 #pragma unroll
-								for (int h = 0; h < 2; ++h) {
-									const int un = 2 * pr + h;
+								for (int h = 0; h < GM_LDU; ++h) {
+									const int un = GM_LDU * pr + h;
 									const int ui = un < MAXU ? un : 0;// keeps the index in range where the unrolled body is dead
 									if (un < MAXU && un < my_units) {
 										acc[0][ui] = fma2(va[2 * h], mul2(rs2[0], cs2[h]), acc[0][ui]);
