@@ -92,6 +92,10 @@ int nhb_repack_q8_0_host(const void* blocks34, int64_t N, int64_t K, int64_t n0,
 int nhb_unpack_q8_0_host(const int8_t* q_plane, const uint16_t* d_plane, int64_t rows, int64_t K, void* blocks34);
 /* GEMV (1), or GEMM (3) for this M?  The runtime form of the reference's compile-time eval/prompt split. */
 int nhb_choose_kernel(int64_t N, int64_t K, int64_t M, int act_mode);
+/* the tile shape the tensor-core GEMM takes for `rows` weight rows and M tokens on a GPU with `sms` SMs: 128 rows of one
+ * side on the TMEM lanes (tokens when *swapped, else weight rows), *tile_cols (16..256) rows of the other side on the
+ * columns, *lane_tiles x *col_tiles CTAs.  Host-only; for tests and for reading performance numbers. */
+int nhb_gemm_tile_plan(int64_t rows, int64_t M, int sms, int* swapped, int* tile_cols, int* lane_tiles, int* col_tiles);
 /* algorithmic bytes / flops of one mul_mat: N*(K/32)*34 + 4*M*K + 4*M*N and 2*M*N*K */
 int64_t nhb_mul_mat_bytes(int64_t N, int64_t K, int64_t M);
 int64_t nhb_mul_mat_flops(int64_t N, int64_t K, int64_t M);

@@ -34,7 +34,7 @@ EXPORTS = (
     "nhb_weight_upload_q8_0", "nhb_weight_free", "nhb_weight_info_get", "nhb_weight_download_q8_0", "nhb_mul_mat",
     "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
-    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_place_rows",
+    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_place_rows", "nhb_gemm_tile_plan",
 )
 
 
@@ -60,6 +60,7 @@ _sig("nhb_arch", _i)
 _sig("nhb_last_error", C.c_char_p, _vp)
 _sig("nhb_shard_rows", _i, _i64, _i, _i, C.POINTER(_i64), C.POINTER(_i64))
 _sig("nhb_place_rows", _i, _i64, _i64, _i, _i, _i64, C.POINTER(_i64), C.POINTER(_i64))
+_sig("nhb_gemm_tile_plan", _i, _i64, _i64, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i))
 _sig("nhb_repack_q8_0_host", _i, _vp, _i64, _i64, _i64, _i64, _vp, _vp)
 _sig("nhb_unpack_q8_0_host", _i, _vp, _vp, _i64, _i64, _vp)
 _sig("nhb_choose_kernel", _i, _i64, _i64, _i64, _i)
@@ -137,6 +138,12 @@ def place_rows(N: int, K: int, world: int, rank: int, replicate_below_bytes: int
     a, b = _i64(), _i64()
     _check(lib.nhb_place_rows(N, K, world, rank, replicate_below_bytes, C.byref(a), C.byref(b)))
     return a.value, b.value
+
+
+def gemm_tile_plan(rows: int, M: int, sms: int = 148) -> dict:
+    sw, nt, lt, ct = _i(), _i(), _i(), _i()
+    _check(lib.nhb_gemm_tile_plan(rows, M, sms, C.byref(sw), C.byref(nt), C.byref(lt), C.byref(ct)))
+    return {"swapped": bool(sw.value), "tile_cols": nt.value, "lane_tiles": lt.value, "col_tiles": ct.value}
 
 
 def repack_host(blocks: np.ndarray, n0: int = 0, n1: int | None = None):

@@ -579,6 +579,17 @@ int nhb_place_rows(int64_t N, int64_t K, int world, int rank, int64_t replicate_
 	return NHB_OK;
 }
 
+int nhb_gemm_tile_plan(int64_t rows, int64_t M, int sms, int* swapped, int* tile_cols, int* lane_tiles, int* col_tiles) {
+	if (rows < 1 || M < 1 || sms < 1 || !swapped || !tile_cols || !lane_tiles || !col_tiles)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_gemm_tile_plan: bad arguments");
+	const gemm_plan p = gemm_tc_plan(rows, M, sms);
+	*swapped		  = p.swapped;
+	*tile_cols		  = p.n_t;
+	*lane_tiles		  = p.lane_tiles;
+	*col_tiles		  = p.col_tiles;
+	return NHB_OK;
+}
+
 int nhb_repack_q8_0_host(const void* blocks34, int64_t N, int64_t K, int64_t n0, int64_t n1, int8_t* q_plane, uint16_t* d_plane) {
 	if (!blocks34 || !q_plane || !d_plane || N < 0 || K <= 0 || K % 32 != 0 || n0 < 0 || n1 > N || n0 > n1)
 		return fail(nullptr, NHB_ERR_ARG, "nhb_repack_q8_0_host: bad arguments");

@@ -36,19 +36,17 @@ namespace nhb {
 
 		constexpr int GM_ROWS	 = 128;// weight rows per CTA = MMA M
 		constexpr int GM_KSLICE	 = 64;// fp16 elements per smem stage row = 128 bytes = two Q8 blocks
-#ifndef NHB_GEMM_EPI_WARPS
-#define NHB_GEMM_EPI_WARPS 16
+		// Epilogue warps: 4 TMEM lane quarters x 3 or 4 column groups.  Wide tiles (>= 144 columns) run 12 warps with 160
+		// registers each -- more columns per warp amortise the fixed cost a warp pays per Q8 block (measured: 512 x 14336
+		// rows 179 -> 159 us, 2048 tokens 646 -> 551 us) -- narrower ones 16 warps with 112 (112-column tiles: 151 us
+		// against 165 with 12 warps).  32-column TMEM loads were slower than 16-column ones in both shapes.
+#ifndef NHB_GEMM_WIDEST_WARPS
+#define NHB_GEMM_WIDEST_WARPS 12
 #endif
-#ifndef NHB_GEMM_LDU
-#define NHB_GEMM_LDU 2
-#endif
-		constexpr int GM_EPI_WARPS = NHB_GEMM_EPI_WARPS;// 4 TMEM lane quarters x (GM_EPI_WARPS / 4) column groups
-		constexpr int GM_NG		   = GM_EPI_WARPS / 4;
-		constexpr int GM_LDU	   = NHB_GEMM_LDU;// 8-column units fetched per TMEM load (2 or 4)
-		// registers: the CTA redistributes what it was launched with (see the kernel): 20 warps -> 96 at launch, 112 for
-		// the epilogue; 16 warps -> 128 at launch, 160 for the epilogue
-		constexpr int GM_EPI_REGS = GM_EPI_WARPS == 16 ? 112 : 160;
-		constexpr int GM_THREADS   = (4 + GM_EPI_WARPS) * 32;// warpgroup 0: producer warp, MMA warp, two idle warps; then the epilogue warpgroups
+		__host__ __device__ constexpr int gemm_epi_warps(int n_t) {
+			return n_t >= 208 ? NHB_GEMM_WIDEST_WARPS : (n_t >= 144 ? 12 : 16);
+		}
+		constexpr int GM_LDU = 2;// 8-column units fetched per TMEM load
 
 		// ---- PTX: TMA, tcgen05 ----
 		__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -231,18 +229,11 @@ namespace nhb {
 			asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
 			return v;
 		}
-		// 16 lanes x (16 or 32) columns: thread t receives, for k = 0, 1, ...: r[4k], r[4k+1] = lane t/4, columns
+		// 16 lanes x 16 columns: thread t receives, for k = 0, 1: r[4k], r[4k+1] = lane t/4, columns
 		// 8k + 2(t%4), +1 and r[4k+2], r[4k+3] = lane t/4 + 8, same columns (lanes relative to the lane in taddr)
 		__device__ __forceinline__ void tmem_ld_16x256b(uint32_t taddr, uint32_t (&r)[8]) {
 			asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
 						 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-						 : "r"(taddr)
-						 : "memory");
-		}
-		__device__ __forceinline__ void tmem_ld_16x256b(uint32_t taddr, uint32_t (&r)[16]) {
-			asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-						 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-						 "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
 						 : "r"(taddr)
 						 : "memory");
 		}
@@ -255,26 +246,20 @@ namespace nhb {
 						 :
 						 : "memory");
 		}
-		__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&a)[16], uint32_t (&b)[16]) {
-			asm volatile("tcgen05.wait::ld.sync.aligned;"
-						 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]),
-						 "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]),
-						 "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15])
-						 :
-						 : "memory");
-		}
 		__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
 			uint64_t r;
 			asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
 			return r;
 		}
 
-		template<int N_T> __global__ void __launch_bounds__(GM_THREADS, 1)
+		template<int N_T> __global__ void __launch_bounds__((4 + gemm_epi_warps(N_T)) * 32, 1)
 			gemm_q8_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const gemm_params p, int* __restrict__ dev_status) {
 			constexpr int STAGE_BYTES = gemm_stage_bytes(N_T);
 			constexpr int B_BYTES	  = N_T * GM_KSLICE * 2;
 			constexpr int SC_FLOATS	  = GM_ROWS + N_T;// scales of one Q8 block: lane side, then column side
 			constexpr int UNITS		  = N_T / 8;// 8-column units in the tile, dealt to the four column groups
+			constexpr int GM_EPI_WARPS = gemm_epi_warps(N_T);
+			constexpr int GM_NG		   = GM_EPI_WARPS / 4;// column groups
 			constexpr int BASE		  = UNITS / GM_NG;
 			constexpr int REM		  = UNITS % GM_NG;
 			constexpr int MAXU		  = BASE + (REM ? 1 : 0);
@@ -316,10 +301,8 @@ namespace nhb {
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();// the quantised activations come from the kernel before this one
 
-			// Registers follow the work: 20 warps put five on every scheduler, which caps a uniform allocation at 96 per
-			// thread; warpgroup 0 (copy and MMA issue, a handful of registers) hands most of its share to the epilogue.
-			// The CTA can only redistribute what it was launched with: 128 threads x (96 - 32) released = 512 threads x
-			// (112 - 96) taken.  Asking for more than 112 would wait forever for registers that never come.
+			// Registers follow the work: warpgroup 0 (copy and MMA issue, a handful of registers) hands most of its share
+			// to the epilogue warps.
 			if (warp < 4) {
 				asm volatile("setmaxnreg.dec.sync.aligned.u32 32;" ::: "memory");
 				if (warp == 0) {
@@ -438,10 +421,15 @@ namespace nhb {
 				}
 			} else {
 				// ---------------- epilogue ----------------
-				if constexpr (GM_EPI_REGS == 112)
+				// The CTA can only redistribute what it was launched with: 20 warps launch with 96 registers per thread, 128
+				// threads release 64 each and 512 take 16 (-> 112); 16 warps launch with 128, 128 threads release 96 each and
+				// 384 take 32 (-> 160).  Asking for more would wait forever for registers that never come.
+				if constexpr (GM_EPI_WARPS == 16)
 					asm volatile("setmaxnreg.inc.sync.aligned.u32 112;" ::: "memory");
-				else
+				else if constexpr (GM_EPI_WARPS == 12)
 					asm volatile("setmaxnreg.inc.sync.aligned.u32 160;" ::: "memory");
+				else
+					asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");// 12 warps launch with 168: 128 x 136 released >= 256 x 64 taken
 				const int q		   = warp & 3;// TMEM lane quarter this warp may touch
 				const int g		   = (warp - 4) >> 2;// column group
 				const int t4	   = lane & 3;
@@ -701,7 +689,7 @@ namespace nhb {
 	}
 
 	// Tile shape for `rows` weight rows and M tokens on `sms` SMs.  Both orientations and every column count from 16
-	// to 256 are priced as waves x (columns per tile + a fixed per-tile overhead); the lane side always holds 128 rows.
+	// to 256 are priced as waves x columns per tile; the lane side always holds 128 rows.
 	gemm_plan gemm_tc_plan(int64_t rows, int64_t M, int sms) {
 		gemm_plan best{};
 		double best_cost = 1e300;
@@ -709,14 +697,14 @@ namespace nhb {
 			const int64_t lane_rows = swapped ? M : rows;
 			const int64_t col_rows	= swapped ? rows : M;
 			const int64_t lane_tiles = (lane_rows + GM_ROWS - 1) / GM_ROWS;
-			// 240 and 256 columns per tile exceed the epilogue's register budget (their accumulators spill)
-			const int n_t_max		= static_cast<int>(std::min<int64_t>(224, ((col_rows + 15) / 16) * 16));
+			const int n_t_max		= static_cast<int>(std::min<int64_t>(256, ((col_rows + 15) / 16) * 16));
 			for (int n_t = 16; n_t <= n_t_max; n_t += 16) {
 				const int64_t col_tiles = (col_rows + n_t - 1) / n_t;
 				const int64_t tiles		= lane_tiles * col_tiles;
 				const int64_t waves		= (tiles + sms - 1) / sms;
-				// narrow tiles re-read the lane-side operand more often: a mild penalty keeps them for when they pay
-				const double cost = static_cast<double>(waves) * (n_t + 24.0) * (1.0 + 8.0 / n_t);
+				// measured: a tile's time per Q8 block is close to proportional to its width (0.32 us at 112 columns, 0.62 at
+				// 208 and 224) down to a floor of about 64 columns' worth, and 256 columns cost a little more per column
+				const double cost = static_cast<double>(waves) * (std::max(n_t, 64) + 8.0) * (n_t > 240 ? 1.08 : 1.0);
 				if (cost < best_cost - 1e-9) {
 					best_cost	   = cost;
 					best.swapped   = swapped;
@@ -850,7 +838,7 @@ namespace nhb {
 		}
 		cudaLaunchConfig_t lc{};
 		lc.gridDim			= dim3(plan.lane_tiles, plan.col_tiles);
-		lc.blockDim			= dim3(GM_THREADS);
+		lc.blockDim			= dim3((4 + gemm_epi_warps(plan.n_t)) * 32);
 		lc.dynamicSmemBytes = smem;
 		lc.stream			= cfg.stream;
 		lc.attrs			= attr;

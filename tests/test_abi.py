@@ -128,3 +128,21 @@ def test_placement_policy_replicates_small_weights_only(capi):
             assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
         assert capi.place_rows(n, k, 1, 0, thr) == (0, n)  # one rank: nothing to decide
         assert capi.place_rows(n, k, 8, 3, 0) == capi.shard_rows(n, 8, 3)  # policy off
+
+
+def test_gemm_tile_plan_covers_the_output_and_fills_waves(capi):
+    for rows in (1, 100, 1024, 4096, 14336, 128256):
+        for M in (9, 16, 64, 127, 128, 130, 512, 2048):
+            p = capi.gemm_tile_plan(rows, M)
+            lanes, cols = (M, rows) if p["swapped"] else (rows, M)
+            assert p["tile_cols"] % 16 == 0 and 16 <= p["tile_cols"] <= 256
+            assert p["lane_tiles"] * 128 >= lanes and (p["lane_tiles"] - 1) * 128 < lanes
+            assert p["col_tiles"] * p["tile_cols"] >= cols and (p["col_tiles"] - 1) * p["tile_cols"] < cols
+    # few tokens: weight rows on the lanes, the tokens (rounded up to 16) on the columns
+    p = capi.gemm_tile_plan(14336, 16)
+    assert not p["swapped"] and p["tile_cols"] == 16
+    # the configs of the prefill benchmark: tokens on the lanes, tile width chosen for whole waves of 148 SMs
+    p = capi.gemm_tile_plan(4096, 512)
+    assert p["swapped"] and p["lane_tiles"] * p["col_tiles"] == 148
+    p = capi.gemm_tile_plan(14336, 512)
+    assert p["swapped"] and 0.9 <= p["lane_tiles"] * p["col_tiles"] / (2 * 148) <= 1.0
