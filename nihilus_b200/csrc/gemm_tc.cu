@@ -36,15 +36,14 @@ namespace nhb {
 
 		constexpr int GM_ROWS	 = 128;// weight rows per CTA = MMA M
 		constexpr int GM_KSLICE	 = 64;// fp16 elements per smem stage row = 128 bytes = two Q8 blocks
-		// Epilogue warps: 4 TMEM lane quarters x 3 or 4 column groups.  Wide tiles (>= 144 columns) run 12 warps with 160
-		// registers each -- more columns per warp amortise the fixed cost a warp pays per Q8 block (measured: 512 x 14336
-		// rows 179 -> 159 us, 2048 tokens 646 -> 551 us) -- narrower ones 16 warps with 112 (112-column tiles: 151 us
-		// against 165 with 12 warps).  32-column TMEM loads were slower than 16-column ones in both shapes.
-#ifndef NHB_GEMM_WIDEST_WARPS
-#define NHB_GEMM_WIDEST_WARPS 12
-#endif
+		// Epilogue warps: 4 TMEM lane quarters x 2, 3 or 4 column groups.  A warp pays a fixed cost per Q8 block (waits,
+		// fences, scale fetches), so wide tiles do better with fewer, fatter warps -- as long as enough warps remain to
+		// cover each other's TMEM round trips.  Measured (us, 12 against 16 warps): 512 tokens x 14336 rows 159 / 179,
+		// 2048 x 14336 551 / 646, but 112-column tiles 165 / 151.  Eight warps with 232 registers: 208-column tiles
+		// 143 against 159 with twelve (512 x 128256: 1203 / 1349), 224-column tiles 559 / 552.  32-column TMEM loads were
+		// slower than 16-column ones in every shape.
 		__host__ __device__ constexpr int gemm_epi_warps(int n_t) {
-			return n_t >= 208 ? NHB_GEMM_WIDEST_WARPS : (n_t >= 144 ? 12 : 16);
+			return n_t >= 224 ? 12 : (n_t >= 208 ? 8 : (n_t >= 144 ? 12 : 16));
 		}
 		constexpr int GM_LDU = 2;// 8-column units fetched per TMEM load
 
