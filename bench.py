@@ -190,6 +190,69 @@ def prefill_run(ctx, stream, torch, ops, weights, timed, world, M=512, iters=10)
             "per_op": out, "note": "outside the timed decode region; weights of one layer (187 MB) exceed L2"}
 
 
+def norm_run(ctx, stream, torch, ops, weights, timed, iters=20):
+    """rms_norm x norm-weight, the producer of the q/k/v and gate/up activations (K = 4096): the kernel alone at 1 and
+    512 rows, and one decode stage (norm -> q, k, v) as two calls against the fused call, rotating over the layers so
+    the weights come from HBM when the rotation exceeds L2.  Every variant is captured into a CUDA graph first, like
+    the decode step itself, so the figures are device time and not the host's launch rate."""
+    K = shapes.LLAMA3_8B["attn_q"][1]
+    by_layer = {}
+    for i, (name, layer, n, k) in enumerate(ops):
+        if name in ("attn_q", "attn_k", "attn_v"):
+            by_layer.setdefault(layer, []).append((weights[i], n))
+    layers = [v for _, v in sorted(by_layer.items()) if len(v) == 3][:8]
+    hbm_peak, _, kind = measured_peaks()
+    out = {"K": K, "eps": 1e-5, "sqrt_mode": "ieee"}
+
+    def graph_us(fn, calls_per_fn):
+        fn()  # first call outside the capture: scratch buffers are allocated here
+        ctx.sync()
+        ctx.graph_begin()
+        fn()
+        g = ctx.graph_end()
+        for _ in range(3):
+            g.launch()
+        ctx.sync()
+        ms = timed(g.launch, iters) / iters
+        g.free()
+        return ms * 1e3 / calls_per_fn
+
+    with torch.cuda.stream(stream):
+        nw = torch.rand(K, device="cuda") + 0.5
+        for M in (1, 512):
+            reps = 16
+            xs = [torch.randn((M, K), device="cuda") for _ in range(reps)]
+            y = torch.empty((M, K), device="cuda")
+            us = graph_us(lambda: [ctx.rms_norm_mul(x, nw, 1e-5, y=y) for x in xs], reps)
+            nbytes = 2 * M * K * 4 + K * 4
+            out["rows_%d" % M] = {"us": us, "gbs": nbytes / (us * 1e-6) / 1e9, "frac_of_hbm_peak": nbytes / (us * 1e-6) / 1e9 / hbm_peak}
+        if layers:
+            x = torch.randn((1, K), device="cuda")
+            ys = [[torch.zeros((1, n), device="cuda") for _, n in lw] for lw in layers]
+            normed = torch.empty((1, K), device="cuda")
+
+            def two_calls():
+                for lw, ly in zip(layers, ys):
+                    ctx.rms_norm_mul(x, nw, 1e-5, y=normed)
+                    ctx.mul_mat_batch([(w, normed, yy) for (w, _), yy in zip(lw, ly)])
+
+            def fused():
+                for lw, ly in zip(layers, ys):
+                    ctx.rms_norm_mul_mat_batch([(w, x, yy) for (w, _), yy in zip(lw, ly)], nw, 1e-5)
+
+            def plain():
+                for lw, ly in zip(layers, ys):
+                    ctx.mul_mat_batch([(w, x, yy) for (w, _), yy in zip(lw, ly)])
+
+            for name, fn in (("qkv_without_norm_us", plain), ("norm_then_qkv_two_calls_us", two_calls), ("norm_qkv_fused_us", fused)):
+                out[name] = graph_us(fn, len(layers))
+            out["stage_layers_in_rotation"] = len(layers)
+    out["peak_kind"] = kind
+    out["note"] = ("CUDA-graph replays; rows_1 and rows_512 are back-to-back launches of the kernel alone; the sum-of-squares chain is "
+                   "K/8 = 512 dependent fma steps per row by the reference's definition")
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -207,7 +270,7 @@ def main():
                     help="N > 1: outputs completed by the GEMV's own peer stores (fused) or by a grouped NCCL all-gather per stage")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the 512-token GEMM figures that ride along in the JSON line")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 512-token GEMM and the rms_norm figures that ride along in the JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -366,6 +429,11 @@ def main():
     if not args.no_prefill:
         prefill = prefill_run(ctx, stream, torch, ops, weights, timed, world)
 
+    # ---- rms_norm x norm-weight, the producer of the decode activations (1 GPU: it does not shard) ----
+    norm = None
+    if not args.no_prefill and world == 1 and args.act_mode == "q8":
+        norm = norm_run(ctx, stream, torch, ops, weights, timed)
+
     # spot parity check of the timed buffers against nothing but themselves being finite (full parity lives in tests/)
     ctx.sync()
     finite = bool(torch.isfinite(y_dev).all().item())
@@ -400,6 +468,7 @@ def main():
                 "note": "per GPU; launch gaps inside the graph are included in the duration",
             },
             "prefill": prefill,
+            "rms_norm": norm,
             "outputs_finite": finite,
             "setup_s": {"generate": gen_s, "upload": upload_s},
         }

@@ -152,6 +152,27 @@ int nhb_mul_mat_block_dots(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev
  * (the fp16-rounded d, widened) [M][K/32] */
 int nhb_quantize_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, int64_t M, int64_t K, int8_t* q_dev, float* d_dev);
 
+/* ---- rms_norm x norm-weight: the producer of a projection's activations ----
+ * Replaces the reference's rms_norm_mul kernel (cpu/avx_2.hpp:3875-3950) and its helpers simd_sum_squares
+ * (:758-779), vec_scale_mul_f32 (:3621-3850) and quantize_row_q8_0_avx2 (:671-721), bit for bit:
+ *   scale = 1 / sqrtf_fast(sum_squares(x) / K + eps),  y = (x * norm_w) * scale.
+ * sqrt_mode picks which of the reference's two sqrtf_fast builds is reproduced: */
+#define NHB_SQRT_IEEE 0     /* the IEEE square root (the NEON build, cpu/common.hpp:310-312) */
+#define NHB_SQRT_X86_FAST 1 /* the x86 build's integer formula (cpu/common.hpp:448-450); as written it returns about
+                               2^64 * sqrt(x), so every output carries a factor of about 2^-64 */
+/* x [M][ldx] -> y [M][ldy], f32, device pointers 16-byte aligned, ldx and ldy multiples of 4, K % 32 == 0, K <= 51200 */
+int nhb_rms_norm_mul(nhb_ctx* ctx, const float* x_dev, int64_t ldx, const float* norm_w_dev, float eps, int sqrt_mode, float* y_dev,
+	int64_t ldy, int64_t M, int64_t K);
+/* the same rows quantised with quantize_row_q8_0: 34-byte Q8_0 blocks [M][K/32] in device memory */
+int nhb_rms_norm_mul_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, const float* norm_w_dev, float eps, int sqrt_mode,
+	void* blocks_dev, int64_t M, int64_t K);
+/* rms_norm x norm-weight feeding a batch of Q8-arithmetic mul_mats (q/k/v, or gate/up): ops[i].x is the row BEFORE the
+ * norm and must be the same pointer, ldx and K in every op.  Results are bit-identical to nhb_rms_norm_mul followed by
+ * nhb_mul_mat_batch(NHB_ACT_Q8).  For decode (the warp-per-row GEMV) the norm kernel writes the quantised row once
+ * and the GEMV stages it as is; for larger M the normalised rows go through a scratch buffer of the context. */
+int nhb_rms_norm_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, const float* norm_w_dev, float eps, int sqrt_mode,
+	int kernel);
+
 /* ---- for callers that cannot allocate ---- */
 /* No counterpart in the reference.  The decode GEMV (Q8 arithmetic, M <= 4) without a context, a weight handle or
  * any allocation: the caller passes the two device planes of a weight (as nhb_weight_info_get returns them, or as

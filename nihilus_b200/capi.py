@@ -23,6 +23,7 @@ if not os.path.exists(LIB_PATH):
 lib = C.CDLL(LIB_PATH)
 
 ACT_Q8, ACT_F32 = 0, 1
+SQRT_IEEE, SQRT_X86_FAST = 0, 1
 KERNEL_AUTO, KERNEL_GEMV_LDG, KERNEL_GEMV_STREAM, KERNEL_GEMM_TC, KERNEL_GEMV_ROWS = 0, 1, 2, 3, 4
 OK, ERR_ARG, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NOMEM = 0, -1, -2, -3, -4, -5, -6
 
@@ -35,6 +36,7 @@ EXPORTS = (
     "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
     "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_place_rows", "nhb_gemm_tile_plan",
+    "nhb_rms_norm_mul", "nhb_rms_norm_mul_q8_0", "nhb_rms_norm_mul_mat_batch",
 )
 
 
@@ -56,6 +58,9 @@ def _sig(name, restype, *argtypes):
 
 _vp, _i, _i64 = C.c_void_p, C.c_int, C.c_int64
 _sig("nhb_version", _i)
+_sig("nhb_rms_norm_mul", _i, _vp, _vp, _i64, _vp, C.c_float, _i, _vp, _i64, _i64, _i64)
+_sig("nhb_rms_norm_mul_q8_0", _i, _vp, _vp, _i64, _vp, C.c_float, _i, _vp, _i64, _i64)
+_sig("nhb_rms_norm_mul_mat_batch", _i, _vp, C.POINTER(MulMatOp), _i, _vp, C.c_float, _i, _i)
 _sig("nhb_arch", _i)
 _sig("nhb_last_error", C.c_char_p, _vp)
 _sig("nhb_shard_rows", _i, _i64, _i, _i, C.POINTER(_i64), C.POINTER(_i64))
@@ -297,6 +302,34 @@ class Context:
         d = torch.empty((M, K // 32), dtype=torch.float32, device=x.device)
         _check(lib.nhb_quantize_q8_0(self.handle, x.data_ptr(), x.stride(0), M, K, q.data_ptr(), d.data_ptr()), self.handle)
         return q, d
+
+    # ---- rms_norm x norm-weight ----
+    def rms_norm_mul(self, x, norm_w, eps: float, sqrt_mode: int = SQRT_IEEE, y=None):
+        import torch
+
+        M, K = x.shape
+        if y is None:
+            y = torch.empty((M, K), dtype=torch.float32, device=x.device)
+        _check(lib.nhb_rms_norm_mul(self.handle, x.data_ptr(), x.stride(0) if M > 0 else K, norm_w.data_ptr(), eps, sqrt_mode, y.data_ptr(),
+                                    y.stride(0) if M > 0 else K, M, K), self.handle)
+        return y
+
+    def rms_norm_mul_q8_0(self, x, norm_w, eps: float, sqrt_mode: int = SQRT_IEEE):
+        """Returns the rows as 34-byte Q8_0 blocks: uint8 [M][K/32][34]."""
+        import torch
+
+        M, K = x.shape
+        out = torch.empty((M, K // 32, 34), dtype=torch.uint8, device=x.device)
+        _check(lib.nhb_rms_norm_mul_q8_0(self.handle, x.data_ptr(), x.stride(0) if M > 0 else K, norm_w.data_ptr(), eps, sqrt_mode,
+                                         out.data_ptr(), M, K), self.handle)
+        return out
+
+    def rms_norm_mul_mat_batch(self, ops, norm_w, eps: float, sqrt_mode: int = SQRT_IEEE, kernel: int = KERNEL_AUTO):
+        """ops: list of (Weight, x, y); x is the row before the norm, the same tensor in every op."""
+        arr = (MulMatOp * len(ops))()
+        for i, (w, x, y) in enumerate(ops):
+            arr[i] = MulMatOp(w.handle, x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.shape[0])
+        _check(lib.nhb_rms_norm_mul_mat_batch(self.handle, arr, len(ops), norm_w.data_ptr(), eps, sqrt_mode, kernel), self.handle)
 
     def memcpy_h2d(self, dst_ptr: int, src_ptr: int, nbytes: int):
         _check(lib.nhb_memcpy_h2d(self.handle, dst_ptr, src_ptr, nbytes), self.handle)

@@ -91,6 +91,12 @@ struct nhb_ctx {
 	int ctas_per_sm	   = 1;// streaming GEMV: persistent CTAs per SM
 	int rows_cps	   = 3;// warp-per-row GEMV: grid cap in CTAs per SM
 	int preq		   = 0;// warp-per-row GEMV: quantise activations in a separate kernel
+	// set only while nhb_rms_norm_mul_mat_batch runs: the GEMV's activations come from the norm kernel, already quantised
+	const float* norm_w = nullptr;
+	float norm_eps		= 0.f;
+	int norm_sqrt		= 0;
+	void* norm_buf		= nullptr;// normalised f32 rows for the paths that quantise for themselves
+	size_t norm_cap		= 0;
 	int rows_db		   = 0;// warp-per-row GEMV: two items in flight per warp
 	int rows_cluster   = 1;// warp-per-row GEMV: CTAs per cluster sharing the activation quantisation
 	int rows_fat	   = 1;// warp-per-row GEMV: one 24-warp CTA per SM for launches with enough rows
@@ -402,7 +408,18 @@ namespace {
 						break;
 					b.act_bytes = static_cast<int>(off);
 					b.f32act	= f32act ? 1 : 0;
-					if (ctx->preq && !f32act) {
+					// rms_norm in front of the quantiser: inside the GEMV when its rows fit the shared memory, else its own kernel
+					int rows_total = 0;
+					for (int i = 0; i < b.n_ops; ++i)
+						rows_total += b.op[i].rows;
+					const bool norm_inside = ctx->norm_w && !f32act && !ctx->rows_db && b.n_ops > 0 &&
+						gemv_rows_norm_inside(rows_total, off, b.op[0].K, mt, cfg.sm_count, ctx->rows_fat != 0);
+					if (norm_inside) {
+						b.norm_w	= ctx->norm_w;
+						b.norm_eps	= ctx->norm_eps;
+						b.norm_sqrt = ctx->norm_sqrt;
+					}
+					if ((ctx->preq || ctx->norm_w) && !f32act && !norm_inside) {
 						int rc = ensure(ctx, &ctx->scratch, &ctx->scratch_cap, off, "activation scratch");
 						if (rc != NHB_OK)
 							return rc;
@@ -412,9 +429,15 @@ namespace {
 							const rows_op& so = b.op[b.slot_op[s]];
 							int8_t* q		  = static_cast<int8_t*>(ctx->scratch) + so.preq_off;
 							float* d		  = reinterpret_cast<float*>(q + static_cast<size_t>(mt) * so.K);
-							cudaError_t e	  = launch_quantize(so.x, so.ldx, mt, so.K, q, d, ctx->stream, ctx->pdl);
+							cudaError_t e;
+							if (ctx->norm_w) {
+								const norm_out no{ nullptr, 0, q, d, nullptr };
+								e = launch_rms_norm(so.x, so.ldx, ctx->norm_w, ctx->norm_eps, ctx->norm_sqrt, mt, so.K, no, ctx->stream, ctx->pdl);
+							} else {
+								e = launch_quantize(so.x, so.ldx, mt, so.K, q, d, ctx->stream, ctx->pdl);
+							}
 							if (e != cudaSuccess)
-								return fail_cuda(ctx, e, "quantize_q8 launch");
+								return fail_cuda(ctx, e, "activation quantise launch");
 							++launches;
 						}
 					}
@@ -434,6 +457,8 @@ namespace {
 				ctx->launches += launches;
 				return NHB_OK;
 			}
+			if (ctx->norm_w)
+				return fail(ctx, NHB_ERR_UNSUPPORTED, "fused rms_norm needs the warp-per-row GEMV");
 			if (kernel == NHB_KERNEL_GEMV_ROWS && ctx->gemv_default != NHB_KERNEL_GEMV_ROWS)
 				return fail(ctx, NHB_ERR_UNSUPPORTED, "K too large for the warp-per-row GEMV's shared memory");
 			kernel = NHB_KERNEL_GEMV_LDG;
@@ -707,6 +732,8 @@ int nhb_ctx_destroy(nhb_ctx* ctx) {
 		cudaFree(ctx->push_local);
 	if (ctx->scratch)
 		cudaFree(ctx->scratch);
+	if (ctx->norm_buf)
+		cudaFree(ctx->norm_buf);
 	if (ctx->io)
 		cudaFree(ctx->io);
 	if (ctx->dev_status)
@@ -1070,6 +1097,109 @@ int nhb_quantize_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, int64_t M, 
 		return fail_cuda(ctx, e, "quantize_q8 launch");
 	ctx->launches += 1;
 	return NHB_OK;
+}
+
+namespace {
+	int check_norm_args(nhb_ctx* ctx, const float* x, int64_t ldx, const float* w, int sqrt_mode, int64_t M, int64_t K, const char* who) {
+		if (!ctx || M < 0 || K <= 0 || K % 32 != 0 || ldx < K || (sqrt_mode != NHB_SQRT_IEEE && sqrt_mode != NHB_SQRT_X86_FAST))
+			return fail(ctx, NHB_ERR_ARG, std::string(who) + ": bad arguments");
+		if (!rms_norm_supports(K))
+			return fail(ctx, NHB_ERR_UNSUPPORTED, std::string(who) + ": K too large for one CTA's shared memory (K <= 51200)");
+		if (M > 0 && (!x || !w || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (ldx & 3)))
+			return fail(ctx, NHB_ERR_ARG, std::string(who) + ": null or misaligned pointer");
+		if (M > INT32_MAX)
+			return fail(ctx, NHB_ERR_ARG, std::string(who) + ": M too large");
+		return NHB_OK;
+	}
+}
+
+int nhb_rms_norm_mul(nhb_ctx* ctx, const float* x_dev, int64_t ldx, const float* norm_w_dev, float eps, int sqrt_mode, float* y_dev, int64_t ldy,
+	int64_t M, int64_t K) {
+	int rc = check_norm_args(ctx, x_dev, ldx, norm_w_dev, sqrt_mode, M, K, "nhb_rms_norm_mul");
+	if (rc != NHB_OK)
+		return rc;
+	if (M == 0)
+		return NHB_OK;
+	if (!y_dev || (reinterpret_cast<uintptr_t>(y_dev) & 15) || (ldy & 3) || ldy < K)
+		return fail(ctx, NHB_ERR_ARG, "nhb_rms_norm_mul: null or misaligned output");
+	device_guard g(ctx->device);
+	const norm_out no{ y_dev, ldy, nullptr, nullptr, nullptr };
+	cudaError_t e = launch_rms_norm(x_dev, ldx, norm_w_dev, eps, sqrt_mode, static_cast<int>(M), static_cast<int>(K), no, ctx->stream, ctx->pdl);
+	if (e != cudaSuccess)
+		return fail_cuda(ctx, e, "rms_norm_mul launch");
+	ctx->launches += 1;
+	return NHB_OK;
+}
+
+int nhb_rms_norm_mul_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, const float* norm_w_dev, float eps, int sqrt_mode, void* blocks_dev, int64_t M,
+	int64_t K) {
+	int rc = check_norm_args(ctx, x_dev, ldx, norm_w_dev, sqrt_mode, M, K, "nhb_rms_norm_mul_q8_0");
+	if (rc != NHB_OK)
+		return rc;
+	if (M == 0)
+		return NHB_OK;
+	if (!blocks_dev || (reinterpret_cast<uintptr_t>(blocks_dev) & 1))
+		return fail(ctx, NHB_ERR_ARG, "nhb_rms_norm_mul_q8_0: null or odd output address");
+	device_guard g(ctx->device);
+	const norm_out no{ nullptr, 0, nullptr, nullptr, static_cast<unsigned char*>(blocks_dev) };
+	cudaError_t e = launch_rms_norm(x_dev, ldx, norm_w_dev, eps, sqrt_mode, static_cast<int>(M), static_cast<int>(K), no, ctx->stream, ctx->pdl);
+	if (e != cudaSuccess)
+		return fail_cuda(ctx, e, "rms_norm_mul_q8_0 launch");
+	ctx->launches += 1;
+	return NHB_OK;
+}
+
+int nhb_rms_norm_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, const float* norm_w_dev, float eps, int sqrt_mode, int kernel) {
+	if (!ctx || (n_ops > 0 && !ops) || n_ops < 0 || n_ops > NHB_MAX_BATCH)
+		return fail(ctx, NHB_ERR_ARG, "nhb_rms_norm_mul_mat_batch: bad batch (at most 8 ops)");
+	if (kernel < NHB_KERNEL_AUTO || kernel > NHB_KERNEL_GEMV_ROWS)
+		return fail(ctx, NHB_ERR_ARG, "unknown kernel id");
+	if (n_ops == 0)
+		return NHB_OK;
+	for (int i = 0; i < n_ops; ++i) {
+		int rc = check_mm_args(ctx, ops[i].w, ops[i].x, ops[i].ldx, ops[i].y, ops[i].ldy, ops[i].M);
+		if (rc != NHB_OK)
+			return rc;
+		if (ops[i].x != ops[0].x || ops[i].ldx != ops[0].ldx || ops[i].M != ops[0].M || ops[i].w->K != ops[0].w->K)
+			return fail(ctx, NHB_ERR_ARG, "nhb_rms_norm_mul_mat_batch: every op must read the same rows (x, ldx, M, K)");
+	}
+	const int64_t M = ops[0].M, K = ops[0].w->K;
+	int rc = check_norm_args(ctx, ops[0].x, ops[0].ldx, norm_w_dev, sqrt_mode, M, K, "nhb_rms_norm_mul_mat_batch");
+	if (rc != NHB_OK)
+		return rc;
+	if (M == 0)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	// decode: the norm kernel hands the GEMV its quantised rows directly
+	int resolved = kernel;
+	if (resolved == NHB_KERNEL_AUTO) {
+		const int forced = env_int("NHB_FORCE_KERNEL", 0);
+		resolved		 = forced >= 1 && forced <= 4 ? forced : (M > ctx->gemv_max_m ? NHB_KERNEL_GEMM_TC : ctx->gemv_default);
+	}
+	if (resolved == NHB_KERNEL_GEMV_ROWS && gemv_rows_supports(K, 1) && gemv_rows_act_bytes(K, 1) <= 96 * 1024) {
+		ctx->norm_w	   = norm_w_dev;
+		ctx->norm_eps  = eps;
+		ctx->norm_sqrt = sqrt_mode;
+		rc			   = nhb_mul_mat_batch(ctx, ops, n_ops, NHB_ACT_Q8, NHB_KERNEL_GEMV_ROWS);
+		ctx->norm_w	   = nullptr;
+		return rc;
+	}
+	// everything else: normalised f32 rows through a scratch buffer, then the ordinary operator
+	rc = ensure(ctx, &ctx->norm_buf, &ctx->norm_cap, static_cast<size_t>(M) * K * 4, "rms_norm scratch");
+	if (rc != NHB_OK)
+		return rc;
+	const norm_out no{ static_cast<float*>(ctx->norm_buf), K, nullptr, nullptr, nullptr };
+	cudaError_t e = launch_rms_norm(ops[0].x, ops[0].ldx, norm_w_dev, eps, sqrt_mode, static_cast<int>(M), static_cast<int>(K), no, ctx->stream, ctx->pdl);
+	if (e != cudaSuccess)
+		return fail_cuda(ctx, e, "rms_norm_mul launch");
+	ctx->launches += 1;
+	nhb_mul_mat_op normed[NHB_MAX_BATCH];
+	for (int i = 0; i < n_ops; ++i) {
+		normed[i]	  = ops[i];
+		normed[i].x	  = static_cast<const float*>(ctx->norm_buf);
+		normed[i].ldx = K;
+	}
+	return nhb_mul_mat_batch(ctx, normed, n_ops, NHB_ACT_Q8, kernel);
 }
 
 int nhb_mul_mat_block_dots(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev, int64_t ldx, int64_t M, int32_t* dots_dev) {

@@ -82,6 +82,19 @@ namespace nhb {
 		// Activations of one input in shared memory, per row m: the first 16 bytes of every block (uint4 [nb]), then the
 		// second 16 bytes (uint4 [nb]) -- two planes, so that a warp reading one block per lane touches consecutive
 		// 16-byte words (no bank conflicts) -- and after all MT rows the f32 scales [MT][nb].
+#ifdef NHB_ROWS_PROF
+		__device__ unsigned long long rows_prof[8];
+		__device__ __forceinline__ unsigned long long gtimer() {
+			unsigned long long t;
+			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+			return t;
+		}
+#define ROWS_STAMP(i) \
+	if (blockIdx.x == 0 && threadIdx.x == 0) \
+	rows_prof[i] = gtimer()
+#else
+#define ROWS_STAMP(i)
+#endif
 		template<int MT> __device__ __forceinline__ void compute_item(const item_regs& r, float (&acc)[MT], const unsigned char* act, int nb, int b0, int lane) {
 			const float* da = reinterpret_cast<const float*>(act + static_cast<size_t>(MT) * nb * QK);
 #pragma unroll
@@ -149,7 +162,7 @@ namespace nhb {
 		}
 
 		// Prologue of both GEMV variants: quantise every distinct input of the batch into shared memory.
-		template<int MT> __device__ __forceinline__ void quantize_inputs(const rows_batch& b, unsigned char* act_smem, int tid) {
+		template<int MT, bool NORM = false> __device__ __forceinline__ void quantize_inputs(const rows_batch& b, unsigned char* act_smem, int tid) {
 		const uint32_t cn = cluster_size();
 		const uint32_t cr = cluster_rank();
 		for (int s = 0; s < b.n_slots; ++s) {
@@ -158,6 +171,67 @@ namespace nhb {
 			const int K		   = op->K;
 			const int nb	   = K >> 5;
 			float* sda		   = reinterpret_cast<float*>(act + static_cast<size_t>(MT) * K);
+			if constexpr (NORM) {
+				// rms_norm x norm-weight in front of the quantiser (rms_norm.cu has the arithmetic and its source):
+				// the rows are staged as f32, eight lanes per row run the sum-of-squares chains -- K / 8 dependent fma
+				// steps, which overlap the weight loads this CTA issued before it waited for the previous kernel -- and
+				// the quantiser below then reads (x * w) * scale instead of x.  Every CTA does this for itself: the
+				// rows are a few KB out of L2 and a separate kernel would put its launch on the critical path.
+				const int KS   = K + 8;// row stride: the MT chains of a step hit different banks
+				float* rows	   = reinterpret_cast<float*>(act_smem + b.norm_off);
+				float* prod	   = rows + MT * KS;// x * w, formed while the row is staged, so nothing is fetched after the chains
+				float* s_scale = prod + MT * KS;
+				const int k4   = K >> 2;
+				for (int i = tid; i < MT * k4; i += static_cast<int>(blockDim.x)) {
+					const int m		= i / k4;
+					const int j		= i - m * k4;
+					const float4 xv = __ldg(reinterpret_cast<const float4*>(op->x + static_cast<size_t>(m) * op->ldx) + j);
+					const float4 wv = __ldg(reinterpret_cast<const float4*>(b.norm_w) + j);
+					reinterpret_cast<float4*>(rows + m * KS)[j] = xv;
+					reinterpret_cast<float4*>(prod + m * KS)[j] =
+						make_float4(__fmul_rn(xv.x, wv.x), __fmul_rn(xv.y, wv.y), __fmul_rn(xv.z, wv.z), __fmul_rn(xv.w, wv.w));
+				}
+				__syncthreads();
+				ROWS_STAMP(2);
+				if (tid < 8 * MT) {
+					constexpr unsigned mask = MT >= 4 ? 0xffffffffu : ((1u << (8 * MT)) - 1u);
+					const float acc			= sum_squares_lane(rows + (tid >> 3) * KS + (tid & 7), K >> 3);
+					const float quad = __fadd_rn(acc, __shfl_down_sync(mask, acc, 4, 8));
+					const float dual = __fadd_rn(quad, __shfl_down_sync(mask, quad, 2, 8));
+					const float sum	 = __fadd_rn(dual, __shfl_down_sync(mask, dual, 1, 8));
+					if ((tid & 7) == 0) {
+						const float v = __fadd_rn(__fdiv_rn(sum, static_cast<float>(K)), b.norm_eps);
+						const float root =
+							b.norm_sqrt == NHB_SQRT_X86_FAST ? __uint_as_float(((__float_as_uint(v) + 0x3f800000u) >> 1) + 0x20000000u) : __fsqrt_rn(v);
+						s_scale[tid >> 3] = __fdiv_rn(1.0f, root);
+					}
+				}
+				ROWS_STAMP(3);
+				__syncthreads();
+				const int n = MT * nb * 2;// quantiser work items: half a block (16 values) each
+				for (int i = tid; i < n; i += static_cast<int>(blockDim.x)) {
+					const int hb	 = i >> 1;
+					const int m		 = hb / nb;
+					const int blk	 = hb - m * nb;
+					const float sc_n = s_scale[m];
+					const float4* p	 = reinterpret_cast<const float4*>(prod + m * KS + blk * QK) + (i & 1) * 4;
+					float4 v[4];
+#pragma unroll
+					for (int j = 0; j < 4; ++j) {
+						const float4 t = p[j];
+						v[j]		   = make_float4(__fmul_rn(t.x, sc_n), __fmul_rn(t.y, sc_n), __fmul_rn(t.z, sc_n), __fmul_rn(t.w, sc_n));
+					}
+					float amax		   = absmax4(v[0], absmax4(v[1], absmax4(v[2], absmax4(v[3], 0.f))));
+					amax			   = fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
+					const act_scale sc = q8_scales(amax);
+					reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] =
+						make_uint4(q8_pack4(v[0].x, v[0].y, v[0].z, v[0].w, sc.id), q8_pack4(v[1].x, v[1].y, v[1].z, v[1].w, sc.id),
+							q8_pack4(v[2].x, v[2].y, v[2].z, v[2].w, sc.id), q8_pack4(v[3].x, v[3].y, v[3].z, v[3].w, sc.id));
+					if ((i & 1) == 0)
+						sda[hb] = sc.d;
+				}
+				__syncthreads();// the staged rows are reused by the next slot
+			} else
 			if (b.preq) {
 				// quantised by quantize_q8_kernel into global scratch: int8 [MT][K] then f32 [MT][nb]
 				const unsigned char* src = b.preq_base + op->preq_off;
@@ -265,7 +339,10 @@ namespace nhb {
 				atomicExch(pc.status, DEV_TIMEOUT_PEER);
 		}
 
-		template<int MT, int OCC, int TPB = ROWS_TPB, bool F32 = false> __global__ void __launch_bounds__(TPB, OCC) gemv_q8_rows(const __grid_constant__ rows_batch b) {
+		// NORM: the rms_norm x norm-weight producer runs inside the prologue (its own instantiation, so that the plain
+		// kernels keep their register allocation)
+		template<int MT, int OCC, int TPB = ROWS_TPB, bool F32 = false, bool NORM = false> __global__ void __launch_bounds__(TPB, OCC)
+			gemv_q8_rows(const __grid_constant__ rows_batch b) {
 			constexpr int WARPS = TPB / 32;
 			extern __shared__ __align__(128) unsigned char act_smem[];
 			const int tid		 = threadIdx.x;
@@ -284,12 +361,15 @@ namespace nhb {
 				load_item(regs, make_row(&b.op[cur], row0 - b.op[cur].row_begin), 0, lane);
 				pre = true;
 			}
+			ROWS_STAMP(0);
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
+			ROWS_STAMP(1);
 			if constexpr (F32)
 				stage_inputs_f32<MT>(b, act_smem, tid);
 			else
-				quantize_inputs<MT>(b, act_smem, tid);
+				quantize_inputs<MT, NORM>(b, act_smem, tid);
+			ROWS_STAMP(4);
 			// ---- rows ----
 			for (int row = row0; row < total_rows; row += W) {
 				while (cur + 1 < n_ops && row >= b.op[cur + 1].row_begin)
@@ -329,6 +409,7 @@ namespace nhb {
 						yrow[static_cast<size_t>(m) * ldy] = rowacc[m];
 				}
 			}
+			ROWS_STAMP(5);
 			if (b.push.world > 1) {
 				// Fused all-gather.  In pass i the warps of this CTA finished WARPS consecutive rows; once they are all
 				// written (CTA barrier) one warp per pass copies that run to every other rank in one coalesced store per
@@ -558,6 +639,21 @@ namespace nhb {
 		return static_cast<size_t>((M * per_row + 127) & ~int64_t(127));
 	}
 
+	// dynamic shared memory a launch with the in-kernel rms_norm may ask for: one CTA per SM, or two
+	size_t gemv_rows_norm_smem_cap(bool fat) {
+		return fat ? 200 * 1024 : 100 * 1024;
+	}
+
+	// whether a launch of `total_rows` rows can run the rms_norm in its prologue (else the caller uses rms_norm.cu's kernel)
+	bool gemv_rows_norm_inside(int total_rows, size_t act_bytes, int64_t K, int M, int sm_count, bool fat_ctas) {
+		const bool fat = fat_ctas && total_rows >= sm_count * ROWS_WARPS_FAT;
+		return ((act_bytes + 127) & ~size_t(127)) + gemv_rows_norm_bytes(K, M) <= gemv_rows_norm_smem_cap(fat);
+	}
+
+	size_t gemv_rows_norm_bytes(int64_t K, int M) {
+		return 2 * static_cast<size_t>(M) * static_cast<size_t>(K + 8) * 4 + 128;// the staged rows and their products with the norm weight
+	}
+
 	bool gemv_rows_supports(int64_t K, int64_t M, bool f32act) {
 		return K % 32 == 0 && M >= 1 && M <= 4 && gemv_rows_act_bytes(K, static_cast<int>(M), f32act) <= 96 * 1024;
 	}
@@ -582,6 +678,14 @@ namespace nhb {
 			cluster		  = 1;
 			ctas_per_sm	  = 2;
 		}
+		if (b.norm_w) {// the in-kernel rms_norm: two shapes only (24-warp CTAs, or 8-warp CTAs at two per SM), this CTA's shared memory only
+			if (b.f32act)
+				return cudaErrorInvalidValue;
+			double_buffer	= false;
+			cluster			= 1;
+			split_long_rows = false;
+			ctas_per_sm		= 2;
+		}
 		const bool fat	= fat_ctas && !double_buffer && cluster <= 1 && rows >= cfg.sm_count * ROWS_WARPS_FAT;
 		const int warps = fat ? ROWS_WARPS_FAT : ROWS_WARPS;
 		if (fat)
@@ -601,8 +705,12 @@ namespace nhb {
 			split = b.op[i].K == b.op[0].K;
 		if (split)
 			grid = cfg.sm_count;
-		const size_t smem = static_cast<size_t>(b.act_bytes);
-		cudaError_t e	  = cudaErrorInvalidValue;
+		if (b.norm_w)
+			b.norm_off = (b.act_bytes + 127) & ~127;
+		const size_t smem = b.norm_w ? static_cast<size_t>(b.norm_off) + gemv_rows_norm_bytes(b.op[0].K, M) : static_cast<size_t>(b.act_bytes);
+		if (smem > (b.norm_w ? gemv_rows_norm_smem_cap(fat) : 100 * 1024))
+			return cudaErrorInvalidValue;
+		cudaError_t e = cudaErrorInvalidValue;
 		cudaLaunchConfig_t lc{};
 		lc.gridDim			= dim3(grid);
 		lc.blockDim			= dim3(warps * 32);
@@ -629,6 +737,26 @@ namespace nhb {
 		lc.numAttrs = n_attr;
 		// registers per thread are capped by the occupancy the grid was sized for (2, 3 or 4 CTAs per SM)
 		const int occ = double_buffer ? 0 : (ctas_per_sm >= 4 ? 4 : (ctas_per_sm == 3 ? 3 : 2));
+#define NHB_ROWS_NORM_CASE(MT) \
+	if (b.norm_w && M == MT) { \
+		e = cudaSuccess; \
+		if (fat) { \
+			auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT, false, true>; \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+			if (e == cudaSuccess) \
+				e = cudaLaunchKernelEx(&lc, kern, b); \
+		} else { \
+			auto kern = gemv_q8_rows<MT, 2, ROWS_TPB, false, true>; \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			if (e == cudaSuccess) \
+				e = cudaLaunchKernelEx(&lc, kern, b); \
+		} \
+	}
+		NHB_ROWS_NORM_CASE(1)
+		NHB_ROWS_NORM_CASE(2)
+		NHB_ROWS_NORM_CASE(3)
+		NHB_ROWS_NORM_CASE(4)
+#undef NHB_ROWS_NORM_CASE
 #define NHB_ROWS_F32_CASE(MT) \
 	if (b.f32act && M == MT) { \
 		e = cudaSuccess; \
@@ -655,7 +783,7 @@ namespace nhb {
 		NHB_ROWS_F32_CASE(4)
 #undef NHB_ROWS_F32_CASE
 #define NHB_ROWS_SPLIT_CASE(MT) \
-	if (!b.f32act && split && M == MT) { \
+	if (!b.f32act && !b.norm_w && split && M == MT) { \
 		auto kern = gemv_q8_rows_split<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 40 * 1024) \
@@ -669,7 +797,7 @@ namespace nhb {
 		NHB_ROWS_SPLIT_CASE(4)
 #undef NHB_ROWS_SPLIT_CASE
 #define NHB_ROWS_FAT_CASE(MT) \
-	if (!b.f32act && fat && !split && M == MT) { \
+	if (!b.f32act && !b.norm_w && fat && !split && M == MT) { \
 		auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
@@ -683,7 +811,7 @@ namespace nhb {
 		NHB_ROWS_FAT_CASE(4)
 #undef NHB_ROWS_FAT_CASE
 #define NHB_ROWS_CASE(MT, OCC) \
-	if (!b.f32act && !fat && M == MT && occ == OCC) { \
+	if (!b.f32act && !b.norm_w && !fat && M == MT && occ == OCC) { \
 		auto kern = gemv_q8_rows<MT, OCC>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
@@ -705,7 +833,7 @@ namespace nhb {
 		NHB_ROWS_CASE(4, 4)
 #undef NHB_ROWS_CASE
 #define NHB_ROWS_DB_CASE(MT) \
-	if (!b.f32act && double_buffer && M == MT) { \
+	if (!b.f32act && !b.norm_w && double_buffer && M == MT) { \
 		auto kern = gemv_q8_rows_db<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
@@ -724,3 +852,9 @@ namespace nhb {
 	}
 
 }
+
+#ifdef NHB_ROWS_PROF
+extern "C" int nhb_debug_rows_prof(unsigned long long* out8) {
+	return static_cast<int>(cudaMemcpyFromSymbol(out8, nhb::rows_prof, 64));
+}
+#endif

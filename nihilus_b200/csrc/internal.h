@@ -75,6 +75,12 @@ namespace nhb {
 		int preq;// 1: activations were quantised by a separate kernel into preq_base
 		int f32act;// 1: f32 activations x dequantised weights instead of the Q8 arithmetic
 		const unsigned char* preq_base;
+		// rms_norm x norm-weight inside the GEMV's prologue (null = off): every CTA normalises the rows for itself,
+		// staging them as f32 at byte offset norm_off of the dynamic shared memory
+		const float* norm_w;
+		float norm_eps;
+		int norm_sqrt;
+		int norm_off;
 		rows_op op[NHB_MAX_BATCH];
 		push_ctl push;
 		float* y_peer[NHB_MAX_BATCH][NHB_MAX_WORLD];// per op: the output on every rank, offset like rows_op::y
@@ -97,10 +103,25 @@ namespace nhb {
 
 	// gemv_rows.cu
 	size_t gemv_rows_act_bytes(int64_t K, int M, bool f32act = false);
+	size_t gemv_rows_norm_bytes(int64_t K, int M);// extra shared memory of the in-kernel rms_norm
+	size_t gemv_rows_norm_smem_cap(bool fat);
+	bool gemv_rows_norm_inside(int total_rows, size_t act_bytes, int64_t K, int M, int sm_count, bool fat_ctas);
 	bool gemv_rows_supports(int64_t K, int64_t M, bool f32act = false);
 	cudaError_t launch_gemv_rows(const rows_batch& b, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer = false, int cluster = 1,
 		bool fat_ctas = false, bool split_long_rows = false);
 	cudaError_t launch_block_dots(const int8_t* wq, const int8_t* qa, int rows, int K, int M, int32_t* dots, cudaStream_t s);
+
+	// rms_norm.cu: any subset of the three outputs (null = not wanted)
+	struct norm_out {
+		float* y;// [M][ldy] f32 rows
+		long long ldy;
+		int8_t* q;// [M][K] quants ...
+		float* d;// ... with [M][K/32] f32 scales (the layout the decode GEMV stages from)
+		unsigned char* blocks;// [M][K/32] 34-byte Q8_0 blocks
+	};
+	bool rms_norm_supports(long long K);
+	cudaError_t launch_rms_norm(const float* x, long long ldx, const float* w, float eps, int sqrt_mode, int M, int K, const norm_out& o, cudaStream_t s,
+		bool pdl = false);
 
 	// repack.cu
 	cudaError_t launch_repack(const uint8_t* blocks34, int64_t rows, int64_t K, int8_t* q, __half* d, cudaStream_t s);

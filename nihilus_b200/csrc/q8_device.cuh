@@ -37,6 +37,36 @@ namespace nhb {
 		return fmaxf(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))), m);
 	}
 
+	// One lane of the reference's simd_sum_squares (include/nihilus-incl/cpu/avx_2.hpp:758-779): acc = fma(v, v, acc) over
+	// r[0], r[8], r[16], ... (`steps` values), strictly in that order.  The fmas depend on each other (4 cycles a step
+	// at best), so the only thing to hide is the latency of the shared-memory loads: a 16-entry register window, each
+	// slot refilled for step s + 16 right after step s consumed it (5.3 cycles a step measured; loading 16 values and
+	// then running 16 fmas takes 7.7, a two-buffer scheme with a copy 11.5).
+	__device__ __forceinline__ float sum_squares_lane(const float* r, int steps) {
+		float acc = 0.f;
+		int s	  = 0;
+		if (steps >= 16) {
+			float buf[16];
+#pragma unroll
+			for (int j = 0; j < 16; ++j)
+				buf[j] = r[8 * j];
+			for (; s + 32 <= steps; s += 16) {
+#pragma unroll
+				for (int j = 0; j < 16; ++j) {
+					acc	   = __fmaf_rn(buf[j], buf[j], acc);
+					buf[j] = r[8 * (s + 16 + j)];
+				}
+			}
+#pragma unroll
+			for (int j = 0; j < 16; ++j)
+				acc = __fmaf_rn(buf[j], buf[j], acc);
+			s += 16;
+		}
+		for (; s < steps; ++s)
+			acc = __fmaf_rn(r[8 * s], r[8 * s], acc);
+		return acc;
+	}
+
 	// exact dot of 16 int8 pairs
 	__device__ __forceinline__ int dot16(const uint4& w, const uint4& a) {
 		int s = __dp4a(static_cast<int>(w.x), static_cast<int>(a.x), 0);

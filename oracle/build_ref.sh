@@ -8,6 +8,10 @@
 #
 # Extracted ranges (all inside the reference's block comment, i.e. dead code there):
 #   cpu/common.hpp 215-221   fp32_to_fp16 / fp16_to_fp32 (F16C)
+#   cpu/common.hpp 448-450   sqrtf_fast (the x86 build's integer approximation)
+#   cpu/avx_2.hpp 671-721    quantize_row_q8_0_avx2
+#   cpu/avx_2.hpp 758-779    simd_sum_squares
+#   cpu/avx_2.hpp 3621-3850  vec_scale_mul_f32<n>
 #   cpu/avx_2.hpp 4418-4677  fp32_to_fp16_f16c, quantize_row_q8_0, int8 pair helpers, vec_dot_q8_0_q8_0<n<=16>
 #   cpu/avx_2.hpp 4749-4852  vec_dot_q8_0_q8_0_impl, vec_dot_q8_f32<K>
 #   cpu/avx_2.hpp 4881-4907  scalar_dot_product_q8_f32
@@ -27,6 +31,14 @@ check() { # file line pattern
 }
 check "$common" 215 'fp32_to_fp16(float f)'
 check "$common" 219 'fp16_to_fp32(half h)'
+check "$common" 448 'sqrtf_fast(float x)'
+check "$common" 450 '}'
+check "$avx2" 671 'quantize_row_q8_0_avx2('
+check "$avx2" 721 '}'
+check "$avx2" 758 'simd_sum_squares('
+check "$avx2" 779 '}'
+check "$avx2" 3621 'struct vec_scale_mul_f32 {};'
+check "$avx2" 3850 '};'
 check "$avx2" 4418 'fp32_to_fp16_f16c(float f)'
 check "$avx2" 4439 'quantize_row_q8_0('
 check "$avx2" 4677 '};'
@@ -37,8 +49,8 @@ check "$avx2" 4907 '}'
 mkdir -p "$here/_ref"
 {
 	cat "$here/ref_prelude.hpp"
-	sed -n '215,221p' "$common"
-	sed -n '4418,4677p;4749,4852p;4881,4907p' "$avx2"
+	sed -n '215,221p;448,450p' "$common"
+	sed -n '671,721p;758,779p;3621,3850p;4418,4677p;4749,4852p;4881,4907p' "$avx2"
 	cat "$here/ref_postlude.cpp"
 } | g++ -x c++ -std=gnu++20 -O3 -mavx2 -mfma -mf16c -fPIC -shared -pthread -o "$here/_ref/libnihilus_ref.so" -
 echo "build_ref: wrote $here/_ref/libnihilus_ref.so"

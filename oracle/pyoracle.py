@@ -68,6 +68,14 @@ class Oracle:
         L.orc_unpack_planes.argtypes = [C.POINTER(C.c_int8), C.POINTER(C.c_uint16), C.c_int64, C.c_int64, _c_u8p]
         L.orc_quantize_matrix_q8_0.restype = None
         L.orc_quantize_matrix_q8_0.argtypes = [_c_f32p, C.c_int64, C.c_int64, _c_u8p, C.c_int]
+        L.orc_sum_squares.restype = C.c_float
+        L.orc_sum_squares.argtypes = [_c_f32p, C.c_int64]
+        L.orc_sqrtf_fast.restype = C.c_float
+        L.orc_sqrtf_fast.argtypes = [C.c_float]
+        L.orc_rms_norm_mul.restype = C.c_int
+        L.orc_rms_norm_mul.argtypes = [_c_f32p, C.c_int64, _c_f32p, C.c_float, C.c_int, _c_f32p, C.c_int64, C.c_int64, C.c_int64]
+        L.orc_rms_norm_mul_q8_0.restype = C.c_int
+        L.orc_rms_norm_mul_q8_0.argtypes = [_c_f32p, C.c_int64, _c_f32p, C.c_float, C.c_int, _c_u8p, C.c_int64, C.c_int64]
 
     # scalars
     def fp32_to_fp16(self, f: float) -> int:
@@ -145,6 +153,38 @@ class Oracle:
                                    K, rows, _ptr(out, _c_u8p))
         return out
 
+    # rms_norm x norm-weight
+    def sum_squares(self, x: np.ndarray) -> float:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        return float(self.lib.orc_sum_squares(_ptr(x, _c_f32p), x.size))
+
+    def sqrtf_fast(self, v: float) -> float:
+        return float(self.lib.orc_sqrtf_fast(v))
+
+    def rms_norm_mul(self, x: np.ndarray, w: np.ndarray, eps: float, sqrt_mode: int = 0) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        if x.ndim == 1:
+            x = x[None, :]
+        M, K = x.shape
+        y = np.empty((M, K), dtype=np.float32)
+        rc = self.lib.orc_rms_norm_mul(_ptr(x, _c_f32p), K, _ptr(w, _c_f32p), eps, sqrt_mode, _ptr(y, _c_f32p), K, M, K)
+        if rc != 0:
+            raise ValueError(f"orc_rms_norm_mul rc={rc}")
+        return y
+
+    def rms_norm_mul_q8_0(self, x: np.ndarray, w: np.ndarray, eps: float, sqrt_mode: int = 0) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        if x.ndim == 1:
+            x = x[None, :]
+        M, K = x.shape
+        out = np.empty((M, K // QK, BLOCK_BYTES), dtype=np.uint8)
+        rc = self.lib.orc_rms_norm_mul_q8_0(_ptr(x, _c_f32p), K, _ptr(w, _c_f32p), eps, sqrt_mode, _ptr(out, _c_u8p), M, K)
+        if rc != 0:
+            raise ValueError(f"orc_rms_norm_mul_q8_0 rc={rc}")
+        return out
+
 
 class Reference:
     """The reference's own helper functions, compiled in place into oracle/_ref/ (may be absent)."""
@@ -169,6 +209,16 @@ class Reference:
             fn.argtypes = [_c_f32p, C.c_void_p, C.c_int64]
         L.ref_mul_mat_q8_0.restype = C.c_int
         L.ref_mul_mat_q8_0.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, _c_f32p, C.c_int64, C.c_int64, _c_f32p, C.c_int64, C.c_int]
+        self.has_rms_norm = hasattr(L, "ref_rms_norm_mul")  # absent from a library built before these were added
+        if self.has_rms_norm:
+            L.ref_sum_squares.restype = C.c_float
+            L.ref_sum_squares.argtypes = [_c_f32p, C.c_int64]
+            L.ref_sqrtf_fast.restype = C.c_float
+            L.ref_sqrtf_fast.argtypes = [C.c_float]
+            L.ref_rms_norm_mul.restype = C.c_int
+            L.ref_rms_norm_mul.argtypes = [_c_f32p, C.c_int64, _c_f32p, C.c_float, C.c_int, _c_f32p, C.c_int64, C.c_int64, C.c_int64]
+            L.ref_rms_norm_mul_q8_0.restype = C.c_int
+            L.ref_rms_norm_mul_q8_0.argtypes = [_c_f32p, C.c_int64, _c_f32p, C.c_float, C.c_int, C.c_void_p, C.c_int64, C.c_int64]
 
     @staticmethod
     def available() -> bool:
@@ -216,3 +266,34 @@ class Reference:
         if rc != 0:
             raise ValueError(f"ref_mul_mat_q8_0 rc={rc}")
         return y
+
+    def sum_squares(self, x: np.ndarray) -> float:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        return float(self.lib.ref_sum_squares(_ptr(x, _c_f32p), x.size))
+
+    def sqrtf_fast(self, v: float) -> float:
+        return float(self.lib.ref_sqrtf_fast(v))
+
+    def rms_norm_mul(self, x: np.ndarray, w: np.ndarray, eps: float, sqrt_mode: int = 0) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        if x.ndim == 1:
+            x = x[None, :]
+        M, K = x.shape
+        y = np.empty((M, K), dtype=np.float32)
+        rc = self.lib.ref_rms_norm_mul(_ptr(x, _c_f32p), K, _ptr(w, _c_f32p), eps, sqrt_mode, _ptr(y, _c_f32p), K, M, K)
+        if rc != 0:
+            raise ValueError(f"ref_rms_norm_mul rc={rc}")
+        return y
+
+    def rms_norm_mul_q8_0(self, x: np.ndarray, w: np.ndarray, eps: float, sqrt_mode: int = 0) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        if x.ndim == 1:
+            x = x[None, :]
+        M, K = x.shape
+        out = np.empty((M, K // QK, BLOCK_BYTES), dtype=np.uint8)
+        rc = self.lib.ref_rms_norm_mul_q8_0(_ptr(x, _c_f32p), K, _ptr(w, _c_f32p), eps, sqrt_mode, out.ctypes.data, M, K)
+        if rc != 0:
+            raise ValueError(f"ref_rms_norm_mul_q8_0 rc={rc}")
+        return out

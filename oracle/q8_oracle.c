@@ -564,3 +564,80 @@ void orc_quantize_matrix_q8_0(const float* w, int64_t N, int64_t K, uint8_t* blo
 		if (threads > 1 && tids[t])
 			pthread_join(tids[t], NULL);
 }
+
+/* ---- rms_norm x norm-weight (-> Q8_0), the producer of a projection's activations ---------------------------------- */
+
+/* simd_sum_squares, avx_2.hpp:758-779 (again at :3598-3619): lane l of a 256-bit accumulator takes elements
+ * 8i + l through one fma each, in ascending i; then (lo + hi) on 4 lanes, (x + movehl) on 2, add_ss on 1. */
+float orc_sum_squares(const float* x, int64_t k) {
+	float lane[8]	   = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
+	const int64_t full = k & ~(int64_t)7;
+	for (int64_t i = 0; i < full; i += 8)
+		for (int l = 0; l < 8; ++l)
+			lane[l] = fmaf(x[i + l], x[i + l], lane[l]);
+	const float q0 = lane[0] + lane[4], q1 = lane[1] + lane[5], q2 = lane[2] + lane[6], q3 = lane[3] + lane[7];
+	const float d0 = q0 + q2, d1 = q1 + q3;
+	float sum	   = d0 + d1;
+	for (int64_t i = full; i < k; ++i)
+		sum += x[i] * x[i]; /* scalar tail of the reference; no caller here has k % 8 != 0 */
+	return sum;
+}
+
+/* sqrtf_fast, cpu/common.hpp:448-450 (the x86 build): an integer approximation of the square root, not sqrtf. */
+float orc_sqrtf_fast(float x) {
+	uint32_t b;
+	memcpy(&b, &x, 4);
+	b = ((b + 0x3f800000u) >> 1) + 0x20000000u;
+	float r;
+	memcpy(&r, &b, 4);
+	return r;
+}
+
+/* the scale of one row: avx_2.hpp:3907-3909.  sqrt_mode 0: sqrtf_fast is the IEEE square root (the NEON build,
+ * cpu/common.hpp:310-312); sqrt_mode 1: the x86 build's integer formula above, which as written returns about
+ * 2^64 * sqrt(x), so every scale carries a factor of about 2^-64 -- kept bit for bit because it is what that build
+ * computes. */
+float orc_rms_norm_scale(const float* x, int64_t k, float eps, int sqrt_mode) {
+	const float sum	 = orc_sum_squares(x, k);
+	const float mean = sum / (float)k;
+	const float root = sqrt_mode == 1 ? orc_sqrtf_fast(mean + eps) : sqrtf(mean + eps);
+	return 1.0f / root;
+}
+
+/* (x * w) * scale, two roundings -- vec_scale_mul_f32, avx_2.hpp:3621-3850, as called by the rms_norm_mul kernel
+ * (:3907-3915).  (The Q8_0-producing helper vec_scale_mul_f32_to_q8_0, :723-756, hands quantize_row_q8_0_avx2 a
+ * count of 1 element, i.e. zero blocks, and so produces nothing to compare with; the Q8_0 output below is the
+ * reference's quantiser applied to the f32 kernel's row, which is what the rms_norm_mul -> mul_mat chain computes.) */
+static inline float norm_elem(float x, float w, float scale) {
+	const float t = x * w;
+	return t * scale;
+}
+
+int orc_rms_norm_mul(const float* x, int64_t ldx, const float* w, float eps, int sqrt_mode, float* y, int64_t ldy, int64_t M, int64_t K) {
+	if (!x || !w || !y || M < 0 || K <= 0 || (K % 8) != 0 || ldx < K || ldy < K || sqrt_mode < 0 || sqrt_mode > 1)
+		return -1;
+	for (int64_t m = 0; m < M; ++m) {
+		const float scale = orc_rms_norm_scale(x + m * ldx, K, eps, sqrt_mode);
+		for (int64_t i = 0; i < K; ++i)
+			y[m * ldy + i] = norm_elem(x[m * ldx + i], w[i], scale);
+	}
+	return 0;
+}
+
+/* the same row, quantised block by block (quantize_row_q8_0_avx2, avx_2.hpp:671-721, has the arithmetic of
+ * quantize_row_q8_0). blocks: [M][K/32][34]. */
+int orc_rms_norm_mul_q8_0(const float* x, int64_t ldx, const float* w, float eps, int sqrt_mode, uint8_t* blocks, int64_t M, int64_t K) {
+	if (!x || !w || !blocks || M < 0 || K <= 0 || (K % ORC_QK) != 0 || ldx < K || sqrt_mode < 0 || sqrt_mode > 1)
+		return -1;
+	float* row = (float*)malloc((size_t)K * sizeof(float));
+	if (!row)
+		return -1;
+	for (int64_t m = 0; m < M; ++m) {
+		const float scale = orc_rms_norm_scale(x + m * ldx, K, eps, sqrt_mode);
+		for (int64_t i = 0; i < K; ++i)
+			row[i] = norm_elem(x[m * ldx + i], w[i], scale);
+		orc_quantize_row_q8_0(row, blocks + m * (K / ORC_QK) * ORC_BLOCK_BYTES, K);
+	}
+	free(row);
+	return 0;
+}

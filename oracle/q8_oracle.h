@@ -66,6 +66,15 @@ void orc_unpack_planes(const int8_t* q_plane, const uint16_t* d_plane, int64_t K
 /* weights for the synthetic workloads: f32 rows -> Q8_0 blocks (row by row, threads-parallel) */
 void orc_quantize_matrix_q8_0(const float* w, int64_t N, int64_t K, uint8_t* blocks, int threads);
 
+/* rms_norm x norm-weight, f32 out or Q8_0 blocks out: y = (x*w)*scale, scale = 1 / sqrtf_fast(sum_squares/K + eps)
+ * (avx_2.hpp:671-779, 3598-3950).  sqrt_mode 0: IEEE square root (sqrtf_fast of the NEON build, cpu/common.hpp:310-312);
+ * 1: the integer formula of the x86 build (cpu/common.hpp:448-450), which is off by a factor of about 2^64. */
+float orc_sum_squares(const float* x, int64_t k);
+float orc_sqrtf_fast(float x);
+float orc_rms_norm_scale(const float* x, int64_t k, float eps, int sqrt_mode);
+int orc_rms_norm_mul(const float* x, int64_t ldx, const float* w, float eps, int sqrt_mode, float* y, int64_t ldy, int64_t M, int64_t K);
+int orc_rms_norm_mul_q8_0(const float* x, int64_t ldx, const float* w, float eps, int sqrt_mode, uint8_t* blocks, int64_t M, int64_t K);
+
 #ifdef __cplusplus
 }
 #endif

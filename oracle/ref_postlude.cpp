@@ -9,6 +9,7 @@
 
 }// namespace nihilus
 
+#include <cstdlib>
 #include <thread>
 #include <vector>
 
@@ -112,6 +113,42 @@ namespace {
 		for (auto& t: pool)
 			t.join();
 	}
+#define NHB_NORM_SIZES(X) X(32) X(64) X(96) X(128) X(160) X(256) X(512) X(1024) X(2048) X(4096) X(14336)
+
+	// one row of the rms_norm_mul kernel (cpu/avx_2.hpp:3907-3915): the reference's sum of squares, its sqrtf_fast and
+	// its vec_scale_mul_f32<K>; the row loop around it is ours.  The reference stores with aligned and streaming
+	// stores, so the row goes through 64-byte aligned buffers.  false when K has no instantiation here.
+	bool norm_row(const float* x, const float* w, float eps, int sqrt_mode, float* y, int64_t K) {
+		const float sum	  = nihilus::simd_sum_squares(x, static_cast<uint64_t>(K));
+		const float mean  = sum / static_cast<float>(K);
+		const float root  = sqrt_mode == 1 ? nihilus::sqrtf_fast(mean + eps) : std::sqrt(mean + eps);// 0: what the NEON build's sqrtf_fast is
+		const float scale = 1.0f / root;
+		switch (K) {
+#define NHB_CASE(v) \
+	case v: \
+		nihilus::vec_scale_mul_f32<v>::impl(y, x, scale, w); \
+		return true;
+			NHB_NORM_SIZES(NHB_CASE)
+#undef NHB_CASE
+			default:
+				return false;
+		}
+	}
+
+	struct aligned_rows {
+		float *x, *w, *y;
+		explicit aligned_rows(int64_t K) {
+			const size_t bytes = (static_cast<size_t>(K) * 4 + 63) & ~size_t(63);
+			x				   = static_cast<float*>(std::aligned_alloc(64, bytes));
+			w				   = static_cast<float*>(std::aligned_alloc(64, bytes));
+			y				   = static_cast<float*>(std::aligned_alloc(64, bytes));
+		}
+		~aligned_rows() {
+			std::free(x);
+			std::free(w);
+			std::free(y);
+		}
+	};
 }
 
 extern "C" {
@@ -188,6 +225,44 @@ int ref_mul_mat_q8_0(int mode, const void* w_blocks, int64_t N, int64_t K, const
 			}
 		}
 	});
+	return 0;
+}
+
+// cpu/avx_2.hpp:758-779 and cpu/common.hpp:448-450
+float ref_sum_squares(const float* x, int64_t K) {
+	return nihilus::simd_sum_squares(x, static_cast<uint64_t>(K));
+}
+float ref_sqrtf_fast(float x) {
+	return nihilus::sqrtf_fast(x);
+}
+
+// rms_norm x norm-weight, f32 out; 0, -1 on bad arguments, -2 when K has no instantiation
+int ref_rms_norm_mul(const float* x, int64_t ldx, const float* w, float eps, int sqrt_mode, float* y, int64_t ldy, int64_t M, int64_t K) {
+	if (!x || !w || !y || M < 0 || K <= 0 || ldx < K || ldy < K)
+		return -1;
+	aligned_rows r(K);
+	std::memcpy(r.w, w, static_cast<size_t>(K) * 4);
+	for (int64_t m = 0; m < M; ++m) {
+		std::memcpy(r.x, x + m * ldx, static_cast<size_t>(K) * 4);
+		if (!norm_row(r.x, r.w, eps, sqrt_mode, r.y, K))
+			return -2;
+		std::memcpy(y + m * ldy, r.y, static_cast<size_t>(K) * 4);
+	}
+	return 0;
+}
+
+// the same rows through the reference's quantize_row_q8_0_avx2 (cpu/avx_2.hpp:671-721); blocks [M][K/32]
+int ref_rms_norm_mul_q8_0(const float* x, int64_t ldx, const float* w, float eps, int sqrt_mode, void* blocks, int64_t M, int64_t K) {
+	if (!x || !w || !blocks || M < 0 || K <= 0 || K % 32 != 0 || ldx < K)
+		return -1;
+	aligned_rows r(K);
+	std::memcpy(r.w, w, static_cast<size_t>(K) * 4);
+	for (int64_t m = 0; m < M; ++m) {
+		std::memcpy(r.x, x + m * ldx, static_cast<size_t>(K) * 4);
+		if (!norm_row(r.x, r.w, eps, sqrt_mode, r.y, K))
+			return -2;
+		nihilus::quantize_row_q8_0_avx2(r.y, static_cast<blk*>(blocks) + m * (K / 32), static_cast<uint64_t>(K));
+	}
 	return 0;
 }
 }
