@@ -37,7 +37,7 @@ namespace nihilus_b200 {
 
 	enum class device_types : uint8_t { cpu, gpu };
 	enum class processing_phases { prompt_eval_time, eval_time };
-	enum class kernel_types : uint8_t { weights, mul_mat };
+	enum class kernel_types : uint8_t { weights, rms_norm, mul, mul_mat };
 	enum class data_types : uint64_t { f32 = 0, f16 = 1, q8_0 = 8 };
 
 	// compute-capability major -> the reference's build-time arch index (cmake/detection/main.cpp:33-44): 10 -> 2
@@ -111,6 +111,40 @@ namespace nihilus_b200 {
 		}
 	};
 
+	// rms_norm: one input, output of the same extents (common/kernel_traits.hpp:904-922)
+	template<typename output_type_new, typename input_01_type_new> struct kernel_traits<kernel_types::rms_norm, output_type_new, input_01_type_new> {
+		using output_type	= output_type_new;
+		using input_01_type = input_01_type_new;
+		static constexpr auto input_01_dims = input_01_type::get_array();
+		static constexpr auto output_dims	= output_type::get_array();
+		static_assert(input_01_dims[0] == output_dims[0], "rms_norm: input dimension 0 must match output");
+		static_assert(input_01_dims[1] == output_dims[1], "rms_norm: input dimension 1 must match output");
+		static_assert(input_01_dims[2] == output_dims[2], "rms_norm: input dimension 2 must match output");
+		static_assert(input_01_dims[3] == output_dims[3], "rms_norm: input dimension 3 must match output");
+		static_assert(std::is_same_v<typename input_01_type::element_type, float> && std::is_same_v<typename output_type::element_type, float>, "rms_norm works on f32");
+		static_assert(input_01_dims[0] % 32 == 0, "the row length must be a multiple of the Q8_0 block size");
+		static constexpr int64_t K = static_cast<int64_t>(input_01_dims[0]);
+	};
+
+	// mul: element-wise, the second input broadcast over dimensions 1-3 (common/kernel_traits.hpp:446-471)
+	template<typename output_type_new, typename input_01_type_new, typename input_02_type_new>
+	struct kernel_traits<kernel_types::mul, output_type_new, input_01_type_new, input_02_type_new> {
+		using output_type	= output_type_new;
+		using input_01_type = input_01_type_new;
+		using input_02_type = input_02_type_new;
+		static constexpr auto input_01_dims = input_01_type::get_array();
+		static constexpr auto input_02_dims = input_02_type::get_array();
+		static constexpr auto output_dims	= output_type::get_array();
+		static_assert(input_01_dims[0] == input_02_dims[0], "mul: element-wise dimension 0 must match");
+		static_assert(input_01_dims[1] == input_02_dims[1] || input_02_dims[1] == 1, "mul: dimension 1 must match or be broadcast");
+		static_assert(input_01_dims[2] == input_02_dims[2] || input_02_dims[2] == 1, "mul: dimension 2 must match or be broadcast");
+		static_assert(input_01_dims[3] == input_02_dims[3] || input_02_dims[3] == 1, "mul: dimension 3 must match or be broadcast");
+		static_assert(output_dims[0] == input_01_dims[0] && output_dims[1] == input_01_dims[1] && output_dims[2] == input_01_dims[2] &&
+				output_dims[3] == input_01_dims[3],
+			"mul: output dimensions must match the first input");
+		static_assert(input_02_dims[1] == 1 && input_02_dims[2] == 1 && input_02_dims[3] == 1, "this library multiplies by a norm weight: one row, broadcast");
+	};
+
 	struct mul_mat_error : std::runtime_error {
 		int status;
 		mul_mat_error(int s, const std::string& m) : std::runtime_error(m), status(s) {
@@ -171,6 +205,28 @@ namespace nihilus_b200 {
 		static constexpr size_t node_count = sizeof...(node_types);
 	};
 
+	// The rms_norm -> mul pair in front of a stage (infra/core_traits.hpp:570-573 and 971-974: attn_norm before q/k/v,
+	// ffn_norm before gate/up).  `input` is the hidden state before the norm, `norm_weight` the f32 norm weight row.
+	template<typename rms_norm_traits_new, typename mul_traits_new> struct norm_mul_node {
+		using rms_norm_traits = rms_norm_traits_new;
+		using mul_traits	  = mul_traits_new;
+		static_assert(std::is_same_v<typename mul_traits::input_01_type, typename rms_norm_traits::output_type>, "mul takes the rms_norm's output");
+		typename rms_norm_traits::input_01_type input;
+		typename mul_traits::input_02_type norm_weight;
+		float eps	  = 1e-5f;// model_traits: layer_norm_rms_epsilon
+		int sqrt_mode = NHB_SQRT_IEEE;
+	};
+
+	// A stage whose mul_mats all read the normalised row: the norm is fused in front of them.  The mul_mat nodes'
+	// `activation` pointers are not read; their extents still carry the token count.
+	template<typename norm_node_type, typename... node_types> struct norm_mul_mat_core {
+		nhb_ctx* ctx = nullptr;
+		norm_node_type norm;
+		std::tuple<node_types...> nodes;
+		static constexpr size_t node_count = sizeof...(node_types);
+		static_assert(((node_types::traits_type::K == norm_node_type::rms_norm_traits::K) && ...), "every mul_mat of the stage must read the normalised row");
+	};
+
 	template<typename config_type, typename core_traits_type, device_types device_type, uint64_t arch_index, processing_phases processing_phase>
 	struct kernel_dispatcher_impl;
 
@@ -187,9 +243,19 @@ namespace nihilus_b200 {
 					if (op.M != 1)
 						raise<config_type::exceptions>(NHB_ERR_ARG, "eval_time dispatch with more than one token", params.ctx);
 			}
-			const int rc = nhb_mul_mat_batch(params.ctx, ops.data(), static_cast<int>(ops.size()), config_type::act_mode, NHB_KERNEL_AUTO);
-			if (rc != NHB_OK)
-				raise<config_type::exceptions>(rc, "nhb_mul_mat_batch", params.ctx);
+			if constexpr (requires { params.norm; }) {
+				static_assert(config_type::act_mode == NHB_ACT_Q8, "the fused norm produces Q8_0 activations");
+				for (auto& op: ops)
+					op.x = static_cast<const float*>(params.norm.input.get_data());
+				const int rc = nhb_rms_norm_mul_mat_batch(params.ctx, ops.data(), static_cast<int>(ops.size()),
+					static_cast<const float*>(params.norm.norm_weight.get_data()), params.norm.eps, params.norm.sqrt_mode, NHB_KERNEL_AUTO);
+				if (rc != NHB_OK)
+					raise<config_type::exceptions>(rc, "nhb_rms_norm_mul_mat_batch", params.ctx);
+			} else {
+				const int rc = nhb_mul_mat_batch(params.ctx, ops.data(), static_cast<int>(ops.size()), config_type::act_mode, NHB_KERNEL_AUTO);
+				if (rc != NHB_OK)
+					raise<config_type::exceptions>(rc, "nhb_mul_mat_batch", params.ctx);
+			}
 		}
 		// global cores (logits): block 0
 		static void impl(core_traits_type& params) {
@@ -223,6 +289,11 @@ namespace nihilus_b200 {
 		using ffn_up	  = projection<E, FF>;
 		using ffn_down	  = projection<FF, E>;
 		using output	  = projection<E, V, 1>;
+		// attn_norm / ffn_norm in front of their stage
+		using norm_w_t = operand<core_trait_dims<E, 1, 1, 1>, float>;
+		using norm_node = norm_mul_node<kernel_traits<kernel_types::rms_norm, act_t<E>, act_t<E>>, kernel_traits<kernel_types::mul, act_t<E>, act_t<E>, norm_w_t>>;
+		using norm_qkv_core		= norm_mul_mat_core<norm_node, attn_q, attn_k, attn_v>;
+		using norm_gate_up_core = norm_mul_mat_core<norm_node, ffn_gate, ffn_up>;
 		using qkv_core	  = mul_mat_core<attn_q, attn_k, attn_v>;
 		using attn_out_core = mul_mat_core<attn_output>;
 		using gate_up_core	= mul_mat_core<ffn_gate, ffn_up>;

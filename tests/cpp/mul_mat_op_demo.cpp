@@ -4,6 +4,8 @@
 //   mul_mat_op_demo check                                  compile-time and host-only checks, no GPU
 //   mul_mat_op_demo run <wk.bin> <wv.bin> <x.bin> M <yk.bin> <yv.bin>
 //        wk/wv: raw Q8_0 blocks of two 1024 x 4096 weights, x: f32 [M][4096]; writes f32 [M][1024] each
+//   mul_mat_op_demo run_norm <wk.bin> <wv.bin> <x.bin> M <yk.bin> <yv.bin> <norm_w.bin>
+//        the same with the rms_norm -> mul pair in front (x is the row before the norm, norm_w: f32 [4096], eps 1e-5)
 #include <nihilus_b200/mul_mat_op.hpp>
 
 #include <cstring>
@@ -21,6 +23,7 @@ static_assert(llama3_8b::ffn_down::traits_type::K == 14336 && llama3_8b::ffn_dow
 static_assert(llama3_8b::output::traits_type::N == 128256);
 static_assert(llama3_8b::qkv_core::node_count == 3 && llama3_8b::gate_up_core::node_count == 2);
 static_assert(llama3_8b::act_t<4096>::runtime_dim == 1);
+static_assert(llama3_8b::norm_qkv_core::node_count == 3 && llama3_8b::norm_node::rms_norm_traits::K == 4096);
 
 static std::vector<char> slurp(const char* path) {
 	std::ifstream f(path, std::ios::binary);
@@ -60,7 +63,7 @@ static int check() {
 	return 0;
 }
 
-static int run(char** a) {
+static int run(char** a, bool with_norm) {
 	const auto wk = slurp(a[0]), wv = slurp(a[1]), x = slurp(a[2]);
 	const int64_t M = std::atoll(a[3]);
 	constexpr int64_t K = 4096, N = 1024;
@@ -91,7 +94,28 @@ static int run(char** a) {
 	nk.output.data[0]							  = yk;
 	nv.output.data[0]							  = yv;
 	nk.activation.get_seq_length_dim() = nv.activation.get_seq_length_dim() = static_cast<uint64_t>(M);
-	if (M == 1)
+	void* nwd = nullptr;
+	if (with_norm) {
+		// the same two projections behind attn_norm: the dispatcher takes the hidden state and the norm weight
+		const auto nw = slurp(a[6]);
+		if (nw.size() != size_t(K) * 4)
+			throw std::runtime_error("norm weight must be f32 [4096]");
+		if (nhb_device_alloc(ctx, nw.size(), &nwd) != NHB_OK)
+			raise<true>(NHB_ERR_NOMEM, "nhb_device_alloc", ctx);
+		nhb_memcpy_h2d(ctx, nwd, nw.data(), nw.size());
+		using ncore_t = norm_mul_mat_core<llama3_8b::norm_node, llama3_8b::attn_k, llama3_8b::attn_v>;
+		ncore_t ncore{};
+		ncore.ctx					   = ctx;
+		ncore.norm.input.data[0]	   = xd;
+		ncore.norm.norm_weight.data[0] = nwd;
+		ncore.norm.eps				   = 1e-5f;
+		std::get<0>(ncore.nodes)	   = nk;
+		std::get<1>(ncore.nodes)	   = nv;
+		if (M == 1)
+			kernel_dispatcher<cfg, processing_phases::eval_time, ncore_t>::impl(ncore, block);
+		else
+			kernel_dispatcher<cfg, processing_phases::prompt_eval_time, ncore_t>::impl(ncore, block);
+	} else if (M == 1)
 		kernel_dispatcher<cfg, processing_phases::eval_time, core_t>::impl(core, block);
 	else
 		kernel_dispatcher<cfg, processing_phases::prompt_eval_time, core_t>::impl(core, block);
@@ -108,6 +132,8 @@ static int run(char** a) {
 	nhb_device_free(ctx, xd);
 	nhb_device_free(ctx, yk);
 	nhb_device_free(ctx, yv);
+	if (nwd)
+		nhb_device_free(ctx, nwd);
 	nhb_ctx_destroy(ctx);
 	std::cout << "run ok\n";
 	return 0;
@@ -118,11 +144,13 @@ int main(int argc, char** argv) {
 		if (argc == 2 && !std::strcmp(argv[1], "check"))
 			return check();
 		if (argc == 8 && !std::strcmp(argv[1], "run"))
-			return run(argv + 2);
+			return run(argv + 2, false);
+		if (argc == 9 && !std::strcmp(argv[1], "run_norm"))
+			return run(argv + 2, true);
 	} catch (const std::exception& e) {
 		std::cerr << "error: " << e.what() << "\n";
 		return 2;
 	}
-	std::cerr << "usage: mul_mat_op_demo check | run wk.bin wv.bin x.bin M yk.bin yv.bin\n";
+	std::cerr << "usage: mul_mat_op_demo check | run wk.bin wv.bin x.bin M yk.bin yv.bin | run_norm ... norm_w.bin\n";
 	return 64;
 }

@@ -70,3 +70,46 @@ def test_dispatch_through_the_cpp_interface_matches_the_oracle(demo, oracle, tmp
         y = np.fromfile(p[name], dtype=np.float32).reshape(M, N)
         ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
         assert float(np.abs(y - ref).max() / np.abs(ref).max()) <= 1e-4
+
+
+def test_static_checks_reject_a_norm_weight_of_the_wrong_length(capi, tmp_path):
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("g++ not available")
+    bad = tmp_path / "bad_norm.cpp"
+    bad.write_text(
+        "#include <nihilus_b200/mul_mat_op.hpp>\n"
+        "using namespace nihilus_b200;\n"
+        "using a = operand<core_trait_dims<4096, 1, 1, 1, 1>, float>;\n"
+        "using w = operand<core_trait_dims<2048, 1, 1, 1>, float>;\n"
+        "using t = kernel_traits<kernel_types::mul, a, a, w>;\n"
+        "int main() { return static_cast<int>(t::output_dims[0]); }\n"
+    )
+    r = subprocess.run([gxx, "-std=c++23", "-fsyntax-only", "-I" + os.path.join(ROOT, "include"), str(bad)], capture_output=True, text=True)
+    assert r.returncode != 0
+    assert "element-wise dimension 0 must match" in r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 3, 40])
+def test_norm_stage_through_the_cpp_interface_matches_the_oracle(demo, oracle, tmp_path, M):
+    """attn_norm -> (k, v) as one core: the dispatcher hands the hidden state and the norm weight to the library."""
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    N, K = 1024, 4096
+    wk, wv = synth.make_weight(N, K, 911), synth.make_weight(N, K, 912)
+    x = (synth.make_activation(M, K, 913 + M) * 3.0).astype(np.float32)
+    nw = np.random.default_rng(914).uniform(0.5, 1.5, K).astype(np.float32)
+    p = {n: str(tmp_path / n) for n in ("wk", "wv", "x", "yk", "yv", "nw")}
+    wk.tofile(p["wk"])
+    wv.tofile(p["wv"])
+    x.tofile(p["x"])
+    nw.tofile(p["nw"])
+    r = subprocess.run([demo, "run_norm", p["wk"], p["wv"], p["x"], str(M), p["yk"], p["yv"], p["nw"]], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    normed = oracle.rms_norm_mul(x, nw, float(np.float32(1e-5)), 0)
+    for w, name in ((wk, "yk"), (wv, "yv")):
+        y = np.fromfile(p[name], dtype=np.float32).reshape(M, N)
+        ref = oracle.mul_mat(po.Q8ACT_LANES, w, normed)
+        assert float(np.abs(y - ref).max() / np.abs(ref).max()) <= 1e-4
