@@ -94,6 +94,19 @@ def _worker(rank, world, uid_path, q):
         g.free()
         for h in hs.values():
             h.free()
+        # ---- rms_norm x norm-weight fused in front of a sharded stage whose outputs the GEMV delivers to every rank ----
+        wn_a, wn_b = synth.make_weight(4096, 4096, 81), synth.make_weight(1024, 4096, 82)
+        hn_a, hn_b = ctx.upload(wn_a), ctx.upload(wn_b)
+        xn = torch.from_numpy(synth.make_activation(1, 4096, 83) * 2.0).cuda()
+        nw = torch.from_numpy(np.linspace(0.5, 1.5, 4096, dtype=np.float32)).cuda()
+        yn_a, yn_b = ctx.symm_empty((1, 4096)), ctx.symm_empty((1, 1024))
+        for _ in range(2):
+            ctx.rms_norm_mul_mat_batch([(hn_a, xn, yn_a), (hn_b, xn, yn_b)], nw, 1e-5)
+            ctx.all_gather_batch([yn_a, yn_b])
+        ctx.sync()
+        out["n_a"], out["n_b"] = yn_a.cpu().numpy(), yn_b.cpu().numpy()
+        hn_a.free()
+        hn_b.free()
         # ---- placement policy: small weights stay whole on every rank, large ones are sharded; one batch mixes both ----
         ctx.set_option("replicate_below_mb", 4)
         w_small, w_big = synth.make_weight(700, 4096, 61), synth.make_weight(2048, 4096, 62)  # 3.0 MB and 8.9 MB
@@ -164,6 +177,13 @@ def test_two_gpu_shards_all_gathered_match_oracle(capi, oracle, tmp_path):
             assert (results[r]["f_" + name].view(np.uint32) == results[0]["g_" + name].view(np.uint32)).all()
         if name in ("even", "ragged"):
             assert (results[0]["f_" + name].view(np.uint32) == results[0][name].view(np.uint32)).all()
+    normed = oracle.rms_norm_mul((synth.make_activation(1, 4096, 83) * 2.0).astype(np.float32), np.linspace(0.5, 1.5, 4096, dtype=np.float32),
+                                 float(np.float32(1e-5)), 0)
+    for key, seed, N in (("n_a", 81, 4096), ("n_b", 82, 1024)):
+        ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, 4096, seed), normed)
+        for r in range(world):
+            assert np.abs(results[r][key] - ref).max() <= 1e-4 * np.abs(ref).max(), (key, r)
+        assert (results[0][key].view(np.uint32) == results[1][key].view(np.uint32)).all()
     xr = synth.make_activation(2, 4096, 63)
     for key, seed, N in (("p_small", 61, 700), ("p_big", 62, 2048)):
         ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, 4096, seed), xr)
