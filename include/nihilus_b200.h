@@ -173,6 +173,35 @@ int nhb_rms_norm_mul_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, const f
 int nhb_rms_norm_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, const float* norm_w_dev, float eps, int sqrt_mode,
 	int kernel);
 
+/* ---- GGUF reader in front of the upload ----
+ * Stands in for the reference's model file parser on this path (infra/model_parser.hpp:635-671 header and metadata,
+ * :855-880 tensor table, :890-940 data placement): same magic, limits (100000 tensors, 10000 key/values, 4 dimensions,
+ * 2^32 per dimension), data section located from the end of the file, offsets rounded up to general.alignment.  The
+ * file is mapped read-only; tensor data is never copied on the host except into the upload's pinned staging. */
+typedef struct nhb_gguf nhb_gguf;
+typedef struct nhb_gguf_tensor {
+	const char* name; /* valid until nhb_gguf_close */
+	int n_dims;
+	int64_t dims[4]; /* ne0 (contiguous) first; unused dimensions are 1 */
+	int type;		 /* ggml type id: 0 f32, 1 f16, 8 q8_0 ... (common/config.hpp:179-201) */
+	int64_t bytes;
+	int64_t offset;	  /* absolute file offset of the data */
+	const void* data; /* the mapped bytes */
+} nhb_gguf_tensor;
+int nhb_gguf_open(const char* path, nhb_gguf** out);
+const char* nhb_gguf_last_error(void); /* why the last nhb_gguf_open on this thread failed */
+int nhb_gguf_close(nhb_gguf* g);
+int64_t nhb_gguf_tensor_count(const nhb_gguf* g);
+int64_t nhb_gguf_find(const nhb_gguf* g, const char* name); /* index or -1 */
+int nhb_gguf_tensor_get(const nhb_gguf* g, int64_t index, nhb_gguf_tensor* out);
+/* scalar metadata by key (integers, floats and booleans as double; e.g. "llama.attention.layer_norm_rms_epsilon") */
+int nhb_gguf_get_number(const nhb_gguf* g, const char* key, double* out);
+const char* nhb_gguf_get_string(const nhb_gguf* g, const char* key); /* NULL when absent */
+/* a Q8_0 matrix [ne1 = N rows][ne0 = K] by tensor name, e.g. "blk.0.attn_q.weight": sharded, repacked, uploaded */
+int nhb_gguf_upload_q8_0(nhb_ctx* ctx, const nhb_gguf* g, const char* name, nhb_weight** out);
+/* an f32 tensor (norm weights) copied out of the mapping; count must equal its element count */
+int nhb_gguf_read_f32(const nhb_gguf* g, const char* name, float* dst, int64_t count);
+
 /* ---- for callers that cannot allocate ---- */
 /* No counterpart in the reference.  The decode GEMV (Q8 arithmetic, M <= 4) without a context, a weight handle or
  * any allocation: the caller passes the two device planes of a weight (as nhb_weight_info_get returns them, or as

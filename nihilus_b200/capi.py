@@ -37,12 +37,19 @@ EXPORTS = (
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
     "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_place_rows", "nhb_gemm_tile_plan",
     "nhb_rms_norm_mul", "nhb_rms_norm_mul_q8_0", "nhb_rms_norm_mul_mat_batch",
+    "nhb_gguf_open", "nhb_gguf_last_error", "nhb_gguf_close", "nhb_gguf_tensor_count", "nhb_gguf_find", "nhb_gguf_tensor_get",
+    "nhb_gguf_get_number", "nhb_gguf_get_string", "nhb_gguf_upload_q8_0", "nhb_gguf_read_f32",
 )
 
 
 class WeightInfo(C.Structure):
     _fields_ = [("N", C.c_int64), ("K", C.c_int64), ("n0", C.c_int64), ("n1", C.c_int64), ("q", C.c_void_p), ("d", C.c_void_p),
                 ("bytes_q8", C.c_int64)]
+
+
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("n_dims", C.c_int), ("dims", C.c_int64 * 4), ("type", C.c_int), ("bytes", C.c_int64),
+                ("offset", C.c_int64), ("data", C.c_void_p)]
 
 
 class MulMatOp(C.Structure):
@@ -58,6 +65,16 @@ def _sig(name, restype, *argtypes):
 
 _vp, _i, _i64 = C.c_void_p, C.c_int, C.c_int64
 _sig("nhb_version", _i)
+_sig("nhb_gguf_open", _i, C.c_char_p, C.POINTER(_vp))
+_sig("nhb_gguf_last_error", C.c_char_p)
+_sig("nhb_gguf_close", _i, _vp)
+_sig("nhb_gguf_tensor_count", _i64, _vp)
+_sig("nhb_gguf_find", _i64, _vp, C.c_char_p)
+_sig("nhb_gguf_tensor_get", _i, _vp, _i64, C.POINTER(GgufTensor))
+_sig("nhb_gguf_get_number", _i, _vp, C.c_char_p, C.POINTER(C.c_double))
+_sig("nhb_gguf_get_string", C.c_char_p, _vp, C.c_char_p)
+_sig("nhb_gguf_upload_q8_0", _i, _vp, _vp, C.c_char_p, C.POINTER(_vp))
+_sig("nhb_gguf_read_f32", _i, _vp, C.c_char_p, _vp, _i64)
 _sig("nhb_rms_norm_mul", _i, _vp, _vp, _i64, _vp, C.c_float, _i, _vp, _i64, _i64, _i64)
 _sig("nhb_rms_norm_mul_q8_0", _i, _vp, _vp, _i64, _vp, C.c_float, _i, _vp, _i64, _i64)
 _sig("nhb_rms_norm_mul_mat_batch", _i, _vp, C.POINTER(MulMatOp), _i, _vp, C.c_float, _i, _i)
@@ -189,6 +206,63 @@ class Weight:
         if self.handle:
             lib.nhb_weight_free(self.ctx.handle, self.handle)
             self.handle = None
+
+
+class Gguf:
+    """A mapped GGUF model file (nhb_gguf_*): tensor table, scalar metadata, Q8_0 upload by tensor name."""
+
+    def __init__(self, path: str):
+        h = _vp()
+        rc = lib.nhb_gguf_open(os.fsencode(path), C.byref(h))
+        if rc != 0:
+            raise NhbError(rc, (lib.nhb_gguf_last_error() or b"").decode())
+        self.handle = h.value
+
+    def close(self):
+        if self.handle:
+            lib.nhb_gguf_close(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def __len__(self):
+        return int(lib.nhb_gguf_tensor_count(self.handle))
+
+    def tensor(self, key):
+        """key: index or name -> dict(name, dims, type, bytes, offset)."""
+        idx = key if isinstance(key, int) else int(lib.nhb_gguf_find(self.handle, key.encode()))
+        t = GgufTensor()
+        if idx < 0 or lib.nhb_gguf_tensor_get(self.handle, idx, C.byref(t)) != 0:
+            raise KeyError(key)
+        return {"name": t.name.decode(), "dims": tuple(t.dims[: max(t.n_dims, 1)]), "type": t.type, "bytes": t.bytes, "offset": t.offset,
+                "data": t.data}
+
+    def number(self, key: str):
+        v = C.c_double()
+        if lib.nhb_gguf_get_number(self.handle, key.encode(), C.byref(v)) != 0:
+            raise KeyError(key)
+        return v.value
+
+    def string(self, key: str):
+        v = lib.nhb_gguf_get_string(self.handle, key.encode())
+        if v is None:
+            raise KeyError(key)
+        return v.decode()
+
+    def read_f32(self, name: str) -> np.ndarray:
+        t = self.tensor(name)
+        out = np.empty(t["bytes"] // 4, dtype=np.float32)
+        _check(lib.nhb_gguf_read_f32(self.handle, name.encode(), out.ctypes.data, out.size))
+        return out.reshape(tuple(reversed(t["dims"])))
+
+    def upload_q8_0(self, ctx: "Context", name: str) -> "Weight":
+        h = _vp()
+        _check(lib.nhb_gguf_upload_q8_0(ctx.handle, self.handle, name.encode(), C.byref(h)), ctx.handle)
+        return Weight(ctx, h.value)
 
 
 class Graph:
