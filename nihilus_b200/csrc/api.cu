@@ -521,7 +521,8 @@ namespace {
 		return NHB_OK;
 	}
 
-	int run_gemm(nhb_ctx* ctx, const nhb_mul_mat_op& op) {
+	// `same_input`: the scratch already holds the quantised activations of this very input (left by the previous op of the batch)
+	int run_gemm(nhb_ctx* ctx, const nhb_mul_mat_op& op, bool same_input = false) {
 		const nhb_weight* w = op.w;
 		const int rows		= static_cast<int>(w->n1 - w->n0);
 		if (rows == 0)
@@ -557,7 +558,7 @@ namespace {
 		}
 		std::string err;
 		cudaError_t e = launch_gemm_tc(w->w16, w->wdT, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
-			cfg_of(ctx), &launches, &err);
+			cfg_of(ctx), &launches, &err, same_input);
 		ctx->launches += launches;
 		if (e != cudaSuccess)
 			return fail_cuda(ctx, e, err.empty() ? "gemm_q8_tc launch" : err.c_str());
@@ -1040,12 +1041,17 @@ int nhb_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int ac
 	if (use_gemm) {
 		if (act_mode != NHB_ACT_Q8)
 			return fail(ctx, NHB_ERR_UNSUPPORTED, "the tensor-core GEMM implements the Q8-activation arithmetic only");
+		int last = -1;// the last op that actually ran (a rank may own no rows of an op)
 		for (int i = 0; i < n_ops; ++i) {
 			if (ops[i].w->n1 > ops[i].w->n0 && !gemm_tc_supports(ops[i].w->n1 - ops[i].w->n0, ops[i].w->K, M))
 				return fail(ctx, NHB_ERR_UNSUPPORTED, "shape not supported by the tensor-core GEMM (needs K % 64 == 0)");
-			int rc = run_gemm(ctx, ops[i]);
+			// ops that share their input (q/k/v, gate/up) quantise it once: the scratch is only rewritten by another input
+			const bool same = last >= 0 && ops[last].x == ops[i].x && ops[last].ldx == ops[i].ldx && ops[last].w->K == ops[i].w->K;
+			int rc			= run_gemm(ctx, ops[i], same);
 			if (rc != NHB_OK)
 				return rc;
+			if (ops[i].w->n1 > ops[i].w->n0)
+				last = i;
 		}
 		return NHB_OK;
 	}

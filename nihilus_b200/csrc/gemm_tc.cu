@@ -746,15 +746,16 @@ namespace nhb {
 	}
 
 	cudaError_t launch_gemm_tc(const __half* w16, const float* wdT, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
-		void* scratch, const launch_cfg& cfg, int* launches, std::string* err) {
+		void* scratch, const launch_cfg& cfg, int* launches, std::string* err, bool activations_ready) {
 		const int m_pad = gemm_tc_pad(M);
 		__half* qa16	= static_cast<__half*>(scratch);
 		float* daT		= reinterpret_cast<float*>(static_cast<char*>(scratch) + ((static_cast<size_t>(M) * K * 2 + 255) & ~size_t(255)));
 		cudaLaunchAttribute attr[1];
 		attr[0].id										   = cudaLaunchAttributeProgrammaticStreamSerialization;
 		attr[0].val.programmaticStreamSerializationAllowed = 1;
-		// 1. quantise the activations (fp16-widened quants + block-major scales)
-		{
+		// 1. quantise the activations (fp16-widened quants + block-major scales), unless the previous mul_mat of the same
+		//    batch left exactly these in the scratch (q, k, v and gate, up share their input)
+		if (!activations_ready) {
 			const long long tot = static_cast<long long>(M) * (K / 32);
 			long long grid		= (tot + 127) / 128;
 			grid				= grid > 148 * 16 ? 148 * 16 : grid;

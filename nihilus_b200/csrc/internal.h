@@ -139,6 +139,6 @@ namespace nhb {
 	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M);
 	cudaError_t launch_weight_gemm_planes(const int8_t* q, const __half* d, int64_t rows, int64_t K, __half* w16, float* wdT, cudaStream_t s);
 	cudaError_t launch_gemm_tc(const __half* w16, const float* wdT, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
-		void* scratch, const launch_cfg& cfg, int* launches, std::string* err);
+		void* scratch, const launch_cfg& cfg, int* launches, std::string* err, bool activations_ready = false);
 
 }

@@ -444,3 +444,37 @@ def test_host_buffer_entry_point(capi, ctx, oracle):
     y = ctx.mul_mat_host(h, x)
     assert _rel(y, oracle.mul_mat(po.Q8ACT_LANES, w, x)) <= TOL
     h.free()
+
+
+@pytest.mark.gpu
+def test_gemm_batch_sharing_its_input_quantises_once_and_is_bit_identical(ctx, capi):
+    """q/k/v-style batch through the tensor-core GEMM: the shared input is quantised by the first op only; results are
+    the bits of three separate calls, also when a different input sits between two uses of the same one."""
+    import torch
+
+    from nihilus_b200 import synth
+
+    K, M = 512, 40
+    ws = [ctx.upload(synth.make_weight(n, K, 300 + n)) for n in (256, 128, 192)]
+    xa = torch.from_numpy(synth.make_activation(M, K, 31)).cuda()
+    xb = torch.from_numpy(synth.make_activation(M, K, 32)).cuda()
+    single = []
+    for w, x in zip(ws, (xa, xa, xb)):
+        y = torch.zeros((M, w.N), device="cuda")
+        ctx.mul_mat(w, x, y, kernel=capi.KERNEL_GEMM_TC)
+        single.append(y)
+    ctx.sync()
+    l0 = ctx.launches
+    ys = [torch.zeros((M, w.N), device="cuda") for w in ws]
+    ctx.mul_mat_batch([(ws[0], xa, ys[0]), (ws[1], xa, ys[1]), (ws[2], xb, ys[2])], kernel=capi.KERNEL_GEMM_TC)
+    ctx.sync()
+    assert ctx.launches - l0 == 3 + 2  # three GEMMs, two quantisations
+    for a, b in zip(single, ys):
+        assert torch.equal(a, b)
+    zs = [torch.zeros((M, w.N), device="cuda") for w in ws]
+    ctx.mul_mat_batch([(ws[0], xa, zs[0]), (ws[2], xb, zs[2]), (ws[1], xa, zs[1])], kernel=capi.KERNEL_GEMM_TC)
+    ctx.sync()
+    for a, b in zip(single, zs):
+        assert torch.equal(a, b)
+    for w in ws:
+        w.free()
