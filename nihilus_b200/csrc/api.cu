@@ -352,7 +352,12 @@ namespace {
 		// ---- warp-per-row GEMV: the default ----
 		const bool f32act = act_mode == NHB_ACT_F32;
 		if (kernel == NHB_KERNEL_GEMV_ROWS) {
-			int mt_max = 4;
+			// rows per pass: 4 in general; up to 8 for the plain Q8 kernel on rows of one 4 KB item (K <= 4096), where a
+			// pass of 8 costs less than two passes of 4 over the weights
+			int mt_max = (f32act || ctx->rows_db || ctx->rows_cluster > 1 || ctx->norm_w || ctx->preq || M <= 4) ? 4 : 8;
+			for (int i = 0; i < n_ops; ++i)
+				if (ops[i].w->K > 4096)
+					mt_max = std::min(mt_max, 4);
 			for (int i = 0; i < n_ops; ++i)
 				while (mt_max > 0 && !gemv_rows_supports(ops[i].w->K, mt_max, f32act))
 					--mt_max;

@@ -655,7 +655,8 @@ namespace nhb {
 	}
 
 	bool gemv_rows_supports(int64_t K, int64_t M, bool f32act) {
-		return K % 32 == 0 && M >= 1 && M <= 4 && gemv_rows_act_bytes(K, static_cast<int>(M), f32act) <= 96 * 1024;
+		// up to 4 rows per pass in every shape of the kernel; 5 to 8 in the plain Q8 shape (8-warp CTAs, two per SM) only
+		return K % 32 == 0 && M >= 1 && M <= (f32act ? 4 : 8) && gemv_rows_act_bytes(K, static_cast<int>(M), f32act) <= 96 * 1024;
 	}
 
 	// `b` arrives with op pointers/shapes, act_off/slot tables and preq fields filled by the caller.
@@ -684,6 +685,15 @@ namespace nhb {
 			double_buffer	= false;
 			cluster			= 1;
 			split_long_rows = false;
+			ctas_per_sm		= 2;
+		}
+		if (M > 4) {// 5 to 8 rows per pass: one kernel shape (more rows per pass means more shared-memory traffic per weight byte, not more HBM)
+			if (b.f32act || b.norm_w)
+				return cudaErrorInvalidValue;
+			double_buffer	= false;
+			cluster			= 1;
+			split_long_rows = false;
+			fat_ctas		= false;
 			ctas_per_sm		= 2;
 		}
 		const bool fat	= fat_ctas && !double_buffer && cluster <= 1 && rows >= cfg.sm_count * ROWS_WARPS_FAT;
@@ -832,6 +842,20 @@ namespace nhb {
 		NHB_ROWS_CASE(4, 3)
 		NHB_ROWS_CASE(4, 4)
 #undef NHB_ROWS_CASE
+#define NHB_ROWS_WIDE_CASE(MT) \
+	if (M == MT) { \
+		auto kern = gemv_q8_rows<MT, 2>; \
+		e		  = cudaSuccess; \
+		if (smem > 48 * 1024) \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+		if (e == cudaSuccess) \
+			e = cudaLaunchKernelEx(&lc, kern, b); \
+	}
+		NHB_ROWS_WIDE_CASE(5)
+		NHB_ROWS_WIDE_CASE(6)
+		NHB_ROWS_WIDE_CASE(7)
+		NHB_ROWS_WIDE_CASE(8)
+#undef NHB_ROWS_WIDE_CASE
 #define NHB_ROWS_DB_CASE(MT) \
 	if (!b.f32act && !b.norm_w && double_buffer && M == MT) { \
 		auto kern = gemv_q8_rows_db<MT>; \

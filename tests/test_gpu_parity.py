@@ -478,3 +478,33 @@ def test_gemm_batch_sharing_its_input_quantises_once_and_is_bit_identical(ctx, c
         assert torch.equal(a, b)
     for w in ws:
         w.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,K,M", [(4096, 4096, 8), (1031, 4096, 5), (300, 512, 7), (14336, 4096, 6), (64, 32, 8)])
+def test_passes_of_up_to_eight_rows_are_bit_identical_to_passes_of_four(ctx, capi, oracle, N, K, M):
+    """5 to 8 tokens go through the decode GEMV in one pass (rows of one 4 KB item); the values are those of the
+    4-row passes -- the per-row arithmetic does not depend on how many rows share a pass -- and match the oracle."""
+    import torch
+
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    w = synth.make_weight(N, K, 500 + N)
+    x = synth.make_activation(M, K, 501 + M)
+    h = ctx.upload(w)
+    xd = torch.from_numpy(x).cuda()
+    y8 = torch.zeros((M, N), device="cuda")
+    l0 = ctx.launches
+    ctx.mul_mat(h, xd, y8, kernel=capi.KERNEL_GEMV_ROWS)
+    ctx.sync()
+    assert ctx.launches - l0 == 1
+    ctx.set_option("prequantize", 1)  # the separate quantiser keeps passes of four
+    y4 = torch.zeros((M, N), device="cuda")
+    ctx.mul_mat(h, xd, y4, kernel=capi.KERNEL_GEMV_ROWS)
+    ctx.sync()
+    ctx.set_option("prequantize", 0)
+    assert torch.equal(y8, y4)
+    ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
+    assert np.abs(y8.cpu().numpy() - ref).max() <= 1e-4 * np.abs(ref).max()
+    h.free()
