@@ -40,7 +40,6 @@ struct nhb_gguf {
 	// scalar key/values kept for the caller (numbers as double, strings verbatim)
 	std::map<std::string, double> numbers;
 	std::map<std::string, std::string> strings;
-	std::string err;
 };
 
 namespace {
