@@ -53,6 +53,7 @@ enum nhb_kernel {
 typedef struct nhb_ctx nhb_ctx;
 typedef struct nhb_weight nhb_weight;
 typedef struct nhb_graph nhb_graph;
+typedef struct nhb_chain nhb_chain;
 
 typedef struct nhb_weight_info {
 	int64_t N, K;	  /* full logical shape */
@@ -220,6 +221,22 @@ int nhb_mul_mat_q8_0_noalloc(const void* q_plane, const void* d_plane, int64_t r
 /* capacity of that array in bytes (98304) and the last error text of this thread for the call above */
 int64_t nhb_noalloc_max_bytes(void);
 const char* nhb_noalloc_last_error(void);
+
+/* ---- a token's whole sequence of dependent decode stages as ONE persistent kernel ----
+ * Stands in for what thread_pool<gpu>::execute_tasks does per token (cuda/thread_pool.hpp:46-67: the input core, the
+ * per-block cores of every layer, the output core, one after the other) on the mul_mat side of those cores.
+ * `ops` lists the stages back to back, ops_per_stage[s] (1..8) independent mul_mats each (q/k/v; o; gate/up; down; ...
+ * lm_head); every op of stage s+1 may read any output of stage s: a stage starts once the one before it has ended on
+ * the whole GPU (a device-side grid barrier with bounded waits), while the weight stream of the following stages is
+ * already running.  Q8 arithmetic, 1 <= M <= 4 (the same M in every op), K % 256 == 0, K <= 16384
+ * (NHB_ERR_UNSUPPORTED otherwise: run such stages with nhb_mul_mat_batch).  Results are bit-identical to
+ * nhb_mul_mat_batch stage by stage.  The op list is read at create time; the activations and outputs it names must stay
+ * valid for every launch.  One launch runs alone on the GPU (cooperative launch: one CTA per SM).  With world > 1 the rules
+ * of nhb_symm_alloc apply per stage: outputs in symmetric memory are delivered to every rank and the next stage waits
+ * for all ranks; the outputs of the LAST stage are whole after nhb_all_gather (or nhb_sync). */
+int nhb_chain_create(nhb_ctx* ctx, const nhb_mul_mat_op* ops, const int* ops_per_stage, int n_stages, nhb_chain** out);
+int nhb_chain_launch(nhb_ctx* ctx, nhb_chain* chain);
+int nhb_chain_free(nhb_ctx* ctx, nhb_chain* chain);
 
 /* ---- launch-overhead removal: record a sequence of nhb_mul_mat* calls once, replay it per token ---- */
 int nhb_graph_begin(nhb_ctx* ctx);

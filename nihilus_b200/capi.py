@@ -39,6 +39,7 @@ EXPORTS = (
     "nhb_rms_norm_mul", "nhb_rms_norm_mul_q8_0", "nhb_rms_norm_mul_mat_batch",
     "nhb_gguf_open", "nhb_gguf_last_error", "nhb_gguf_close", "nhb_gguf_tensor_count", "nhb_gguf_find", "nhb_gguf_tensor_get",
     "nhb_gguf_get_number", "nhb_gguf_get_string", "nhb_gguf_upload_q8_0", "nhb_gguf_read_f32",
+    "nhb_chain_create", "nhb_chain_launch", "nhb_chain_free",
 )
 
 
@@ -121,6 +122,9 @@ _sig("nhb_mul_mat_q8_0_noalloc", _i, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _i64,
 _sig("nhb_noalloc_max_bytes", _i64)
 _sig("nhb_noalloc_last_error", C.c_char_p)
 _sig("nhb_all_gather_batch", _i, _vp, C.POINTER(_vp), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), _i)
+_sig("nhb_chain_create", _i, _vp, C.POINTER(MulMatOp), C.POINTER(_i), _i, C.POINTER(_vp))
+_sig("nhb_chain_launch", _i, _vp, _vp)
+_sig("nhb_chain_free", _i, _vp, _vp)
 
 
 def _tensor_from_ptr(ptr: int, nbytes: int, device: int, dtype):
@@ -278,6 +282,22 @@ class Graph:
             self.handle = None
 
 
+class Chain:
+    """A token's sequence of dependent stages as one persistent kernel (nhb_chain_*)."""
+
+    def __init__(self, ctx: "Context", handle: int, keep):
+        self.ctx, self.handle, self._keep = ctx, handle, keep  # the tensors the chain names stay alive with it
+
+    def launch(self):
+        _check(lib.nhb_chain_launch(self.ctx.handle, self.handle), self.ctx.handle)
+
+    def free(self):
+        if self.handle:
+            lib.nhb_chain_free(self.ctx.handle, self.handle)
+            self.handle = None
+            self._keep = None
+
+
 class Context:
     """One GPU, one row shard (rank of world)."""
 
@@ -410,6 +430,17 @@ class Context:
 
     def memcpy_d2h(self, dst_ptr: int, src_ptr: int, nbytes: int):
         _check(lib.nhb_memcpy_d2h(self.handle, dst_ptr, src_ptr, nbytes), self.handle)
+
+    def chain(self, stages) -> Chain:
+        """stages: list of stages, each a list of (Weight, x, y); every stage may read the outputs of the one before."""
+        flat = [op for st in stages for op in st]
+        arr = (MulMatOp * max(len(flat), 1))()
+        for i, (w, x, y) in enumerate(flat):
+            arr[i] = MulMatOp(w.handle, x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.shape[0])
+        counts = (_i * max(len(stages), 1))(*[len(st) for st in stages])
+        h = _vp()
+        _check(lib.nhb_chain_create(self.handle, arr, counts, len(stages), C.byref(h)), self.handle)
+        return Chain(self, h.value, flat)
 
     # ---- graphs ----
     def graph_begin(self):

@@ -5,6 +5,7 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -69,6 +70,8 @@ namespace {
 	}
 
 	thread_local std::string g_err;
+	thread_local unsigned long long g_err_seq = 0;
+	std::atomic<unsigned long long> g_err_counter{ 0 };
 
 }
 
@@ -97,7 +100,7 @@ struct nhb_ctx {
 	int norm_sqrt		= 0;
 	void* norm_buf		= nullptr;// normalised f32 rows for the paths that quantise for themselves
 	size_t norm_cap		= 0;
-	int rows_db		   = 0;// warp-per-row GEMV: two items in flight per warp
+	int rows_db		   = -1;// warp-per-row GEMV: two items in flight per warp (1), one (0), or chosen per launch (-1)
 	int rows_cluster   = 1;// warp-per-row GEMV: CTAs per cluster sharing the activation quantisation
 	int rows_fat	   = 1;// warp-per-row GEMV: one 24-warp CTA per SM for launches with enough rows
 	int rows_split	   = 1;// ... and within those, the item-parallel kernel for rows longer than 4096
@@ -123,6 +126,10 @@ struct nhb_ctx {
 	size_t up_cap		   = 0;
 	unsigned* push_local = nullptr;// [0] CTAs done in the running launch, [1] fused launches completed
 	int fused_gather	 = 1;
+	bool pending_wait	 = false;// a delivering launch was enqueued and no later launch of this context has waited for the peers yet
+	long long peer_wait_us = 2000000;// bound of a kernel's wait for the other ranks' announcements
+	int symm_loopback	 = 0;// test aid: "peer" mappings alias this rank's own memory, so no announcement ever arrives
+	unsigned long long err_seq = 0;
 };
 
 struct nhb_weight {
@@ -134,6 +141,17 @@ struct nhb_weight {
 	int device	= 0;
 };
 
+// A recorded sequence of dependent decode stages (nhb_chain_*): one warp-per-row GEMV launch per stage, each told what the
+// next one will read first
+struct nhb_chain {
+	std::vector<rows_batch> stages;// launch descriptors, prefetch hints included
+	int M = 0;
+	std::vector<const void*> delivered;// outputs the launches complete on every rank
+	std::vector<const void*> written;// every output pointer they write
+	std::vector<char> delivers;// per stage: its rows go to the other ranks
+	int device = 0;
+};
+
 struct nhb_graph {
 	cudaGraph_t graph	 = nullptr;
 	cudaGraphExec_t exec = nullptr;
@@ -142,9 +160,12 @@ struct nhb_graph {
 namespace {
 
 	int fail(nhb_ctx* ctx, int code, const std::string& msg) {
-		g_err = msg;
-		if (ctx)
-			ctx->err = msg;
+		g_err	  = msg;
+		g_err_seq = ++g_err_counter;
+		if (ctx) {
+			ctx->err	 = msg;
+			ctx->err_seq = g_err_seq;
+		}
 		return code;
 	}
 
@@ -246,7 +267,13 @@ namespace {
 		reg.local			= static_cast<char*>(p);
 		reg.peer[ctx->rank] = reg.local;
 		cudaError_t e		= cudaMemsetAsync(p, 0, bytes, ctx->stream);
-		if (e == cudaSuccess && ctx->world > 1) {
+		if (e == cudaSuccess && ctx->world > 1 && ctx->symm_loopback) {
+			// every "peer" is this rank's own allocation: stores meant for the peers land on the values already there, and
+			// no other rank ever announces anything -- the waits of the following launches run into their time limit
+			for (int r = 0; r < ctx->world; ++r)
+				reg.peer[r] = reg.local;
+			e = cudaStreamSynchronize(ctx->stream);
+		} else if (e == cudaSuccess && ctx->world > 1) {
 			if (!ctx->comm) {
 				cudaFree(p);
 				return fail(ctx, NHB_ERR_NCCL, "symmetric memory needs nhb_comm_init first (the handles travel over NCCL)");
@@ -294,7 +321,7 @@ namespace {
 
 	void symm_release(nhb_ctx* ctx, nhb_ctx::symm_region& reg) {
 		for (int r = 0; r < ctx->world; ++r)
-			if (r != ctx->rank && reg.peer[r])
+			if (r != ctx->rank && reg.peer[r] && reg.peer[r] != reg.local)
 				cudaIpcCloseMemHandle(reg.peer[r]);
 		if (reg.local)
 			cudaFree(reg.local);
@@ -303,6 +330,18 @@ namespace {
 
 	// Fills the fused all-gather part of a warp-per-row launch when every output of the batch lies in symmetric memory.
 	// regions[0] is the control region holding the flag array.
+	// The waiting half: every launch of a context that has symmetric memory first waits for the other ranks' announcements.
+	void setup_peer_wait(nhb_ctx* ctx, push_ctl& pc) {
+		pc.status = ctx->dev_status;
+		if (ctx->world <= 1 || ctx->regions.empty() || !ctx->push_local)
+			return;
+		pc.wait_world  = ctx->world;
+		pc.rank		   = ctx->rank;
+		pc.wait_ns	   = static_cast<unsigned long long>(ctx->peer_wait_us) * 1000ull;
+		pc.epoch	   = ctx->push_local + 1;
+		pc.flags_local = reinterpret_cast<unsigned*>(ctx->regions[0].local);
+	}
+
 	bool setup_push(nhb_ctx* ctx, rows_batch& b, const nhb_mul_mat_op* const* src_ops, int mt, int64_t m0) {
 		if (ctx->world <= 1 || !ctx->fused_gather || ctx->regions.empty() || !ctx->push_local || b.n_ops == 0)
 			return false;
@@ -342,6 +381,83 @@ namespace {
 		return true;
 	}
 
+	// One launch's worth of ops as the warp-per-row kernels see them: this rank's row shard of every weight (ops it owns no
+	// rows of are left out), token rows [m0, m0 + mt), and one shared-memory slot per distinct activation input.  Returns
+	// the shared memory the quantised activations take.
+	size_t fill_rows_batch(const nhb_mul_mat_op* ops, int n_ops, int64_t m0, int mt, bool f32act, rows_batch& b, const nhb_mul_mat_op** src_ops) {
+		size_t off = 0;
+		for (int i = 0; i < n_ops; ++i) {
+			const nhb_weight* w = ops[i].w;
+			if (w->n1 == w->n0)
+				continue;
+			src_ops[b.n_ops] = &ops[i];
+			rows_op& ro		 = b.op[b.n_ops];
+			ro.wq			 = w->q;
+			ro.wd			 = w->d;
+			ro.x			 = ops[i].x + m0 * ops[i].ldx;
+			ro.y			 = ops[i].y + m0 * ops[i].ldy + w->n0;
+			ro.ldx			 = ops[i].ldx;
+			ro.ldy			 = ops[i].ldy;
+			ro.rows			 = static_cast<int>(w->n1 - w->n0);
+			ro.K			 = static_cast<int>(w->K);
+			int slot		 = -1;
+			for (int s = 0; s < b.n_slots; ++s) {
+				const rows_op& so = b.op[b.slot_op[s]];
+				if (so.x == ro.x && so.ldx == ro.ldx && so.K == ro.K)
+					slot = s;
+			}
+			if (slot < 0) {
+				b.slot_op[b.n_slots++] = b.n_ops;
+				ro.act_off			   = static_cast<int>(off);
+				ro.preq_off			   = static_cast<int>(off);
+				off += gemv_rows_act_bytes(ro.K, mt, f32act);
+			} else {
+				ro.act_off	= b.op[b.slot_op[slot]].act_off;
+				ro.preq_off = ro.act_off;
+			}
+			++b.n_ops;
+		}
+		b.act_bytes = static_cast<int>(off);
+		b.f32act	= f32act ? 1 : 0;
+		return off;
+	}
+
+	// Which register-fed kernel a launch takes.  A short launch (a q/k/v or attn_output stage: a few rows of one 4 KB item
+	// per warp) is over before a single-buffered warp has hidden one memory latency, so it runs the variant with two
+	// items in flight per warp, at two 8-warp CTAs per SM: everything it needs is then requested before it waits for
+	// the kernel in front of it (attn_output 6.1 -> 4.5 us, q+k+v 7.0 -> 6.1 us on a B200).  Long launches keep one 24-warp
+	// CTA per SM, whose steady state is faster (gate+up 21.6 against 23.0 us).  The choice never shows in the results.
+	bool pick_double_buffer(const nhb_ctx* ctx, const rows_batch& b, int mt, bool delivers) {
+		if (ctx->rows_db >= 0)
+			return ctx->rows_db != 0;
+		if (b.f32act || b.norm_w || b.preq || mt > 4 || delivers || ctx->rows_cluster > 1)
+			return false;
+		int64_t bytes = 0;
+		for (int i = 0; i < b.n_ops; ++i) {
+			if (b.op[i].K > 4096)
+				return false;
+			bytes += static_cast<int64_t>(b.op[i].rows) * (b.op[i].K + (b.op[i].K >> 4));
+		}
+		return bytes >= (int64_t(4) << 20) && bytes <= (int64_t(40) << 20);
+	}
+
+	// Rows delivered by a fused launch are whole on this rank only after the other ranks' announcements have arrived.  The
+	// decode GEMV kernels wait for them in their own prologue; in front of anything else that may read such rows this
+	// enqueues a one-warp kernel that does nothing but that (bounded) wait.
+	int wait_pending(nhb_ctx* ctx) {
+		if (!ctx->pending_wait)
+			return NHB_OK;
+		push_ctl pc{};
+		setup_peer_wait(ctx, pc);
+		int launches  = 0;
+		cudaError_t e = launch_peer_wait(pc, cfg_of(ctx), &launches);
+		if (e != cudaSuccess)
+			return fail_cuda(ctx, e, "peer-wait launch");
+		ctx->launches += launches;
+		ctx->pending_wait = false;
+		return NHB_OK;
+	}
+
 	// GEMV family over M rows (looping over row groups the kernels support)
 	int run_gemv(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int act_mode, int kernel) {
 		const int64_t M = ops[0].M;
@@ -351,10 +467,15 @@ namespace {
 			kernel = ctx->gemv_default;
 		// ---- warp-per-row GEMV: the default ----
 		const bool f32act = act_mode == NHB_ACT_F32;
+		if (!(kernel == NHB_KERNEL_GEMV_ROWS && !ctx->preq && !ctx->norm_w)) {
+			int rc = wait_pending(ctx);// kernels without the wait in their own prologue
+			if (rc != NHB_OK)
+				return rc;
+		}
 		if (kernel == NHB_KERNEL_GEMV_ROWS) {
 			// rows per pass: 4 in general; up to 8 for the plain Q8 kernel on rows of one 4 KB item (K <= 4096), where a
 			// pass of 8 costs less than two passes of 4 over the weights
-			int mt_max = (f32act || ctx->rows_db || ctx->rows_cluster > 1 || ctx->norm_w || ctx->preq || M <= 4) ? 4 : 8;
+			int mt_max = (f32act || ctx->rows_db > 0 || ctx->rows_cluster > 1 || ctx->norm_w || ctx->preq || M <= 4) ? 4 : 8;
 			for (int i = 0; i < n_ops; ++i)
 				if (ops[i].w->K > 4096)
 					mt_max = std::min(mt_max, 4);
@@ -377,47 +498,14 @@ namespace {
 					const int mt = static_cast<int>(std::min<int64_t>(mt_max, M - m0));
 					rows_batch b{};
 					const nhb_mul_mat_op* src_ops[NHB_MAX_BATCH];
-					size_t off = 0;
-					for (int i = 0; i < n_ops; ++i) {
-						const nhb_weight* w = ops[i].w;
-						if (w->n1 == w->n0)
-							continue;
-						src_ops[b.n_ops] = &ops[i];
-						rows_op& ro		 = b.op[b.n_ops];
-						ro.wq		= w->q;
-						ro.wd		= w->d;
-						ro.x		= ops[i].x + m0 * ops[i].ldx;
-						ro.y		= ops[i].y + m0 * ops[i].ldy + w->n0;
-						ro.ldx		= ops[i].ldx;
-						ro.ldy		= ops[i].ldy;
-						ro.rows		= static_cast<int>(w->n1 - w->n0);
-						ro.K		= static_cast<int>(w->K);
-						int slot	= -1;
-						for (int s = 0; s < b.n_slots; ++s) {
-							const rows_op& so = b.op[b.slot_op[s]];
-							if (so.x == ro.x && so.ldx == ro.ldx && so.K == ro.K)
-								slot = s;
-						}
-						if (slot < 0) {
-							b.slot_op[b.n_slots++] = b.n_ops;
-							ro.act_off			   = static_cast<int>(off);
-							ro.preq_off			   = static_cast<int>(off);
-							off += gemv_rows_act_bytes(ro.K, mt, f32act);
-						} else {
-							ro.act_off	= b.op[b.slot_op[slot]].act_off;
-							ro.preq_off = ro.act_off;
-						}
-						++b.n_ops;
-					}
+					const size_t off = fill_rows_batch(ops, n_ops, m0, mt, f32act, b, src_ops);
 					if (b.n_ops == 0)
 						break;
-					b.act_bytes = static_cast<int>(off);
-					b.f32act	= f32act ? 1 : 0;
 					// rms_norm in front of the quantiser: inside the GEMV when its rows fit the shared memory, else its own kernel
 					int rows_total = 0;
 					for (int i = 0; i < b.n_ops; ++i)
 						rows_total += b.op[i].rows;
-					const bool norm_inside = ctx->norm_w && !f32act && !ctx->rows_db && b.n_ops > 0 &&
+					const bool norm_inside = ctx->norm_w && !f32act && ctx->rows_db <= 0 && b.n_ops > 0 &&
 						gemv_rows_norm_inside(rows_total, off, b.op[0].K, mt, cfg.sm_count, ctx->rows_fat != 0);
 					if (norm_inside) {
 						b.norm_w	= ctx->norm_w;
@@ -450,14 +538,18 @@ namespace {
 					bool all_ranks_have_rows = true;
 					for (int i = 0; i < n_ops; ++i)
 						all_ranks_have_rows = all_ranks_have_rows && ops[i].w->N >= ctx->world;
-					const bool pushed = !ctx->rows_db && ctx->rows_cluster <= 1 && all_ranks_have_rows && setup_push(ctx, b, src_ops, mt, m0);
+					const bool pushed = ctx->rows_db <= 0 && ctx->rows_cluster <= 1 && all_ranks_have_rows && setup_push(ctx, b, src_ops, mt, m0);
 					if (pushed && m0 + mt >= M)
 						for (int i = 0; i < b.n_ops; ++i)
 							if (b.y_peer[i][0])
 								ctx->complete.push_back(src_ops[i]->y);
-					cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, ctx->rows_db != 0, ctx->rows_cluster, ctx->rows_fat != 0, ctx->rows_split != 0);
+					setup_peer_wait(ctx, b.push);
+					const bool db = pick_double_buffer(ctx, b, mt, pushed);
+					cudaError_t e = launch_gemv_rows(b, mt, cfg, db && ctx->rows_db < 0 ? 2 : ctx->rows_cps, &launches, db, ctx->rows_cluster, ctx->rows_fat != 0, ctx->rows_split != 0);
 					if (e != cudaSuccess)
 						return fail_cuda(ctx, e, "gemv_q8_rows launch");
+					if (b.push.wait_world > 1)
+						ctx->pending_wait = pushed;// this launch waited for everything before it; its own rows are the next launch's to wait for
 				}
 				ctx->launches += launches;
 				return NHB_OK;
@@ -534,6 +626,8 @@ namespace {
 			return NHB_OK;
 		const size_t need = gemm_tc_scratch_bytes(w->K, op.M);
 		int rc			  = ensure(ctx, &ctx->scratch, &ctx->scratch_cap, need, "GEMM scratch");
+		if (rc == NHB_OK)
+			rc = wait_pending(ctx);
 		if (rc != NHB_OK)
 			return rc;
 		int launches = 0;
@@ -583,7 +677,8 @@ int nhb_arch(void) {
 }
 
 const char* nhb_last_error(const nhb_ctx* ctx) {
-	if (ctx && !ctx->err.empty())
+	// the more recent of this context's last error and this thread's last error
+	if (ctx && !ctx->err.empty() && ctx->err_seq >= g_err_seq)
 		return ctx->err.c_str();
 	return g_err.c_str();
 }
@@ -703,7 +798,7 @@ int nhb_ctx_create(nhb_ctx** out, int device, int rank, int world) {
 	ctx->ctas_per_sm = env_int("NHB_CTAS_PER_SM", 1);
 	ctx->rows_cps	 = env_int("NHB_ROWS_CPS", 3);
 	ctx->preq		 = env_int("NHB_PREQ", 0);
-	ctx->rows_db	 = env_int("NHB_ROWS_DB", 0);
+	ctx->rows_db	 = env_int("NHB_ROWS_DB", -1);
 	ctx->rows_cluster = env_int("NHB_ROWS_CLUSTER", 1);
 	ctx->replicate_below = static_cast<int64_t>(std::max(0, env_int("NHB_REPLICATE_MB", 0))) << 20;
 	ctx->rows_fat	  = env_int("NHB_ROWS_FAT", 1);
@@ -736,6 +831,7 @@ int nhb_ctx_destroy(nhb_ctx* ctx) {
 	}
 	if (ctx->push_local)
 		cudaFree(ctx->push_local);
+
 	if (ctx->scratch)
 		cudaFree(ctx->scratch);
 	if (ctx->norm_buf)
@@ -780,7 +876,7 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 	else if (!std::strcmp(name, "prequantize"))
 		ctx->preq = value != 0;
 	else if (!std::strcmp(name, "rows_double_buffer"))
-		ctx->rows_db = value != 0;
+		ctx->rows_db = value < 0 ? -1 : (value != 0);
 	else if (!std::strcmp(name, "rows_cluster"))
 		ctx->rows_cluster = value < 1 ? 1 : value;
 	else if (!std::strcmp(name, "replicate_below_mb"))
@@ -795,7 +891,10 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 		if (value != NHB_KERNEL_GEMV_LDG && value != NHB_KERNEL_GEMV_STREAM && value != NHB_KERNEL_GEMV_ROWS)
 			return fail(ctx, NHB_ERR_ARG, "gemv_kernel must be 1, 2 or 4");
 		ctx->gemv_default = value;
-	}
+	} else if (!std::strcmp(name, "peer_wait_us"))
+		ctx->peer_wait_us = value < 1 ? 1 : value;
+	else if (!std::strcmp(name, "symm_loopback"))
+		ctx->symm_loopback = value != 0;
 	else
 		return fail(ctx, NHB_ERR_ARG, std::string("unknown option ") + name);
 	return NHB_OK;
@@ -809,11 +908,18 @@ int nhb_sync(nhb_ctx* ctx) {
 	if (!ctx)
 		return fail(nullptr, NHB_ERR_ARG, "null context");
 	device_guard g(ctx->device);
+	if (!ctx->capturing) {
+		int rc = wait_pending(ctx);// rows other ranks are still delivering belong to "everything enqueued so far"
+		if (rc != NHB_OK)
+			return rc;
+	}
 	NHB_CUDA(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, NHB_STATUS_WORDS * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
 	NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
 	if (ctx->host_status[0] != DEV_OK) {
 		const int code = ctx->host_status[0];
 		cudaMemsetAsync(ctx->dev_status, 0, NHB_STATUS_WORDS * sizeof(int), ctx->stream);
+		if (ctx->push_local)
+			cudaMemsetAsync(ctx->push_local, 0, sizeof(unsigned), ctx->stream);
 		cudaStreamSynchronize(ctx->stream);
 		return fail(ctx, NHB_ERR_TIMEOUT, "a device-side wait ran out (code " + std::to_string(code) + "); results of the last launches are invalid");
 	}
@@ -1103,6 +1209,8 @@ int nhb_quantize_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, int64_t M, 
 	if (!x_dev || !q_dev || !d_dev || (reinterpret_cast<uintptr_t>(x_dev) & 15) || (ldx & 3) || (reinterpret_cast<uintptr_t>(q_dev) & 15))
 		return fail(ctx, NHB_ERR_ARG, "nhb_quantize_q8_0: null or misaligned pointer");
 	device_guard g(ctx->device);
+	if (int rc = wait_pending(ctx); rc != NHB_OK)
+		return rc;
 	cudaError_t e = launch_quantize(x_dev, ldx, static_cast<int>(M), static_cast<int>(K), q_dev, d_dev, ctx->stream);
 	if (e != cudaSuccess)
 		return fail_cuda(ctx, e, "quantize_q8 launch");
@@ -1134,6 +1242,8 @@ int nhb_rms_norm_mul(nhb_ctx* ctx, const float* x_dev, int64_t ldx, const float*
 	if (!y_dev || (reinterpret_cast<uintptr_t>(y_dev) & 15) || (ldy & 3) || ldy < K)
 		return fail(ctx, NHB_ERR_ARG, "nhb_rms_norm_mul: null or misaligned output");
 	device_guard g(ctx->device);
+	if (int rcw = wait_pending(ctx); rcw != NHB_OK)
+		return rcw;
 	const norm_out no{ y_dev, ldy, nullptr, nullptr, nullptr };
 	cudaError_t e = launch_rms_norm(x_dev, ldx, norm_w_dev, eps, sqrt_mode, static_cast<int>(M), static_cast<int>(K), no, ctx->stream, ctx->pdl);
 	if (e != cudaSuccess)
@@ -1152,6 +1262,8 @@ int nhb_rms_norm_mul_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, const f
 	if (!blocks_dev || (reinterpret_cast<uintptr_t>(blocks_dev) & 1))
 		return fail(ctx, NHB_ERR_ARG, "nhb_rms_norm_mul_q8_0: null or odd output address");
 	device_guard g(ctx->device);
+	if (int rcw = wait_pending(ctx); rcw != NHB_OK)
+		return rcw;
 	const norm_out no{ nullptr, 0, nullptr, nullptr, static_cast<unsigned char*>(blocks_dev) };
 	cudaError_t e = launch_rms_norm(x_dev, ldx, norm_w_dev, eps, sqrt_mode, static_cast<int>(M), static_cast<int>(K), no, ctx->stream, ctx->pdl);
 	if (e != cudaSuccess)
@@ -1197,6 +1309,8 @@ int nhb_rms_norm_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_op
 	}
 	// everything else: normalised f32 rows through a scratch buffer, then the ordinary operator
 	rc = ensure(ctx, &ctx->norm_buf, &ctx->norm_cap, static_cast<size_t>(M) * K * 4, "rms_norm scratch");
+	if (rc == NHB_OK)
+		rc = wait_pending(ctx);
 	if (rc != NHB_OK)
 		return rc;
 	const norm_out no{ static_cast<float*>(ctx->norm_buf), K, nullptr, nullptr, nullptr };
@@ -1228,12 +1342,109 @@ int nhb_mul_mat_block_dots(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev
 		return rc;
 	int8_t* qa	  = static_cast<int8_t*>(ctx->scratch);
 	float* da	  = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + qb);
+	rc			  = wait_pending(ctx);
+	if (rc != NHB_OK)
+		return rc;
 	cudaError_t e = launch_quantize(x_dev, ldx, static_cast<int>(M), static_cast<int>(w->K), qa, da, ctx->stream);
 	if (e == cudaSuccess)
 		e = launch_block_dots(w->q, qa, static_cast<int>(rows), static_cast<int>(w->K), static_cast<int>(M), dots_dev, ctx->stream);
 	if (e != cudaSuccess)
 		return fail_cuda(ctx, e, "block-dot launch");
 	ctx->launches += 2;
+	return NHB_OK;
+}
+
+int nhb_chain_create(nhb_ctx* ctx, const nhb_mul_mat_op* ops, const int* ops_per_stage, int n_stages, nhb_chain** out) {
+	if (!ctx || !out || n_stages < 0 || (n_stages > 0 && (!ops || !ops_per_stage)))
+		return fail(ctx, NHB_ERR_ARG, "nhb_chain_create: bad arguments");
+	*out = nullptr;
+	nhb_chain* ch = new nhb_chain();
+	ch->device	  = ctx->device;
+	ch->stages.resize(static_cast<size_t>(n_stages));
+	ch->delivers.assign(static_cast<size_t>(n_stages), 0);
+	int64_t M				 = -1;
+	const nhb_mul_mat_op* op = ops;
+	for (int s = 0; s < n_stages; ++s) {
+		const int n = ops_per_stage[s];
+		if (n < 1 || n > NHB_MAX_BATCH) {
+			delete ch;
+			return fail(ctx, NHB_ERR_ARG, "nhb_chain_create: a stage holds 1 to 8 ops");
+		}
+		size_t act_total = 0;
+		for (int i = 0; i < n; ++i) {
+			int rc = check_mm_args(ctx, op[i].w, op[i].x, op[i].ldx, op[i].y, op[i].ldy, op[i].M);
+			if (rc == NHB_OK && M >= 0 && op[i].M != M)
+				rc = fail(ctx, NHB_ERR_ARG, "nhb_chain_create: all ops of a chain must share M");
+			if (rc == NHB_OK && (op[i].M < 1 || op[i].M > 4 || !gemv_rows_supports(op[i].w->K, op[i].M)))
+				rc = fail(ctx, NHB_ERR_UNSUPPORTED, "nhb_chain_create: needs 1 <= M <= 4 and rows the warp-per-row GEMV takes; run other stages with nhb_mul_mat_batch");
+			if (rc != NHB_OK) {
+				delete ch;
+				return rc;
+			}
+			M = op[i].M;
+		}
+		rows_batch& b = ch->stages[static_cast<size_t>(s)];
+		b			  = rows_batch{};
+		const nhb_mul_mat_op* src_ops[NHB_MAX_BATCH];
+		act_total = fill_rows_batch(op, n, 0, static_cast<int>(M), false, b, src_ops);
+		if (act_total > 96 * 1024) {
+			delete ch;
+			return fail(ctx, NHB_ERR_UNSUPPORTED, "nhb_chain_create: a stage's distinct activation inputs exceed the GEMV's shared memory");
+		}
+		bool all_ranks_have_rows = true;
+		for (int i = 0; i < n; ++i)
+			all_ranks_have_rows = all_ranks_have_rows && op[i].w->N >= ctx->world;
+		const bool pushed = b.n_ops > 0 && all_ranks_have_rows && setup_push(ctx, b, src_ops, static_cast<int>(M), 0);
+		setup_peer_wait(ctx, b.push);
+		for (int i = 0; i < n; ++i) {
+			ch->written.push_back(op[i].y);
+			if (op[i].w->n1 - op[i].w->n0 == op[i].w->N && ctx->world > 1)
+				ch->delivered.push_back(op[i].y);// replicated weight: this rank writes the whole row itself
+		}
+		for (int i = 0; i < b.n_ops && pushed; ++i)
+			if (b.y_peer[i][0])
+				ch->delivered.push_back(src_ops[i]->y);
+		ch->delivers[static_cast<size_t>(s)] = pushed ? 1 : 0;
+		op += n;
+	}
+	ch->M = static_cast<int>(M < 0 ? 0 : M);
+	*out = ch;
+	return NHB_OK;
+}
+
+int nhb_chain_launch(nhb_ctx* ctx, nhb_chain* ch) {
+	if (!ctx || !ch)
+		return fail(ctx, NHB_ERR_ARG, "nhb_chain_launch: null argument");
+	if (ch->device != ctx->device)
+		return fail(ctx, NHB_ERR_ARG, "nhb_chain_launch: the chain belongs to a context of another device");
+	if (ch->stages.empty() || ch->M == 0)
+		return NHB_OK;
+	device_guard g(ctx->device);
+	// what these launches write is this rank's slice only, except where they deliver the rows themselves
+	if (ctx->world > 1) {
+		auto& c = ctx->complete;
+		for (const void* y: ch->written)
+			c.erase(std::remove(c.begin(), c.end(), y), c.end());
+		for (const void* y: ch->delivered)
+			c.push_back(y);
+	}
+	const launch_cfg cfg = cfg_of(ctx);
+	int launches		 = 0;
+	for (size_t s = 0; s < ch->stages.size(); ++s) {
+		const bool db = pick_double_buffer(ctx, ch->stages[s], ch->M, ch->delivers[s] != 0);
+		cudaError_t e = launch_gemv_rows(ch->stages[s], ch->M, cfg, db && ctx->rows_db < 0 ? 2 : ctx->rows_cps, &launches, db, 1, ctx->rows_fat != 0, ctx->rows_split != 0);
+		if (e != cudaSuccess)
+			return fail_cuda(ctx, e, "gemv_q8_rows launch (chain)");
+		if (ch->stages[s].push.wait_world > 1)
+			ctx->pending_wait = ch->delivers[s] != 0;
+	}
+	ctx->launches += launches;
+	return NHB_OK;
+}
+
+int nhb_chain_free(nhb_ctx* ctx, nhb_chain* ch) {
+	(void)ctx;
+	delete ch;
 	return NHB_OK;
 }
 
@@ -1384,9 +1595,18 @@ int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, 
 	device_guard g(ctx->device);
 	// outputs a fused GEMV launch has already completed on every rank need no collective
 	auto is_complete = [&](const void* y) { return std::find(ctx->complete.begin(), ctx->complete.end(), y) != ctx->complete.end(); };
-	bool any_left	 = false;
-	for (int i = 0; i < n; ++i)
+	bool any_left = false, any_done = false;
+	for (int i = 0; i < n; ++i) {
 		any_left = any_left || !is_complete(y_dev[i]);
+		any_done = any_done || is_complete(y_dev[i]);
+	}
+	if (any_done) {
+		// delivered by a fused launch: whole once the other ranks' announcements are in (nothing to do for rows this rank
+		// computed itself from a replicated weight, or when a later launch has already waited)
+		int rc = wait_pending(ctx);
+		if (rc != NHB_OK)
+			return rc;
+	}
 	if (!any_left)
 		return NHB_OK;
 	nccl_api& nc = nccl();

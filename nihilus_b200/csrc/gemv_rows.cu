@@ -11,9 +11,7 @@
 // summation order depends on K only, so any row sharding gives bit-identical outputs.
 #include <algorithm>
 
-#include "internal.h"
-#include "ptx.cuh"
-#include "q8_device.cuh"
+#include "gemv_common.cuh"
 
 namespace nhb {
 
@@ -26,12 +24,6 @@ namespace nhb {
 		constexpr int ROWS_WARPS_FAT = 24;
 		constexpr int ROWS_TPB_FAT	 = ROWS_WARPS_FAT * 32;
 		constexpr int ITEM		 = 4;// 32-byte Q8 blocks per lane per step: 4 KB of a row per warp
-
-		__device__ __forceinline__ int rows_find_op(const rows_batch& b, int row, int cur) {
-			while (cur + 1 < b.n_ops && row >= b.op[cur + 1].row_begin)
-				++cur;
-			return cur;
-		}
 
 		struct blk32 {
 			uint4 lo, hi;
@@ -79,22 +71,6 @@ namespace nhb {
 			}
 		}
 
-		// Activations of one input in shared memory, per row m: the first 16 bytes of every block (uint4 [nb]), then the
-		// second 16 bytes (uint4 [nb]) -- two planes, so that a warp reading one block per lane touches consecutive
-		// 16-byte words (no bank conflicts) -- and after all MT rows the f32 scales [MT][nb].
-#ifdef NHB_ROWS_PROF
-		__device__ unsigned long long rows_prof[8];
-		__device__ __forceinline__ unsigned long long gtimer() {
-			unsigned long long t;
-			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-			return t;
-		}
-#define ROWS_STAMP(i) \
-	if (blockIdx.x == 0 && threadIdx.x == 0) \
-	rows_prof[i] = gtimer()
-#else
-#define ROWS_STAMP(i)
-#endif
 		template<int MT> __device__ __forceinline__ void compute_item(const item_regs& r, float (&acc)[MT], const unsigned char* act, int nb, int b0, int lane) {
 			const float* da = reinterpret_cast<const float*>(act + static_cast<size_t>(MT) * nb * QK);
 #pragma unroll
@@ -161,183 +137,6 @@ namespace nhb {
 			__syncthreads();
 		}
 
-		// Prologue of both GEMV variants: quantise every distinct input of the batch into shared memory.
-		template<int MT, bool NORM = false> __device__ __forceinline__ void quantize_inputs(const rows_batch& b, unsigned char* act_smem, int tid) {
-		const uint32_t cn = cluster_size();
-		const uint32_t cr = cluster_rank();
-		for (int s = 0; s < b.n_slots; ++s) {
-			const rows_op* op  = &b.op[b.slot_op[s]];
-			unsigned char* act = act_smem + op->act_off;
-			const int K		   = op->K;
-			const int nb	   = K >> 5;
-			float* sda		   = reinterpret_cast<float*>(act + static_cast<size_t>(MT) * K);
-			if constexpr (NORM) {
-				// rms_norm x norm-weight in front of the quantiser (rms_norm.cu has the arithmetic and its source):
-				// the rows are staged as f32, eight lanes per row run the sum-of-squares chains -- K / 8 dependent fma
-				// steps, which overlap the weight loads this CTA issued before it waited for the previous kernel -- and
-				// the quantiser below then reads (x * w) * scale instead of x.  Every CTA does this for itself: the
-				// rows are a few KB out of L2 and a separate kernel would put its launch on the critical path.
-				const int KS   = K + 8;// row stride: the MT chains of a step hit different banks
-				float* rows	   = reinterpret_cast<float*>(act_smem + b.norm_off);
-				float* prod	   = rows + MT * KS;// x * w, formed while the row is staged, so nothing is fetched after the chains
-				float* s_scale = prod + MT * KS;
-				const int k4   = K >> 2;
-				for (int i = tid; i < MT * k4; i += static_cast<int>(blockDim.x)) {
-					const int m		= i / k4;
-					const int j		= i - m * k4;
-					const float4 xv = __ldg(reinterpret_cast<const float4*>(op->x + static_cast<size_t>(m) * op->ldx) + j);
-					const float4 wv = __ldg(reinterpret_cast<const float4*>(b.norm_w) + j);
-					reinterpret_cast<float4*>(rows + m * KS)[j] = xv;
-					reinterpret_cast<float4*>(prod + m * KS)[j] =
-						make_float4(__fmul_rn(xv.x, wv.x), __fmul_rn(xv.y, wv.y), __fmul_rn(xv.z, wv.z), __fmul_rn(xv.w, wv.w));
-				}
-				__syncthreads();
-				ROWS_STAMP(2);
-				if (tid < 8 * MT) {
-					constexpr unsigned mask = MT >= 4 ? 0xffffffffu : ((1u << (8 * MT)) - 1u);
-					const float acc			= sum_squares_lane(rows + (tid >> 3) * KS + (tid & 7), K >> 3);
-					const float quad = __fadd_rn(acc, __shfl_down_sync(mask, acc, 4, 8));
-					const float dual = __fadd_rn(quad, __shfl_down_sync(mask, quad, 2, 8));
-					const float sum	 = __fadd_rn(dual, __shfl_down_sync(mask, dual, 1, 8));
-					if ((tid & 7) == 0) {
-						const float v = __fadd_rn(__fdiv_rn(sum, static_cast<float>(K)), b.norm_eps);
-						const float root =
-							b.norm_sqrt == NHB_SQRT_X86_FAST ? __uint_as_float(((__float_as_uint(v) + 0x3f800000u) >> 1) + 0x20000000u) : __fsqrt_rn(v);
-						s_scale[tid >> 3] = __fdiv_rn(1.0f, root);
-					}
-				}
-				ROWS_STAMP(3);
-				__syncthreads();
-				const int n = MT * nb * 2;// quantiser work items: half a block (16 values) each
-				for (int i = tid; i < n; i += static_cast<int>(blockDim.x)) {
-					const int hb	 = i >> 1;
-					const int m		 = hb / nb;
-					const int blk	 = hb - m * nb;
-					const float sc_n = s_scale[m];
-					const float4* p	 = reinterpret_cast<const float4*>(prod + m * KS + blk * QK) + (i & 1) * 4;
-					float4 v[4];
-#pragma unroll
-					for (int j = 0; j < 4; ++j) {
-						const float4 t = p[j];
-						v[j]		   = make_float4(__fmul_rn(t.x, sc_n), __fmul_rn(t.y, sc_n), __fmul_rn(t.z, sc_n), __fmul_rn(t.w, sc_n));
-					}
-					float amax		   = absmax4(v[0], absmax4(v[1], absmax4(v[2], absmax4(v[3], 0.f))));
-					amax			   = fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
-					const act_scale sc = q8_scales(amax);
-					reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] =
-						make_uint4(q8_pack4(v[0].x, v[0].y, v[0].z, v[0].w, sc.id), q8_pack4(v[1].x, v[1].y, v[1].z, v[1].w, sc.id),
-							q8_pack4(v[2].x, v[2].y, v[2].z, v[2].w, sc.id), q8_pack4(v[3].x, v[3].y, v[3].z, v[3].w, sc.id));
-					if ((i & 1) == 0)
-						sda[hb] = sc.d;
-				}
-				__syncthreads();// the staged rows are reused by the next slot
-			} else
-			if (b.preq) {
-				// quantised by quantize_q8_kernel into global scratch: int8 [MT][K] then f32 [MT][nb]
-				const unsigned char* src = b.preq_base + op->preq_off;
-				for (int i = tid; i < MT * nb * 2; i += static_cast<int>(blockDim.x)) {
-					const int hb  = i >> 1;
-					const int m	  = hb / nb;
-					const int blk = hb - m * nb;
-					reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K)[(i & 1) * nb + blk] = __ldg(reinterpret_cast<const uint4*>(src) + i);
-				}
-				const float* sd = reinterpret_cast<const float*>(src + static_cast<size_t>(MT) * K);
-				for (int i = tid; i < MT * nb; i += static_cast<int>(blockDim.x))
-					sda[i] = __ldg(sd + i);
-			} else {
-				// two threads per 32-wide block (16 floats each); the pair shares its absmax by shuffle.  In a cluster
-				// launch every CTA quantises 1/cn of the input and writes it into the shared memory of all cn CTAs.
-				const float* x		= op->x;
-				const long long ldx = op->ldx;
-				const int n			= MT * nb * 2;
-				const int per		= ((n / 2 + static_cast<int>(cn) - 1) / static_cast<int>(cn)) * 2;
-				const int i_begin	= static_cast<int>(cr) * per;
-				const int i_end		= min(n, i_begin + per);
-				for (int i = i_begin + tid; i < i_end; i += static_cast<int>(blockDim.x)) {
-					const int hb	= i >> 1;
-					const int m		= hb / nb;
-					const int blk	= hb - m * nb;
-					const float4* p = reinterpret_cast<const float4*>(x + static_cast<size_t>(m) * ldx + static_cast<size_t>(blk) * QK) + (i & 1) * 4;
-					const float4 v0 = __ldg(p), v1 = __ldg(p + 1), v2 = __ldg(p + 2), v3 = __ldg(p + 3);
-					float amax		= absmax4(v0, absmax4(v1, absmax4(v2, absmax4(v3, 0.f))));
-					amax			= fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
-					const act_scale sc = q8_scales(amax);
-					const uint4 qv	   = make_uint4(q8_pack4(v0.x, v0.y, v0.z, v0.w, sc.id), q8_pack4(v1.x, v1.y, v1.z, v1.w, sc.id),
-						   q8_pack4(v2.x, v2.y, v2.z, v2.w, sc.id), q8_pack4(v3.x, v3.y, v3.z, v3.w, sc.id));
-					uint4* dst		   = reinterpret_cast<uint4*>(act + static_cast<size_t>(m) * K) + ((i & 1) * nb + blk);
-					if (cn == 1) {
-						*dst = qv;
-						if ((i & 1) == 0)
-							sda[hb] = sc.d;
-					} else {
-						const uint32_t a_q = smem_u32(dst);
-						const uint32_t a_d = smem_u32(sda + hb);
-						for (uint32_t r = 0; r < cn; ++r) {
-							cluster_st_v4(cluster_map(a_q, r), qv);
-							if ((i & 1) == 0)
-								cluster_st_f32(cluster_map(a_d, r), sc.d);
-						}
-					}
-				}
-			}
-		}
-		// everyone's activations are complete (own writes and, in a cluster, the peers' remote stores)
-		if (cn == 1)
-			__syncthreads();
-		else
-			cluster_barrier();
-		}
-
-		__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
-			asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-		}
-		__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p) {
-			unsigned v;
-			asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-			return v;
-		}
-		__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-			unsigned v;
-			asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-			return v;
-		}
-
-		// End of a fused launch.  Every CTA orders its stores (CTA barrier, then a device-scope fence by thread 0) and
-		// counts itself done; the last one issues the launch's single system-scope fence, tells every rank "this rank
-		// has finished launch number e" and then waits, for a bounded time, until all ranks have said the same.
-		// System-scope fences wait for the stores that crossed NVLink to be acknowledged, so there is exactly one on the
-		// critical path; the polls are relaxed loads and one acquire load closes the wait.  Nothing here waits on a CTA
-		// of this grid that has not run yet, and a peer's flag only depends on that peer's own kernel, so ranks cannot
-		// wait on each other in a cycle.
-		__device__ __forceinline__ void push_finish(const push_ctl& pc, int tid) {
-			__syncthreads();
-			if (tid != 0)
-				return;
-			asm volatile("fence.acq_rel.gpu;" ::: "memory");
-			const unsigned prev = atomicAdd(pc.done_ctas, 1u);
-			if (prev != gridDim.x - 1)
-				return;
-			asm volatile("fence.acq_rel.sys;" ::: "memory");
-			const unsigned e = *reinterpret_cast<volatile unsigned*>(pc.epoch) + 1u;
-			for (int r = 0; r < pc.world; ++r)
-				st_relaxed_sys(pc.flags_peer[r] + pc.rank, e);
-			bool ok = true;
-			for (int r = 0; r < pc.world && ok; ++r) {
-				ok = false;
-				for (uint32_t i = 0; i < NHB_SPIN_LIMIT; ++i) {
-					if (static_cast<int>(ld_relaxed_sys(pc.flags_local + r) - e) >= 0) {
-						ok = static_cast<int>(ld_acquire_sys(pc.flags_local + r) - e) >= 0;
-						break;
-					}
-					if (i > 4096)
-						__nanosleep(20);
-				}
-			}
-			*reinterpret_cast<volatile unsigned*>(pc.done_ctas) = 0u;
-			*reinterpret_cast<volatile unsigned*>(pc.epoch)	   = e;
-			if (!ok)
-				atomicExch(pc.status, DEV_TIMEOUT_PEER);
-		}
 
 		// NORM: the rms_norm x norm-weight producer runs inside the prologue (its own instantiation, so that the plain
 		// kernels keep their register allocation)
@@ -361,15 +160,13 @@ namespace nhb {
 				load_item(regs, make_row(&b.op[cur], row0 - b.op[cur].row_begin), 0, lane);
 				pre = true;
 			}
-			ROWS_STAMP(0);
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
-			ROWS_STAMP(1);
+			push_wait_peers(b.push, tid);
 			if constexpr (F32)
 				stage_inputs_f32<MT>(b, act_smem, tid);
 			else
-				quantize_inputs<MT, NORM>(b, act_smem, tid);
-			ROWS_STAMP(4);
+				quantize_inputs<MT, NORM>(b, act_smem, tid, TPB);
 			// ---- rows ----
 			for (int row = row0; row < total_rows; row += W) {
 				while (cur + 1 < n_ops && row >= b.op[cur + 1].row_begin)
@@ -409,7 +206,6 @@ namespace nhb {
 						yrow[static_cast<size_t>(m) * ldy] = rowacc[m];
 				}
 			}
-			ROWS_STAMP(5);
 			if (b.push.world > 1) {
 				// Fused all-gather.  In pass i the warps of this CTA finished WARPS consecutive rows; once they are all
 				// written (CTA barrier) one warp per pass copies that run to every other rank in one coalesced store per
@@ -432,7 +228,7 @@ namespace nhb {
 						}
 					}
 				}
-				push_finish(b.push, tid);
+				push_announce(b.push, tid);
 			}
 		}
 
@@ -471,10 +267,11 @@ namespace nhb {
 			}
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
+			push_wait_peers(b.push, tid);
 			if constexpr (F32)
 				stage_inputs_f32<MT>(b, act_smem, tid);
 			else
-				quantize_inputs<MT>(b, act_smem, tid);
+				quantize_inputs<MT>(b, act_smem, tid, ROWS_TPB_FAT);
 			for (int it = warp; it < n_items; it += WARPS) {
 				const int rl  = it / ipr;
 				const int b0  = (it - rl * ipr) * 32 * ITEM;
@@ -520,7 +317,7 @@ namespace nhb {
 							b.y_peer[ocur][r][off] = v;
 			}
 			if (b.push.world > 1)
-				push_finish(b.push, tid);
+				push_announce(b.push, tid);
 		}
 
 		// ---- double-buffered variant: two 4 KB items in flight per warp ----
@@ -582,7 +379,8 @@ namespace nhb {
 			}
 			pdl_launch_dependents();
 			pdl_wait_prior_grids();
-			quantize_inputs<MT>(b, act_smem, tid);
+			push_wait_peers(b.push, tid);
+			quantize_inputs<MT>(b, act_smem, tid, ROWS_TPB);
 			float acc[MT], rowacc[MT];
 #pragma unroll
 			for (int m = 0; m < MT; ++m)
@@ -634,6 +432,30 @@ namespace nhb {
 		}
 	}
 
+	namespace {
+		__global__ void __launch_bounds__(32) peer_wait_kernel(const push_ctl pc) {
+			pdl_launch_dependents();
+			pdl_wait_prior_grids();
+			push_wait_peers(pc, threadIdx.x);
+		}
+	}
+
+	cudaError_t launch_peer_wait(const push_ctl& pc, const launch_cfg& cfg, int* launches) {
+		cudaLaunchConfig_t lc{};
+		lc.gridDim	= dim3(1);
+		lc.blockDim = dim3(32);
+		lc.stream	= cfg.stream;
+		cudaLaunchAttribute attr[1];
+		attr[0].id										   = cudaLaunchAttributeProgrammaticStreamSerialization;
+		attr[0].val.programmaticStreamSerializationAllowed = 1;
+		lc.attrs										   = attr;
+		lc.numAttrs										   = cfg.pdl ? 1 : 0;
+		cudaError_t e									   = cudaLaunchKernelEx(&lc, peer_wait_kernel, pc);
+		if (e == cudaSuccess && launches)
+			*launches += 1;
+		return e;
+	}
+
 	size_t gemv_rows_act_bytes(int64_t K, int M, bool f32act) {
 		const int64_t per_row = f32act ? K * 4 : K + (K / 32) * 4;
 		return static_cast<size_t>((M * per_row + 127) & ~int64_t(127));
@@ -659,6 +481,79 @@ namespace nhb {
 		return K % 32 == 0 && M >= 1 && M <= (f32act ? 4 : 8) && gemv_rows_act_bytes(K, static_cast<int>(M), f32act) <= 96 * 1024;
 	}
 
+	namespace {
+		struct rows_flags {
+			int ctas_per_sm;
+			bool double_buffer;
+			int cluster;
+			bool fat_ctas, split_long_rows;
+		};
+
+		// which of the options a batch of this kind can take; false = a combination no kernel shape serves
+		bool settle_flags(const rows_batch& b, int M, rows_flags& f) {
+			if (f.ctas_per_sm < 1)
+				f.ctas_per_sm = 1;
+			if (b.f32act) {// one shape family for the f32 mode: no double buffering, no clusters, 2 CTAs per SM when not fat
+				f.double_buffer = false;
+				f.cluster		= 1;
+				f.ctas_per_sm	= 2;
+			}
+			if (b.norm_w) {// the in-kernel rms_norm: two shapes only (24-warp CTAs, or 8-warp CTAs at two per SM), this CTA's shared memory only
+				if (b.f32act)
+					return false;
+				f.double_buffer	  = false;
+				f.cluster		  = 1;
+				f.split_long_rows = false;
+				f.ctas_per_sm	  = 2;
+			}
+			if (M > 4) {// 5 to 8 rows per pass: one kernel shape (more rows per pass means more shared-memory traffic per weight byte, not more HBM)
+				if (b.f32act || b.norm_w)
+					return false;
+				f.double_buffer	  = false;
+				f.cluster		  = 1;
+				f.split_long_rows = false;
+				f.fat_ctas		  = false;
+				f.ctas_per_sm	  = 2;
+			}
+			return true;
+		}
+
+		// one 24-warp CTA per SM when every one of those warps gets a row, else 8-warp CTAs
+		rows_shape shape_of(const rows_batch& b, int rows, int sm_count, rows_flags& f) {
+			rows_shape sh{};
+			sh.fat	 = f.fat_ctas && !f.double_buffer && f.cluster <= 1 && rows >= sm_count * ROWS_WARPS_FAT;
+			sh.warps = sh.fat ? ROWS_WARPS_FAT : ROWS_WARPS;
+			if (sh.fat)
+				f.ctas_per_sm = 1;
+			sh.grid		  = (rows + sh.warps - 1) / sh.warps;
+			const int cap = sm_count * f.ctas_per_sm;
+			if (sh.grid > cap) {
+				// even split: every warp gets ceil(rows / W) or one fewer rows, with as few short warps as possible
+				const int per_warp = (rows + cap * sh.warps - 1) / (cap * sh.warps);
+				sh.grid			   = (rows + per_warp * sh.warps - 1) / (per_warp * sh.warps);
+			}
+			// long rows: the item-parallel kernel, one CTA per SM, when all ops share K and a CTA's rows fit its partial-sum array
+			// (for rows of a single item the same distribution loses: decode set 4702 against 4884 GB/s)
+			sh.split = sh.fat && f.split_long_rows && (b.op[0].K >> 5) > 32 * ITEM && (b.op[0].K >> 5) <= 8 * 32 * ITEM &&
+				(rows + sm_count - 1) / sm_count <= SPLIT_MAX_ROWS;
+			for (int i = 1; i < b.n_ops && sh.split; ++i)
+				sh.split = b.op[i].K == b.op[0].K;
+			if (sh.split)
+				sh.grid = sm_count;
+			return sh;
+		}
+	}
+
+	rows_shape gemv_rows_shape(const rows_batch& b, int M, int sm_count, int ctas_per_sm, bool double_buffer, int cluster, bool fat_ctas, bool split_long_rows) {
+		rows_flags f{ ctas_per_sm, double_buffer, cluster, fat_ctas, split_long_rows };
+		int rows = 0;
+		for (int i = 0; i < b.n_ops; ++i)
+			rows += b.op[i].rows;
+		if (rows == 0 || !settle_flags(b, M, f))
+			return rows_shape{};
+		return shape_of(b, rows, sm_count, f);
+	}
+
 	// `b` arrives with op pointers/shapes, act_off/slot tables and preq fields filled by the caller.
 	cudaError_t launch_gemv_rows(const rows_batch& b_in, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer, int cluster, bool fat_ctas,
 		bool split_long_rows) {
@@ -671,50 +566,16 @@ namespace nhb {
 		b.total_rows = rows;
 		if (rows == 0)
 			return cudaSuccess;
-		if (ctas_per_sm < 1)
-			ctas_per_sm = 1;
-		// one 24-warp CTA per SM when every one of those warps gets a row, else 8-warp CTAs
-		if (b.f32act) {// one shape family for the f32 mode: no double buffering, no clusters, 2 CTAs per SM when not fat
-			double_buffer = false;
-			cluster		  = 1;
-			ctas_per_sm	  = 2;
-		}
-		if (b.norm_w) {// the in-kernel rms_norm: two shapes only (24-warp CTAs, or 8-warp CTAs at two per SM), this CTA's shared memory only
-			if (b.f32act)
-				return cudaErrorInvalidValue;
-			double_buffer	= false;
-			cluster			= 1;
-			split_long_rows = false;
-			ctas_per_sm		= 2;
-		}
-		if (M > 4) {// 5 to 8 rows per pass: one kernel shape (more rows per pass means more shared-memory traffic per weight byte, not more HBM)
-			if (b.f32act || b.norm_w)
-				return cudaErrorInvalidValue;
-			double_buffer	= false;
-			cluster			= 1;
-			split_long_rows = false;
-			fat_ctas		= false;
-			ctas_per_sm		= 2;
-		}
-		const bool fat	= fat_ctas && !double_buffer && cluster <= 1 && rows >= cfg.sm_count * ROWS_WARPS_FAT;
-		const int warps = fat ? ROWS_WARPS_FAT : ROWS_WARPS;
-		if (fat)
-			ctas_per_sm = 1;
-		int grid	  = (rows + warps - 1) / warps;
-		const int cap = cfg.sm_count * ctas_per_sm;
-		if (grid > cap) {
-			// even split: every warp gets ceil(rows / W) or one fewer rows, with as few short warps as possible
-			const int per_warp = (rows + cap * warps - 1) / (cap * warps);
-			grid			   = (rows + per_warp * warps - 1) / (per_warp * warps);
-		}
-		// long rows: the item-parallel kernel, one CTA per SM, when all ops share K and a CTA's rows fit its partial-sum array
-		// (for rows of a single item the same distribution loses: decode set 4702 against 4884 GB/s)
-		bool split = fat && split_long_rows && (b.op[0].K >> 5) > 32 * ITEM && (b.op[0].K >> 5) <= 8 * 32 * ITEM &&
-			(rows + cfg.sm_count - 1) / cfg.sm_count <= SPLIT_MAX_ROWS;
-		for (int i = 1; i < b.n_ops && split; ++i)
-			split = b.op[i].K == b.op[0].K;
-		if (split)
-			grid = cfg.sm_count;
+		rows_flags f{ ctas_per_sm, double_buffer, cluster, fat_ctas, split_long_rows };
+		if (!settle_flags(b, M, f))
+			return cudaErrorInvalidValue;
+		const rows_shape sh = shape_of(b, rows, cfg.sm_count, f);
+		ctas_per_sm			= f.ctas_per_sm;
+		double_buffer		= f.double_buffer;
+		cluster				= f.cluster;
+		const bool fat = sh.fat, split = sh.split;
+		const int warps = sh.warps;
+		int grid		= sh.grid;
 		if (b.norm_w)
 			b.norm_off = (b.act_bytes + 127) & ~127;
 		const size_t smem = b.norm_w ? static_cast<size_t>(b.norm_off) + gemv_rows_norm_bytes(b.op[0].K, M) : static_cast<size_t>(b.act_bytes);
@@ -752,12 +613,12 @@ namespace nhb {
 		e = cudaSuccess; \
 		if (fat) { \
 			auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT, false, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} else { \
 			auto kern = gemv_q8_rows<MT, 2, ROWS_TPB, false, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} \
@@ -772,17 +633,17 @@ namespace nhb {
 		e = cudaSuccess; \
 		if (split) { \
 			auto kern = gemv_q8_rows_split<MT, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} else if (fat) { \
 			auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} else { \
 			auto kern = gemv_q8_rows<MT, 2, ROWS_TPB, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} \
@@ -796,8 +657,8 @@ namespace nhb {
 	if (!b.f32act && !b.norm_w && split && M == MT) { \
 		auto kern = gemv_q8_rows_split<MT>; \
 		e		  = cudaSuccess; \
-		if (smem > 40 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+		if (smem > 32 * 1024) /* the kernel also has static shared memory */ \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -811,7 +672,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -825,7 +686,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows<MT, OCC>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -847,7 +708,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows<MT, 2>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -861,7 +722,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows_db<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -877,8 +738,3 @@ namespace nhb {
 
 }
 
-#ifdef NHB_ROWS_PROF
-extern "C" int nhb_debug_rows_prof(unsigned long long* out8) {
-	return static_cast<int>(cudaMemcpyFromSymbol(out8, nhb::rows_prof, 64));
-}
-#endif

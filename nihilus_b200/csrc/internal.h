@@ -53,14 +53,18 @@ namespace nhb {
 		int pad;
 	};
 
-	// Fused all-gather of the decode GEMV: every rank stores its output values straight into all ranks' copies of
-	// the output (peer-mapped memory) and the last CTA of the grid trades "done" flags with the peers before it exits,
-	// so the kernel's completion means the whole row is there on this rank.
+	// Fused all-gather of the decode GEMV.  A delivering launch (world > 1) stores its output values straight into all
+	// ranks' copies of the output (peer-mapped memory) and its last CTA announces "this rank has finished launch e" in a
+	// flag array on every rank.  Every launch of such a context (wait_world > 1) first waits, for a bounded time, until all
+	// ranks have announced the launches this rank has completed, so the rows it reads are whole.
 	struct push_ctl {
-		int world;// 0 or 1: not a fused launch
+		int world;// > 1: this launch delivers its rows to the other ranks
+		int wait_world;// > 1: wait for the other ranks' announcements before reading activations
 		int rank;
+		int pad;
+		unsigned long long wait_ns;// bound of that wait
 		unsigned* done_ctas;// local: CTAs of this grid that have stored everything
-		unsigned* epoch;// local: number of fused launches completed on this rank
+		unsigned* epoch;// local: number of delivering launches completed on this rank
 		unsigned* flags_local;// [world], written by the peers: their epoch after their matching launch
 		unsigned* flags_peer[NHB_MAX_WORLD];// the same array on every rank (this rank's own included)
 		int* status;// the context's device status word
@@ -109,6 +113,15 @@ namespace nhb {
 	bool gemv_rows_supports(int64_t K, int64_t M, bool f32act = false);
 	cudaError_t launch_gemv_rows(const rows_batch& b, int M, const launch_cfg& cfg, int ctas_per_sm, int* launches, bool double_buffer = false, int cluster = 1,
 		bool fat_ctas = false, bool split_long_rows = false);
+	// the CTA shape launch_gemv_rows takes for this batch: grid size, and whether CTAs get contiguous row ranges (split)
+	struct rows_shape {
+		int grid, warps;
+		bool fat, split;
+	};
+	rows_shape gemv_rows_shape(const rows_batch& b, int M, int sm_count, int ctas_per_sm, bool double_buffer, int cluster, bool fat_ctas, bool split_long_rows);
+	// a one-warp kernel that only waits for the other ranks' announcements (for consumers that are not GEMV launches)
+	cudaError_t launch_peer_wait(const push_ctl& pc, const launch_cfg& cfg, int* launches);
+
 	cudaError_t launch_block_dots(const int8_t* wq, const int8_t* qa, int rows, int K, int M, int32_t* dots, cudaStream_t s);
 
 	// rms_norm.cu: any subset of the three outputs (null = not wanted)
