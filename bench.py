@@ -3,11 +3,13 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One step = one token's worth of Q8_0 mul_mats: 32 layers x (q, k, v, o, gate, up, down) + lm_head =
-225 matrices, 7.97 GB of Q8_0 weights streamed once.  With N > 1 (torchrun, one rank per GPU) every
-weight is row-sharded over the ranks and each stage's output slices are all-gathered with NCCL.
-Prints ONE JSON line (rank 0).  `--impl reference` times the reference's own CPU row-dot code
-(oracle/_ref, built from the reference sources) on the host cores instead.
+One step = one token's worth of Q8_0 mul_mats: 32 layers x (q, k, v | o | gate, up | down) + lm_head =
+225 matrices in 129 dependent stages, 7.97 GB of Q8_0 weights streamed once.  The independent projections of a
+stage share one launch and one input vector (q/k/v read the same normalised row, gate/up likewise, as in the
+reference's graph: include/nihilus-incl/infra/core_traits.hpp:575-594, 976-980).  With N > 1 (torchrun, one rank per
+GPU) the larger weights are row-sharded over the ranks and every stage's output slices are delivered to all ranks
+before the next stage reads them.  Prints ONE JSON line (rank 0).  `--impl reference` times the reference's own CPU
+row-dot code (oracle/_ref, built from the reference sources) on the host cores instead, on the same 225 matrices.
 """
 from __future__ import annotations
 
@@ -28,6 +30,7 @@ from nihilus_b200 import shapes, synth  # noqa: E402
 METRIC = "q8_0_mul_mat_decode_set_hbm_gbs"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
+DTYPE = "i8xi8->i32, f32 scales"
 # dram__bytes_read.sum + dram__bytes_write.sum of one full step (129 GEMV launches), from an ncu capture of one layer +
 # lm_head scaled to 32 layers (every layer repeats the captured shapes): profiles/gemv_q8_rows_decode_set.md
 NCU_DRAM_BYTES_PER_STEP = 8094.8e6
@@ -43,13 +46,14 @@ def measured_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML every few milliseconds; `window` picks the samples that fell
+    inside the timed region."""
 
-    def __init__(self, index: int, period: float = 0.05):
+    def __init__(self, index: int, period: float = 0.002):
         super().__init__(daemon=True)
         self.period = period
-        self.samples: list[int] = []
-        self.reasons: set[str] = set()
+        self.samples: list[tuple[float, int]] = []
+        self.reasons: list[tuple[float, str]] = []
         self.max_mhz = None
         self._halt = threading.Event()
         self.ok = False
@@ -77,11 +81,12 @@ class ClockSampler(threading.Thread):
         }
         while not self._halt.is_set():
             try:
-                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                now = time.perf_counter()
+                self.samples.append((now, int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))))
                 mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
                 for bit, name in names.items():
                     if mask & bit:
-                        self.reasons.add(name)
+                        self.reasons.append((now, name))
             except Exception:
                 pass
             time.sleep(self.period)
@@ -89,11 +94,15 @@ class ClockSampler(threading.Thread):
     def stop(self):
         self._halt.set()
         self.join(timeout=2)
-        med = int(np.median(self.samples)) if self.samples else None
-        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+    def window(self, t0: float, t1: float):
+        inside = [mhz for t, mhz in self.samples if t0 <= t <= t1]
+        return {"sm_mhz": int(np.median(inside)) if inside else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted({n for t, n in self.reasons if t0 <= t <= t1}), "samples": len(inside),
+                "sampling": "NVML every %.0f ms; samples taken between the start and the end of the timed region" % (self.period * 1e3)}
 
 
-def host_weights(layers_unique: int = 1):
+def host_weights():
     """Unique host tensors: one layer's seven projections + lm_head (other layers are row rotations)."""
     t0 = time.time()
     base = {}
@@ -102,31 +111,101 @@ def host_weights(layers_unique: int = 1):
     return base, time.time() - t0
 
 
-def cpu_reference_run(base, seconds_target: float, threads: int):
-    """Times the reference's CPU row-dot code (oracle/_ref) or, if absent, the oracle port, on a bounded sample:
-    layer-0's seven matrices + lm_head at batch 1, repeated until ~seconds_target of CPU work."""
-    from oracle import pyoracle as po
+def layer_weight(base, name, layer):
+    return base[name] if layer <= 0 else synth.roll_rows(base[name], 17 * layer)
 
-    po.build()
-    if po.Reference.available():
-        impl, kind = po.Reference(), "reference"
-        run = lambda w, x: impl.mul_mat(0, w, x, threads=threads)  # noqa: E731
-    else:
-        impl, kind = po.Oracle(), "port"
-        run = lambda w, x: impl.mul_mat(po.Q8ACT_LANES, w, x, threads=threads)  # noqa: E731
-    xs = {name: synth.make_activation(1, k, synth.seed_for(2, name, "activations")) for name, (n, k) in shapes.LLAMA3_8B.items()}
-    nbytes = sum(shapes.mul_mat_bytes(n, k, 1) for n, k in shapes.LLAMA3_8B.values())
-    run(base["attn_k"], xs["attn_k"])  # warm
+
+# ---------------------------------------------------------------------------------------------------------------
+# CPU legs: the reference's own row-dot code (oracle/_ref) or, where it could not be built, the oracle port.
+# The only place in this file that touches oracle/.
+# ---------------------------------------------------------------------------------------------------------------
+class CpuSet:
+    """The decode set on the host: every one of the 225 matrices materialised (rows rotated per layer exactly as the GPU
+    upload does) when the machine has the memory for it, otherwise layer 0's matrices stand in for every layer."""
+
+    def __init__(self, base, layers: int):
+        from oracle import pyoracle as po
+
+        po.build()
+        if po.Reference.available():
+            self.impl, self.kind = po.Reference(), "reference"
+            self.q8_mode = 0
+        else:
+            self.impl, self.kind = po.Oracle(), "port"
+            self.q8_mode = po.Q8ACT_LANES
+        self.po = po
+        self.ops = shapes.decode_set(layers)
+        need = sum(n * (k // 32) * 34 for _, _, n, k in self.ops)
+        try:
+            import psutil
+
+            avail = psutil.virtual_memory().available
+        except Exception:
+            avail = 0
+        self.distinct = avail > need + (6 << 30)
+        self.mats = []
+        for name, layer, n, k in self.ops:
+            self.mats.append(layer_weight(base, name, layer) if self.distinct else base[name])
+        self.xs = {k: synth.make_activation(1, k, synth.seed_for(2, "attn_q", "activations") + k) for k in {k for _, _, _, k in self.ops}}
+        self.nbytes = sum(shapes.mul_mat_bytes(n, k, 1) for _, _, n, k in self.ops)
+
+    def run(self, w, x, threads):
+        return self.impl.mul_mat(self.q8_mode, w, x, threads=threads)
+
+    def step(self, threads: int) -> float:
+        t0 = time.perf_counter()
+        for (name, layer, n, k), w in zip(self.ops, self.mats):
+            self.run(w, self.xs[k], threads)
+        return time.perf_counter() - t0
+
+    def describe(self, threads):
+        return ("all %d matrices of the set at M=1 (%.2f GB of Q8_0 per pass; %s), %d host threads, row-partitioned" %
+                (len(self.ops), self.nbytes / 1e9, ("%d distinct host copies" % len(self.ops)) if self.distinct else "layer 0's matrices reused for every layer: not enough host memory for a copy of each", threads))
+
+
+def cpu_baseline_leg(base, layers, seconds_target: float, gpu_check=None):
+    """Bounded CPU sample for the repo arm's JSON line (N = 1, rank 0): the full set on all host threads, a one-thread leg
+    on layer 0 + lm_head (how the reference's eval dispatcher ran it, cpu/avx_2.hpp:4983-4984), a 512-token prefill
+    leg, and -- the oracle as checker -- parity of outputs the timed GPU run left behind."""
+    threads = os.cpu_count() or 1
+    cs = CpuSet(base, layers)
+    cs.step(threads)  # warm
     times = []
     t_end = time.time() + seconds_target
-    while True:
-        t0 = time.perf_counter()
-        for name in shapes.LLAMA3_8B:
-            run(base[name], xs[name])
-        times.append(time.perf_counter() - t0)
-        if time.time() >= t_end or len(times) >= 50:
-            break
-    return kind, nbytes, times
+    while time.time() < t_end and len(times) < 50:
+        times.append(cs.step(threads))
+    out = {"value": cs.nbytes / float(np.mean(times)) / 1e9, "unit": UNIT, "cores": threads, "kind": cs.kind,
+           "sample": cs.describe(threads) + ", %d passes" % len(times)}
+    # one thread: layer 0's seven matrices + lm_head
+    idx = [i for i, (name, layer, n, k) in enumerate(cs.ops) if layer <= 0]
+    nb1 = sum(shapes.mul_mat_bytes(cs.ops[i][2], cs.ops[i][3], 1) for i in idx)
+    t0 = time.perf_counter()
+    for i in idx:
+        cs.run(cs.mats[i], cs.xs[cs.ops[i][3]], 1)
+    out["one_thread"] = {"value": nb1 / (time.perf_counter() - t0) / 1e9, "unit": UNIT, "cores": 1,
+                         "sample": "layer 0 q,k,v,o,gate,up,down + lm_head at M=1 (%.2f GB), one pass" % (nb1 / 1e9)}
+    # prefill on the CPU: 512 tokens x 2048 rows of ffn_gate (a bounded slice of configs[3])
+    rows = 2048
+    wg = base["ffn_gate"][:rows]
+    xp = synth.make_activation(512, shapes.E, 5)
+    t0 = time.perf_counter()
+    cs.run(wg, xp, threads)
+    dt = time.perf_counter() - t0
+    out["prefill_m512"] = {"value": shapes.mul_mat_flops(rows, shapes.E, 512) / dt / 1e9, "unit": "GFLOP/s", "cores": threads,
+                           "sample": "512 tokens x %d rows of ffn_gate (K = 4096), Q8_0-quantised activations, one pass" % rows}
+    parity = None
+    if gpu_check is not None:
+        from oracle import pyoracle as po
+
+        orc = po.Oracle()
+        parity = {"tolerance": 1e-4, "cases": {}}
+        for label, w, x, y, rows_idx in gpu_check:
+            ref = orc.mul_mat(po.Q8ACT_LANES, w if rows_idx is None else w[rows_idx], x)
+            got = y if rows_idx is None else y[:, rows_idx]
+            parity["cases"][label] = float(np.abs(got - ref).max() / np.abs(ref).max())
+        parity["max_rel"] = max(parity["cases"].values())
+        parity["ok"] = parity["max_rel"] <= 1e-4
+    return out, parity
 
 
 def run_reference_arm(args):
@@ -135,42 +214,50 @@ def run_reference_arm(args):
         return
     threads = os.cpu_count() or 1
     base, _ = host_weights()
-    per_step_target = 2.0
-    all_times = []
-    kind, nbytes = "reference", 0
-    for _ in range(args.warmup + args.steps):
-        kind, nbytes, times = cpu_reference_run(base, per_step_target, threads)
-        all_times.append(float(np.mean(times)))
-        if len(all_times) >= 8:  # bounded: the whole arm stays within a few minutes
-            break
-    timed = all_times[min(args.warmup, len(all_times) - 1):]
-    sec = float(np.mean(timed))
-    value = nbytes / sec / 1e9
-    sample = "layer-0 q,k,v,o,gate,up,down + lm_head at M=1 (790 MB of Q8_0 per pass), all host threads, row-partitioned"
+    cs = CpuSet(base, args.layers)
+    for _ in range(args.warmup):
+        cs.step(threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cs.step(threads)
+    sec = (time.perf_counter() - t0) / args.steps
+    value = cs.nbytes / sec / 1e9
+    weight_bytes = sum(n * (k // 32) * 34 for _, _, n, k in cs.ops)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": len(timed), "warmup": args.warmup,
-        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "i8xi8->i32, f32 scales",
-        "data": "synthetic",
-        "config": {"workload": "configs[2]: LLaMA-3-8B full decode matmul set, batch 1 (bounded sample: 8 of 225 matrices per pass)",
-                   "act_mode": "q8_0 activations"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": workload_config(args.layers, len(cs.ops), weight_bytes, "q8"),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": cs.kind, "sample": cs.describe(threads)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def prefill_run(ctx, stream, torch, ops, weights, timed, world, M=512, iters=10):
+def workload_config(layers, n_ops, weight_bytes, act_mode):
+    return {
+        "workload": "configs[2]: LLaMA-3-8B full decode matmul set, batch 1: %d layers x (q,k,v,o,gate,up,down) + lm_head = %d Q8_0 mul_mats, "
+                    "%.3f GB of Q8_0 weights per step" % (layers, n_ops, weight_bytes / 1e9),
+        "act_mode": "q8_0 activations (reference quantiser), exact int8 block dots" if act_mode == "q8" else "f32 activations x dequantised weights",
+    }
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# GPU legs that ride along in the JSON line, outside the timed region
+# ---------------------------------------------------------------------------------------------------------------
+def prefill_run(ctx, stream, torch, ops, weights, base, timed, world, M=512, iters=10):
     """configs[3]: a 512-token activation matrix times layer 0's gate, up and down weights (this rank's row shards).
-    Returns whole-job TFLOP/s (2*M*N*K flops per mul_mat) and the fraction of the measured dense bf16 peak per GPU."""
+    Returns whole-job TFLOP/s (2*M*N*K flops per mul_mat), the fraction of the measured dense bf16 peak per GPU, and
+    the parity inputs (outputs of the timed kernels) for the CPU checker."""
     by_name = {}
     for i, (name, layer, n, k) in enumerate(ops):
         if layer == 0 and name in ("ffn_gate", "ffn_up", "ffn_down"):
             by_name[name] = (weights[i], n, k)
     if len(by_name) != 3:
-        return None
-    out = {}
+        return None, []
+    out, checks = {}, []
+    xh = {k: synth.make_activation(M, k, 777 + k) for k in {v[2] for v in by_name.values()}}
     with torch.cuda.stream(stream):
-        xs = {k: torch.randn((M, k), device="cuda") for k in {v[2] for v in by_name.values()}}
+        xs = {k: torch.from_numpy(v).cuda() for k, v in xh.items()}
         ys = {name: torch.zeros((M, n), device="cuda") for name, (_, n, _) in by_name.items()}
     stream.synchronize()
     flops_total, ms_sum = 0, 0.0
@@ -180,14 +267,19 @@ def prefill_run(ctx, stream, torch, ops, weights, timed, world, M=512, iters=10)
             fn()
         ctx.sync()
         ms = timed(fn, iters) / iters
-        out[name] = {"N": n, "K": k, "M": M, "ms": ms, "tflops": shapes.mul_mat_flops(n, k, M) / (ms * 1e-3) / 1e12}
+        plan = ctx.capi.gemm_tile_plan(w.n1 - w.n0, M)
+        out[name] = {"N": n, "K": k, "M": M, "ms": ms, "tflops": shapes.mul_mat_flops(n, k, M) / (ms * 1e-3) / 1e12,
+                     "tile": "%s x %d" % ("tokens on lanes" if plan["swapped"] else "rows on lanes", plan["tile_cols"])}
         flops_total += shapes.mul_mat_flops(n, k, M)
         ms_sum += ms
+        # this rank's rows of the output the timed kernel wrote, a strided subset of them for the CPU checker
+        idx = np.arange(w.n0, w.n1, 37)
+        checks.append(("prefill_%s_m%d" % (name, M), base[name], xh[k], ys[name].cpu().numpy(), idx))
     _, tf_peak, kind = measured_peaks()
     agg = flops_total / (ms_sum * 1e-3) / 1e12
-    return {"workload": "configs[3]: M=512 x (gate, up 14336x4096; down 4096x14336), Q8_0 weights, Q8_0-quantised activations",
-            "tflops": agg, "per_gpu_tflops": agg / world, "frac_of_bf16_peak": agg / world / tf_peak, "peak_tflops": tf_peak, "peak_kind": kind,
-            "per_op": out, "note": "outside the timed decode region; weights of one layer (187 MB) exceed L2"}
+    return ({"workload": "configs[3]: M=512 x (gate, up 14336x4096; down 4096x14336), Q8_0 weights, Q8_0-quantised activations",
+             "tflops": agg, "per_gpu_tflops": agg / world, "frac_of_bf16_peak": agg / world / tf_peak, "peak_tflops": tf_peak, "peak_kind": kind,
+             "per_op": out, "note": "outside the timed decode region; weights of one layer (187 MB) exceed L2"}, checks)
 
 
 def norm_run(ctx, stream, torch, ops, weights, timed, iters=20):
@@ -253,14 +345,38 @@ def norm_run(ctx, stream, torch, ops, weights, timed, iters=20):
     return out
 
 
+def noalloc_run(ctx, stream, torch, ops, weights, timed, iters=20):
+    """The allocation-free entry point (nhb_mul_mat_q8_0_noalloc) on the attn_q weights of up to 8 layers, M = 1: per call
+    one quantise launch + one GEMV launch from raw plane pointers."""
+    capi = ctx.capi
+    ws = [(weights[i], n, k) for i, (name, layer, n, k) in enumerate(ops) if name == "attn_q" and weights[i].n1 - weights[i].n0 == n][:8]
+    if not ws:
+        return None
+    with torch.cuda.stream(stream):
+        x = torch.randn((1, ws[0][2]), device="cuda")
+        ys = [torch.zeros((1, n), device="cuda") for _, n, _ in ws]
+
+    def run():
+        for (w, n, k), y in zip(ws, ys):
+            rc = capi.lib.nhb_mul_mat_q8_0_noalloc(w.q_ptr, w.d_ptr, n, k, x.data_ptr(), k, y.data_ptr(), n, 1, stream.cuda_stream)
+            if rc != 0:
+                raise RuntimeError(capi.lib.nhb_noalloc_last_error().decode())
+
+    run()
+    stream.synchronize()
+    ms = timed(run, iters) / iters
+    nbytes = sum(shapes.mul_mat_bytes(n, k, 1) for _, n, k in ws)
+    return {"workload": "attn_q 4096x4096, M=1, %d layers in rotation (%.0f MB), host-issued calls (no graph)" % (len(ws), nbytes / 1e6),
+            "us_per_call": ms * 1e3 / len(ws), "gbs": nbytes / (ms * 1e-3) / 1e9}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=shapes.L, help="debug: fewer layers (the reported workload is 32)")
-    ap.add_argument("--group", default="stage", choices=["stage", "op"], help="ops launched together: independent ops of a stage, or one by one")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--act-mode", default="q8", choices=["q8", "f32"],
                     help="q8: activations quantised to Q8_0, exact int8 block dots (the reported metric); f32: f32 activations x dequantised weights")
@@ -270,7 +386,7 @@ def main():
                     help="N > 1: outputs completed by the GEMV's own peer stores (fused) or by a grouped NCCL all-gather per stage")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the 512-token GEMM and the rms_norm figures that ride along in the JSON line")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 512-token GEMM, the rms_norm and the no-alloc figures that ride along in the JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -300,6 +416,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     ctx = capi.Context(local, rank, world)
+    ctx.capi = capi
     if world > 1:
         ctx.set_option("replicate_below_mb", args.replicate_mb)
     stream = torch.cuda.Stream()
@@ -315,46 +432,54 @@ def main():
     weights = []
     t0 = time.time()
     for name, layer, n, k in ops:
-        blocks = base[name] if layer <= 0 else synth.roll_rows(base[name], 17 * layer)
-        weights.append(ctx.upload(blocks))
+        weights.append(ctx.upload(layer_weight(base, name, layer)))
     upload_s = time.time() - t0
+    # stages: (q,k,v) (o) (gate,up) (down) per layer, then lm_head; the ops of a stage read ONE input vector
+    stages, i = [], 0
+    for layer in range(args.layers):
+        for stage in shapes.LAYER_STAGES:
+            stages.append(list(range(i, i + len(stage))))
+            i += len(stage)
+    stages.append([i])
     x_off, y_off = [], []
     xo = yo = 0
-    for name, layer, n, k in ops:
+    for st in stages:
         x_off.append(xo)
+        xo += ops[st[0]][3]
+    for name, layer, n, k in ops:
         y_off.append(yo)
-        xo += k
         yo += n
     x_host = torch.empty(xo, dtype=torch.float32).pin_memory()
     rng = np.random.default_rng(synth.seed_for(2, "attn_q", "activations"))
     x_host.numpy()[:] = rng.standard_normal(xo, dtype=np.float32)
     y_host = torch.empty(yo, dtype=torch.float32).pin_memory()
+    fused = world > 1 and args.gather == "fused"
     with torch.cuda.stream(stream):
         x_dev = x_host.to("cuda", non_blocking=True)
         # with several ranks the outputs live in symmetric memory and the GEMV delivers every rank's columns itself
-        y_dev = ctx.symm_empty((yo,)) if (world > 1 and args.gather == "fused") else torch.zeros(yo, dtype=torch.float32, device="cuda")
+        y_dev = ctx.symm_empty((yo,)) if fused else torch.zeros(yo, dtype=torch.float32, device="cuda")
     stream.synchronize()
-    xs = [x_dev[x_off[i]:x_off[i] + ops[i][3]].view(1, -1) for i in range(len(ops))]
-    ys = [y_dev[y_off[i]:y_off[i] + ops[i][2]].view(1, -1) for i in range(len(ops))]
-
-    # groups of independent ops: (q,k,v) (o) (gate,up) (down) per layer, then lm_head
-    groups, i = [], 0
-    if args.group == "stage":
-        for layer in range(args.layers):
-            for stage in shapes.LAYER_STAGES:
-                groups.append(list(range(i, i + len(stage))))
-                i += len(stage)
-        groups.append([i])
-    else:
-        groups = [[j] for j in range(len(ops))]
-
+    xs = [x_dev[x_off[s]:x_off[s] + ops[st[0]][3]].view(1, -1) for s, st in enumerate(stages)]
+    ys = [y_dev[y_off[j]:y_off[j] + ops[j][2]].view(1, -1) for j in range(len(ops))]
     act_mode = capi.ACT_Q8 if args.act_mode == "q8" else capi.ACT_F32
 
+    # A stage chain records the whole step once (Q8 arithmetic).  A stage's rows are whole on every rank before the next
+    # stage reads its input: with fused delivery every launch waits for the peers' announcements in its prologue and the
+    # step ends with one explicit wait for the last stage; with NCCL every stage is followed by its grouped all-gather.
+    chain = None
+    if act_mode == capi.ACT_Q8 and (world == 1 or fused):
+        chain = ctx.chain([[(weights[j], xs[s], ys[j]) for j in st] for s, st in enumerate(stages)])
+
     def enqueue_step():
-        for g in groups:
-            ctx.mul_mat_batch([(weights[j], xs[j], ys[j]) for j in g], act_mode=act_mode)
+        if chain is not None:
+            chain.launch()
+            if world > 1:
+                ctx.all_gather_batch([ys[j] for j in stages[-1]])
+            return
+        for s, st in enumerate(stages):
+            ctx.mul_mat_batch([(weights[j], xs[s], ys[j]) for j in st], act_mode=act_mode)
             if world > 1 and args.gather != "none":  # "none" leaves the rows incomplete: timing experiments only
-                ctx.all_gather_batch([ys[j] for j in g])
+                ctx.all_gather_batch([ys[j] for j in st])
 
     l0 = ctx.launches
     enqueue_step()  # eager once: allocations, attributes
@@ -377,17 +502,21 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, stamps=None):
         ev0 = torch.cuda.Event(enable_timing=True)
         ev1 = torch.cuda.Event(enable_timing=True)
         barrier()
+        t_begin = time.perf_counter()
         with torch.cuda.stream(stream):
             ev0.record(stream)
             for _ in range(steps):
                 fn()
             ev1.record(stream)
         ctx.sync()
+        t_end = time.perf_counter()
         barrier()
+        if stamps is not None:
+            stamps.extend([t_begin, t_end])
         ms = ev0.elapsed_time(ev1)
         if world > 1:
             t = torch.tensor([ms], device="cuda")
@@ -395,13 +524,14 @@ def main():
             ms = float(t.item())
         return ms
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     ctx.sync()
-    sampler = ClockSampler(local)
-    sampler.start()
-    ms_total = timed(step, args.steps)
-    clocks = sampler.stop()
+    stamps = []
+    ms_total = timed(step, args.steps, stamps)
+    clocks = sampler.window(stamps[0], stamps[1])
     ms_step = ms_total / args.steps
 
     # ---- end to end: host activations in, host outputs out, through the C ABI every step ----
@@ -417,73 +547,111 @@ def main():
     ctx.sync()
     e2e_steps = max(10, args.steps // 4)
     e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    sampler.stop()
+    y_after = y_host.numpy().copy()  # the outputs of the last end-to-end step, as the host received them
 
     total_bytes = sum(shapes.mul_mat_bytes(n, k, 1) for _, _, n, k in ops)
     weight_bytes = sum(n * (k // 32) * 34 for _, _, n, k in ops)
     value = total_bytes / (ms_step * 1e-3) / 1e9
     e2e_value = total_bytes / (e2e_ms * 1e-3) / 1e9
     hbm_peak, _, peak_kind = measured_peaks()
+    # what THIS rank streams per step under the placement policy: its row shard of every weight, whole or split
+    rank_weight_bytes = sum(w.bytes_q8 for w in weights)
+    rank_bytes = rank_weight_bytes + sum(4 * k + 4 * (w.n1 - w.n0) for (_, _, n, k), w in zip(ops, weights))
 
-    # ---- prefill (configs[3]): 512 tokens through layer 0's gate, up and down with the tensor-core GEMM ----
-    prefill = None
+    # ---- parity of the timed buffers ----
+    # every rank must hold the same complete outputs (delivered rows included) ...
+    digest = int(torch.from_numpy(y_after.view(np.int32)).to(torch.int64).sum().item()) & 0xFFFFFFFFFFFF
+    all_equal = True
+    if world > 1:
+        t = torch.tensor([digest], dtype=torch.int64, device="cuda")
+        gathered = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        all_equal = all(int(g.item()) == digest for g in gathered)
+    # ... and they are checked against the CPU oracle in the CPU leg below (1 GPU), or against an unsharded
+    # single-context run of the same stages on this GPU (N > 1: "the same numbers as one GPU")
+    gpu_check = []
+    for label, j in (("layer0_ffn_gate", next(j for j, o in enumerate(ops) if o[0] == "ffn_gate")),
+                     ("layer0_ffn_down", next(j for j, o in enumerate(ops) if o[0] == "ffn_down")), ("lm_head", len(ops) - 1)):
+        s = next(s for s, st in enumerate(stages) if j in st)
+        xh = x_host.numpy()[x_off[s]:x_off[s] + ops[j][3]][None, :]
+        yh = y_after[y_off[j]:y_off[j] + ops[j][2]][None, :]
+        idx = None if ops[j][2] <= 16384 else np.arange(0, ops[j][2], 13)
+        gpu_check.append((label, layer_weight(base, ops[j][0], ops[j][1]), xh, yh, idx))
+    one_gpu_equal = None
+    if world > 1 and rank == 0:
+        solo = capi.Context(local, 0, 1)
+        solo.set_stream(stream.cuda_stream)
+        one_gpu_equal = True
+        for label, w, xh, yh, idx in gpu_check[:2]:
+            h = solo.upload(w)
+            with torch.cuda.stream(stream):
+                got = solo.mul_mat(h, torch.from_numpy(np.ascontiguousarray(xh)).cuda())
+            solo.sync()
+            one_gpu_equal = one_gpu_equal and bool((got.cpu().numpy().view(np.uint32) == yh.view(np.uint32)).all())
+            h.free()
+        solo.close()
+
+    # ---- prefill (configs[3]), rms_norm and the allocation-free entry point: outside the timed region ----
+    prefill, norm, noalloc = None, None, None
     if not args.no_prefill:
-        prefill = prefill_run(ctx, stream, torch, ops, weights, timed, world)
-
-    # ---- rms_norm x norm-weight, the producer of the decode activations (1 GPU: it does not shard) ----
-    norm = None
-    if not args.no_prefill and world == 1 and args.act_mode == "q8":
-        norm = norm_run(ctx, stream, torch, ops, weights, timed)
-
-    # spot parity check of the timed buffers against nothing but themselves being finite (full parity lives in tests/)
-    ctx.sync()
-    finite = bool(torch.isfinite(y_dev).all().item())
+        prefill, pchecks = prefill_run(ctx, stream, torch, ops, weights, base, timed, world)
+        gpu_check.extend(pchecks)
+        if world == 1 and args.act_mode == "q8":
+            norm = norm_run(ctx, stream, torch, ops, weights, timed)
+            noalloc = noalloc_run(ctx, stream, torch, ops, weights, timed)
 
     if rank == 0:
-        gemv_launches = len(groups)
-        per_launch_bytes = total_bytes / world / gemv_launches
-        per_launch_ms = ms_step / gemv_launches
-        per_gpu_gbs = total_bytes / world / (ms_step * 1e-3) / 1e9
+        n_launch = len(stages)
+        per_launch_bytes = rank_bytes / n_launch
+        per_launch_ms = ms_step / n_launch
+        per_gpu_gbs = rank_bytes / (ms_step * 1e-3) / 1e9
+        config = workload_config(args.layers, len(ops), weight_bytes, args.act_mode)
+        config.update({
+            "launch_grouping": "one launch per stage (the independent projections of a stage together), recorded as a stage chain" if chain is not None else "one launch per stage",
+            "cuda_graph": graph is not None,
+            "parallelism": "row-shard x%d" % world + ("" if world == 1 or not args.replicate_mb else " (weights under %d MiB replicated)" % args.replicate_mb) +
+                           ("" if world == 1 else (" + all-gather fused into the GEMV (peer stores over NVLink, the next launch waits for the peers)" if fused else " + NCCL all-gather per stage")),
+            "l2": "inputs larger than L2 (this rank streams %.2f GB of weights per step vs 126 MB)" % (rank_weight_bytes / 1e9),
+        })
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "i8xi8->i32, f32 scales", "data": "synthetic",
-            "config": {
-                "workload": "configs[2]: LLaMA-3-8B full decode matmul set, batch 1: %d layers x (q,k,v,o,gate,up,down) + lm_head = %d Q8_0 mul_mats, "
-                            "%.3f GB of Q8_0 weights per step" % (args.layers, len(ops), weight_bytes / 1e9),
-                "act_mode": "q8_0 activations (reference quantiser), exact int8 block dots" if args.act_mode == "q8" else "f32 activations x dequantised weights",
-                "launch_grouping": args.group, "cuda_graph": graph is not None, "parallelism": "row-shard x%d" % world + ("" if world == 1 or not args.replicate_mb else " (weights under %d MiB replicated)" % args.replicate_mb) + ("" if world == 1 else (" + all-gather fused into the GEMV (peer stores over NVLink)" if args.gather == "fused" else " + NCCL all-gather per stage")),
-                "l2": "inputs larger than L2 (%.2f GB of weights per GPU per step vs 126 MB)" % (weight_bytes / world / 1e9),
-            },
+            "dtype": DTYPE, "data": "synthetic", "config": config,
             "tokens_per_s_equiv": 1e3 / ms_step,
             "frac_of_nominal_8TBs": per_gpu_gbs / NOMINAL_HBM_GBS,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_bytes, "d2h_bytes_per_step": y_bytes, "ms_per_step": e2e_ms},
             "gpu_launches": launches_per_step * args.steps,
             "launches_per_step": launches_per_step,
             "clocks": clocks,
+            "ms_per_step_x_sm_mhz": (ms_step * clocks["sm_mhz"]) if clocks.get("sm_mhz") else None,
             "roofline": {
                 "bound": "hbm", "kernel": "gemv_q8_rows", "achieved": per_launch_bytes / (per_launch_ms * 1e-3) / 1e9, "peak": hbm_peak,
                 "unit": "GB/s", "frac": per_launch_bytes / (per_launch_ms * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind,
-                "traffic": (NCU_DRAM_BYTES_PER_STEP / gemv_launches) if (args.layers == shapes.L and world == 1) else None,
+                "traffic": (NCU_DRAM_BYTES_PER_STEP / n_launch) if (args.layers == shapes.L and world == 1) else None,
                 "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms,
-                "note": "per GPU; launch gaps inside the graph are included in the duration",
+                "note": "per GPU: the bytes this rank streams under the placement policy; launch gaps inside the graph are included in the duration",
             },
+            "parity": {"all_ranks_hold_the_same_outputs": all_equal, "bit_identical_to_one_gpu": one_gpu_equal},
             "prefill": prefill,
             "rms_norm": norm,
-            "outputs_finite": finite,
+            "noalloc": noalloc,
             "setup_s": {"generate": gen_s, "upload": upload_s},
         }
         if world == 1 and not args.no_cpu_baseline:
-            kind, nbytes, times = cpu_reference_run(base, args.cpu_seconds, os.cpu_count() or 1)
-            line["cpu_baseline"] = {
-                "value": nbytes / float(np.mean(times)) / 1e9, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": kind,
-                "sample": "layer-0 q,k,v,o,gate,up,down + lm_head at M=1 (790 MB of Q8_0 per pass, %d passes), all host threads" % len(times),
-            }
+            cpu, parity = cpu_baseline_leg(base, args.layers, args.cpu_seconds, gpu_check)
+            line["cpu_baseline"] = cpu
+            line["parity"].update(parity)
+            if prefill is not None:
+                prefill["parity_max_rel"] = max(v for k, v in parity["cases"].items() if k.startswith("prefill_"))
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
 
     if graph is not None:
         graph.free()
+    if chain is not None:
+        chain.free()
     for w in weights:
         w.free()
     ctx.close()

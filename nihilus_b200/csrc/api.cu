@@ -918,8 +918,12 @@ int nhb_sync(nhb_ctx* ctx) {
 	if (ctx->host_status[0] != DEV_OK) {
 		const int code = ctx->host_status[0];
 		cudaMemsetAsync(ctx->dev_status, 0, NHB_STATUS_WORDS * sizeof(int), ctx->stream);
-		if (ctx->push_local)
-			cudaMemsetAsync(ctx->push_local, 0, sizeof(unsigned), ctx->stream);
+		if (ctx->push_local) {
+			// the exchange starts over: no launch counted, no announcement seen (every rank that saw the timeout does the same)
+			cudaMemsetAsync(ctx->push_local, 0, 2 * sizeof(unsigned), ctx->stream);
+			cudaMemsetAsync(ctx->regions[0].local, 0, ctx->regions[0].bytes, ctx->stream);
+		}
+		ctx->pending_wait = false;
 		cudaStreamSynchronize(ctx->stream);
 		return fail(ctx, NHB_ERR_TIMEOUT, "a device-side wait ran out (code " + std::to_string(code) + "); results of the last launches are invalid");
 	}
@@ -980,6 +984,8 @@ int nhb_weight_upload_q8_0(nhb_ctx* ctx, const void* host_blocks34, int64_t N, i
 		return fail(ctx, NHB_ERR_ARG, "nhb_weight_upload_q8_0: K must be a positive multiple of 32 and N >= 0");
 	if (N > 0 && !host_blocks34)
 		return fail(ctx, NHB_ERR_ARG, "nhb_weight_upload_q8_0: null tensor data");
+	if (K > INT32_MAX || N > (int64_t(1) << 30) * ctx->world)
+		return fail(ctx, NHB_ERR_ARG, "nhb_weight_upload_q8_0: K beyond 2^31 - 1 or more than 2^30 rows per rank (the kernels index rows and columns with 32-bit integers)");
 	if (ctx->capturing)
 		return fail(ctx, NHB_ERR_UNSUPPORTED, "weight upload during graph capture");
 	device_guard g(ctx->device);

@@ -144,24 +144,6 @@ namespace nhb {
 			return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(GM_ROWS >> 4) << 24);
 		}
 
-#ifdef NHB_GEMM_PROF
-		// debug builds only: cycles CTA (0,0) spent waiting, per role.  [0..3] epilogue warp 4: full, tmem_full, total;
-		// [8..11] MMA warp: full, tmem_empty, total; [16..18] producer: empty, total
-		__device__ long long g_prof[32];
-#define PROF_T(var) const long long var = clock64()
-#define PROF_ACC(slot, a, b) prof_acc[slot] += (b) - (a)
-#define PROF_DECL long long prof_acc[4] = {}
-#define PROF_FLUSH(base_slot) \
-	if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) { \
-		for (int i_ = 0; i_ < 4; ++i_) \
-			g_prof[(base_slot) + i_] = prof_acc[i_]; \
-	}
-#else
-#define PROF_T(var)
-#define PROF_ACC(slot, a, b)
-#define PROF_DECL
-#define PROF_FLUSH(base_slot)
-#endif
 		constexpr int GM_TMEM_COLS = 512;// the whole tensor memory of the SM: one CTA per SM
 		// accumulator stages: as many as fit, so the MMA warp can run several Q8 blocks ahead of the epilogue (narrow
 		// tiles are bound by the latency of the MMA -> epilogue -> MMA hand-over, which more stages overlap)
@@ -314,16 +296,11 @@ namespace nhb {
 						const uint32_t empty0 = smem_u32(&hd->empty[0]);
 						int s				  = 0;
 						uint32_t ph			  = 1;// a fresh barrier reads as "phase 1 complete": the first S waits pass at once
-						PROF_DECL;
-						PROF_T(pt0);
 						for (int kb = 0; kb < n_kb; ++kb) {
-							PROF_T(p0);
 							if (!mbar_wait_a(empty0 + 8 * s, ph)) {
 								atomicExch(dev_status, DEV_TIMEOUT_EMPTY);
 								break;
 							}
-							PROF_T(p1);
-							PROF_ACC(0, p0, p1);
 							const uint32_t st = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
 							mbar_expect_tx(&hd->full[s], tx);
 							tma_load_2d(st, &map_a, kb * GM_KSLICE, lane0, &hd->full[s]);
@@ -341,9 +318,6 @@ namespace nhb {
 								ph ^= 1;
 							}
 						}
-						PROF_T(pt1);
-						PROF_ACC(2, pt0, pt1);
-						PROF_FLUSH(16);
 					}
 				} else if (warp == 1 || (NS >= 8 && warp == 2)) {
 					// ---------------- MMA issuers ----------------
@@ -369,18 +343,13 @@ namespace nhb {
 							ph ^= 1;
 						}
 						bool ok = true;
-						PROF_DECL;
-						PROF_T(mt0);
 						for (int kb = static_cast<int>(first); kb < n_kb && ok; kb += ISSUERS) {
 							const uint32_t a_lo = smem_desc_lo(ring + s * STAGE_BYTES);// descriptor low word of this slot's A tile
-							PROF_T(m0);
 							if (!mbar_wait_a(full0 + 8 * s, ph)) {
 								atomicExch(dev_status, DEV_TIMEOUT_FULL);
 								break;
 							}
 							tc_fence_after();
-							PROF_T(m1);
-							PROF_ACC(0, m0, m1);
 							const uint32_t b_lo = a_lo + (GM_A_BYTES >> 4);
 							// Q8 block t = 2 kb + j goes to accumulator stage t % NS, in its (t / NS)-th use
 							const uint32_t a0	  = static_cast<uint32_t>(2 * kb) & (NS - 1);
@@ -388,15 +357,12 @@ namespace nhb {
 #pragma unroll
 							for (uint32_t j = 0; j < 2; ++j) {
 								const uint32_t a = a0 + j;
-								PROF_T(m2);
 								if (!mbar_wait_a(tmem_empty0 + 8 * a, use_ph ^ 1u)) {
 									atomicExch(dev_status, DEV_TIMEOUT_MMA);
 									ok = false;
 									break;
 								}
 								tc_fence_after();
-								PROF_T(m3);
-								PROF_ACC(1, m2, m3);
 								const uint32_t d_tmem = tmem_base + a * STAGE_COLS;
 								// the block's two K = 16 steps sit 32 bytes apart inside the 128-byte rows: (j * 64 + k2 * 32) >> 4
 								umma_f16_set(d_tmem, a_lo + 4 * j, b_lo + 4 * j, GM_DESC_HI, idesc);
@@ -410,11 +376,6 @@ namespace nhb {
 								s -= S;
 								ph ^= 1;
 							}
-						}
-						PROF_T(mt1);
-						PROF_ACC(2, mt0, mt1);
-						if (warp == 1) {
-							PROF_FLUSH(8);
 						}
 					}
 				}
@@ -453,17 +414,12 @@ namespace nhb {
 				bool ok		= true;
 				int s		= 0;
 				uint32_t ph = 0;
-				PROF_DECL;
-				PROF_T(et0);
 				for (int kb = 0; kb < n_kb && ok; ++kb) {
 					// the scales of this K slice were written by the async proxy: acquire them
-					PROF_T(e0);
 					if (!mbar_wait_a(full0 + 8 * s, ph)) {
 						ok = false;
 						break;
 					}
-					PROF_T(e1);
-					PROF_ACC(0, e0, e1);
 					const uint32_t st	  = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
 					const int a0		  = (2 * kb) & (NS - 1);
 					const uint32_t use_ph = static_cast<uint32_t>((2 * kb) / NS) & 1u;
@@ -476,14 +432,11 @@ namespace nhb {
 							const float r = lds_f32(st + rs_off + (j * SC_FLOATS + 8 * i) * 4);
 							rs2[i]		  = pack2(r, r);
 						}
-						PROF_T(e2);
 						if (!mbar_wait_a(tmem_full0 + 8 * a, use_ph)) {
 							ok = false;
 							break;
 						}
 						tc_fence_after();
-						PROF_T(e3);
-						PROF_ACC(1, e2, e3);
 						if (MAXU == 0 || my_units == 0) {
 							// a narrow tile leaves this column group empty; the stage still counts this warp's release
 							__syncwarp();
@@ -536,15 +489,6 @@ namespace nhb {
 						ph ^= 1;
 					}
 				}
-#ifdef NHB_GEMM_PROF
-				{
-					PROF_T(et1);
-					PROF_ACC(2, et0, et1);
-					if (warp == 4) {
-						PROF_FLUSH(0);
-					}
-				}
-#endif
 				if (!ok) {
 					if (lane == 0)
 						atomicExch(dev_status, DEV_TIMEOUT_MMA);
@@ -856,13 +800,3 @@ namespace nhb {
 
 }
 
-#ifdef NHB_GEMM_PROF
-extern "C" int nhb_debug_gemm_prof(long long* out32, int reset) {
-	cudaError_t e = cudaMemcpyFromSymbol(out32, nhb::g_prof, sizeof(long long) * 32);
-	if (e == cudaSuccess && reset) {
-		long long z[32] = {};
-		e = cudaMemcpyToSymbol(nhb::g_prof, z, sizeof(z));
-	}
-	return e == cudaSuccess ? 0 : -2;
-}
-#endif

@@ -613,12 +613,12 @@ namespace nhb {
 		e = cudaSuccess; \
 		if (fat) { \
 			auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT, false, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} else { \
 			auto kern = gemv_q8_rows<MT, 2, ROWS_TPB, false, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} \
@@ -633,17 +633,17 @@ namespace nhb {
 		e = cudaSuccess; \
 		if (split) { \
 			auto kern = gemv_q8_rows_split<MT, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} else if (fat) { \
 			auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} else { \
 			auto kern = gemv_q8_rows<MT, 2, ROWS_TPB, true>; \
-			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e		  = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 			if (e == cudaSuccess) \
 				e = cudaLaunchKernelEx(&lc, kern, b); \
 		} \
@@ -658,7 +658,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows_split<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 32 * 1024) /* the kernel also has static shared memory */ \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -672,7 +672,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -686,7 +686,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows<MT, OCC>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -708,7 +708,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows<MT, 2>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}
@@ -722,7 +722,7 @@ namespace nhb {
 		auto kern = gemv_q8_rows_db<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); \
+			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
 		if (e == cudaSuccess) \
 			e = cudaLaunchKernelEx(&lc, kern, b); \
 	}

@@ -287,7 +287,15 @@ int nhb_gguf_open(const char* path, nhb_gguf** out) {
 		if (t.dims[0] % bs != 0)
 			return open_fail(g, NHB_ERR_ARG, "tensor '" + t.name + "': row length is not a multiple of its block size");
 		// common/type_traits.hpp:38-60 for contiguous tensors: blocks per row x type size x rows
-		t.bytes = t.dims[0] / bs * ts * t.dims[1] * t.dims[2] * t.dims[3];
+		// (each factor may be up to 2^32: the product is formed with overflow checks, a wrapped size would pass every
+		// "inside the file" test below)
+		uint64_t bytes = t.dims[0] / bs;
+		bool wrapped   = __builtin_mul_overflow(bytes, ts, &bytes);
+		for (int d = 1; d < 4; ++d)
+			wrapped = wrapped || __builtin_mul_overflow(bytes, t.dims[d], &bytes);
+		if (wrapped)
+			return open_fail(g, NHB_ERR_ARG, "tensor '" + t.name + "': size does not fit 64 bits");
+		t.bytes = bytes;
 		if (t.offset > g->size || t.bytes > g->size)
 			return open_fail(g, NHB_ERR_ARG, "tensor '" + t.name + "': data outside the file");
 		max_end = std::max(max_end, t.offset + t.bytes);

@@ -31,7 +31,7 @@ namespace {
 
 	// In host code `nhb_noalloc_scratch` names a host-side shadow of the symbol, not memory a kernel may touch;
 	// the device address has to be asked for, once per device, with that device current.
-	int scratch_for_current_device(unsigned char** out) {
+	int scratch_for_current_device(unsigned char** out, int* device) {
 		int dev		  = -1;
 		cudaError_t e = cudaGetDevice(&dev);
 		if (e != cudaSuccess)
@@ -46,7 +46,8 @@ namespace {
 				return fail(NHB_ERR_CUDA, std::string("cudaGetSymbolAddress(nhb_noalloc_scratch): ") + cudaGetErrorString(e));
 			g_scratch_dev[dev] = static_cast<unsigned char*>(p);
 		}
-		*out = g_scratch_dev[dev];
+		*out	= g_scratch_dev[dev];
+		*device = dev;
 		return NHB_OK;
 	}
 
@@ -73,8 +74,9 @@ int nhb_mul_mat_q8_0_noalloc(const void* q_plane, const void* d_plane, int64_t r
 		return fail(NHB_ERR_ARG, "null pointer");
 	if (ldx < K || ldy < rows)
 		return fail(NHB_ERR_ARG, "leading dimension smaller than the row length");
-	if ((reinterpret_cast<uintptr_t>(q_plane) & 31) || (reinterpret_cast<uintptr_t>(d_plane) & 1) || (reinterpret_cast<uintptr_t>(x_dev) & 15) || (ldx & 3))
-		return fail(NHB_ERR_ARG, "the int8 plane must be 32-byte aligned, activations 16-byte aligned, ldx a multiple of 4");
+	if ((reinterpret_cast<uintptr_t>(q_plane) & 31) || (reinterpret_cast<uintptr_t>(d_plane) & 1) || (reinterpret_cast<uintptr_t>(x_dev) & 15) || (ldx & 3) ||
+		(reinterpret_cast<uintptr_t>(y_dev) & 3))
+		return fail(NHB_ERR_ARG, "the int8 plane must be 32-byte aligned, activations 16-byte aligned with ldx a multiple of 4, outputs 4-byte aligned");
 	if (rows > (int64_t(1) << 30))
 		return fail(NHB_ERR_ARG, "too many rows");
 	const size_t need = gemv_rows_act_bytes(K, static_cast<int>(M > 4 ? 4 : M));
@@ -83,7 +85,8 @@ int nhb_mul_mat_q8_0_noalloc(const void* q_plane, const void* d_plane, int64_t r
 			"nhb_mul_mat_q8_0_noalloc: M = " + std::to_string(M) + ", K = " + std::to_string(K) + " needs " + std::to_string(M * (K + K / 8)) +
 				" bytes of quantised activations; the fixed scratch holds at most M = 4 rows and 98304 bytes (M * (K + K/8) <= 98304)");
 	unsigned char* scratch = nullptr;
-	int rc				   = scratch_for_current_device(&scratch);
+	int dev				   = 0;
+	int rc				   = scratch_for_current_device(&scratch, &dev);
 	if (rc != NHB_OK)
 		return rc;
 	cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
@@ -116,9 +119,7 @@ int nhb_mul_mat_q8_0_noalloc(const void* q_plane, const void* d_plane, int64_t r
 	op.act_off	  = 0;
 	op.preq_off	  = 0;
 	int sm_count  = 0;
-	int dev		  = 0;
-	cudaGetDevice(&dev);
-	e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+	e			  = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
 	if (e != cudaSuccess)
 		return fail(NHB_ERR_CUDA, std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
 	launch_cfg cfg{};

@@ -4,7 +4,7 @@
 # extracted line ranges are piped straight into the compiler and only the shared object lands in
 # oracle/_ref/ (git-ignored).
 #
-#   usage: oracle/build_ref.sh [reference-root]     (default /root/reference)
+#   usage: oracle/build_ref.sh <reference-root>     (or set NIHILUS_REFERENCE)
 #
 # Extracted ranges (all inside the reference's block comment, i.e. dead code there):
 #   cpu/common.hpp 215-221   fp32_to_fp16 / fp16_to_fp32 (F16C)
@@ -18,7 +18,11 @@
 # Skipped: 4679-4747 (names vec_dot_q8_0_q8_0<device_types::cpu, 1>, which is ill-formed).
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-ref="${1:-/root/reference}"
+ref="${1:-${NIHILUS_REFERENCE:-}}"
+if [[ -z "$ref" ]]; then
+	echo "build_ref: no reference root given (argument or NIHILUS_REFERENCE)" >&2
+	exit 3
+fi
 common="$ref/include/nihilus-incl/cpu/common.hpp"
 avx2="$ref/include/nihilus-incl/cpu/avx_2.hpp"
 if [[ ! -f "$common" || ! -f "$avx2" ]]; then

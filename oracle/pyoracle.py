@@ -25,15 +25,31 @@ _c_f32p = C.POINTER(C.c_float)
 _c_u8p = C.POINTER(C.c_uint8)
 
 
+def reference_root() -> str:
+    """Where the reference's source tree lies: $NIHILUS_REFERENCE, else `reference_path` of BASELINE.json beside this
+    package, else nowhere (the prebuilt oracle/_ref is then used as it is)."""
+    env = os.environ.get("NIHILUS_REFERENCE")
+    if env:
+        return env
+    try:
+        import json
+
+        with open(os.path.join(HERE, "..", "BASELINE.json")) as f:
+            return str(json.load(f).get("reference_path") or "")
+    except (OSError, ValueError):
+        return ""
+
+
 def build(force: bool = False) -> None:
     """Compile liboracle.so (and oracle/_ref when the reference tree is present)."""
     src_m = max(os.path.getmtime(os.path.join(HERE, f)) for f in ("q8_oracle.c", "q8_oracle.h"))
     if force or not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < src_m:
         subprocess.run(["make", "-C", HERE, "liboracle.so"], check=True, capture_output=True)
-    if os.path.isdir("/root/reference/include/nihilus-incl"):
+    ref = reference_root()
+    if ref and os.path.isdir(os.path.join(ref, "include", "nihilus-incl")):
         shim_m = max(os.path.getmtime(os.path.join(HERE, f)) for f in ("ref_prelude.hpp", "ref_postlude.cpp", "build_ref.sh"))
         if force or not os.path.exists(REF_SO) or os.path.getmtime(REF_SO) < shim_m:
-            subprocess.run(["make", "-C", HERE, "ref"], check=True, capture_output=True)
+            subprocess.run(["make", "-C", HERE, "ref", "REF=" + ref], check=True, capture_output=True)
 
 
 def _ptr(a: np.ndarray, typ):

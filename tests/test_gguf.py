@@ -91,6 +91,22 @@ def test_malformed_files_are_rejected(capi, tmp_path):
         capi.Gguf(p3)
 
 
+def test_a_tensor_size_that_wraps_64_bits_is_rejected(capi, tmp_path):
+    """Every dimension may be up to 2^32, so blocks x type size x rows can wrap: a q8_0 tensor of [2^32, 4042322161]
+    would come out as 2^28 bytes and pass every inside-the-file check."""
+    dims = [1 << 32, 4042322161]
+    assert (dims[0] // 32 * 34 * dims[1]) % (1 << 64) == 1 << 28
+    name = b"blk.0.attn_q.weight"
+    head = struct.pack("<IIQQ", 0x46554747, 3, 1, 0)
+    head += struct.pack("<Q", len(name)) + name + struct.pack("<I", 2) + struct.pack("<QQ", *dims) + struct.pack("<IQ", 8, 0)
+    head += b"\0" * ((-len(head)) % 32)
+    p = str(tmp_path / "wrap.gguf")
+    with open(p, "wb") as f:
+        f.write(head + b"\0" * (1 << 28))
+    with pytest.raises(capi.NhbError, match="64 bits"):
+        capi.Gguf(p)
+
+
 def test_f16_and_upload_argument_checks(capi, tmp_path):
     p = str(tmp_path / "h.gguf")
     write_gguf(p, [], [("h", GGML_F16, np.ones((3, 32), dtype=np.float16))])

@@ -1,4 +1,5 @@
-"""Row-sharded mul_mat + NCCL all-gather on 2 GPUs, one process per GPU (skipped with fewer than 2 devices)."""
+"""Row-sharded mul_mat on 2, 4 and 8 GPUs, one process per GPU: NCCL all-gather, the all-gather fused into the decode GEMV,
+stage chains and the placement policy (each world size is skipped where the box has fewer devices)."""
 import os
 import sys
 
@@ -127,53 +128,84 @@ def _worker(rank, world, uid_path, q):
         hs_small.free()
         hs_big.free()
         ctx.set_option("replicate_below_mb", 0)
+        # ---- a buffer written again two delivering launches later, with a reader in between (the documented reuse rule) ----
+        wp = synth.make_weight(2048, 4096, 91)
+        hp = ctx.upload(wp)
+        bufs = [ctx.symm_empty((1, 2048)), ctx.symm_empty((1, 2048))]
+        xp = [torch.from_numpy(synth.make_activation(1, 4096, 92 + j)).cuda() for j in range(6)]
+        logs = [torch.zeros((1, 2048), device="cuda") for _ in range(6)]
+        for j in range(6):
+            ctx.mul_mat(hp, xp[j], bufs[j % 2])
+            ctx.all_gather(bufs[j % 2])  # the reader below is not a GEMV launch: this is where it waits for the peers
+            logs[j].copy_(bufs[j % 2])
+        ctx.sync()
+        out["pingpong"] = [t.cpu().numpy() for t in logs]
+        # ---- a chain of dependent stages: 4096 -> 14336 -> 4096 -> 1024, every stage sharded and delivered ----
+        dims = [(14336, 4096), (4096, 14336), (1024, 4096)]
+        hc = [ctx.upload(synth.make_weight(n, k, 95 + i)) for i, (n, k) in enumerate(dims)]
+        xc = torch.from_numpy(synth.make_activation(1, 4096, 99)).cuda()
+        yc = [ctx.symm_empty((1, n)) for n, _ in dims]
+        ch = ctx.chain([[(hc[0], xc, yc[0])], [(hc[1], yc[0], yc[1])], [(hc[2], yc[1], yc[2])]])
+        for _ in range(3):
+            ch.launch()
+        ctx.all_gather(yc[2])
+        ctx.sync()
+        out["chain"] = [t.cpu().numpy() for t in yc]
+        ch.free()
+        for h in hc + [hp]:
+            h.free()
     q.put((rank, out))
     ha.free()
     hb.free()
     ctx.close()
 
 
-def test_two_gpu_shards_all_gathered_match_oracle(capi, oracle, tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_shards_delivered_to_every_rank_match_oracle_and_one_gpu(capi, oracle, tmp_path, world):
     import torch
     import torch.multiprocessing as mp
 
     from nihilus_b200 import synth
     from oracle import pyoracle as po
 
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     mpctx = mp.get_context("spawn")
     q = mpctx.Queue()
     uid_path = str(tmp_path / "nccl_uid.bin")
     procs = [mpctx.Process(target=_worker, args=(r, world, uid_path, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = dict(q.get(timeout=300) for _ in range(world))
+    results = dict(q.get(timeout=600) for _ in range(world))
     for p in procs:
-        p.join(60)
+        p.join(120)
         assert p.exitcode == 0
+    ranks = range(world)
+
+    def same_on_all_ranks(key):
+        for r in ranks:
+            assert (np.asarray(results[r][key]).view(np.uint32) == np.asarray(results[0][key]).view(np.uint32)).all(), (key, r)
+
+    def close(y, ref):
+        return np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+
     for name, (N, K, M) in {"even": (4096, 4096, 1), "ragged": (1031, 4096, 3), "qkv": (1024, 4096, 2)}.items():
-        w = synth.make_weight(N, K, 900 + N)
-        x = synth.make_activation(M, K, 901 + N)
-        ref = oracle.mul_mat(po.Q8ACT_LANES, w, x)
-        for r in range(world):
-            y = results[r][name]
-            assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max(), (name, r)
-        assert (results[0][name].view(np.uint32) == results[1][name].view(np.uint32)).all()
+        ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, K, 900 + N), synth.make_activation(M, K, 901 + N))
+        for r in ranks:
+            assert close(results[r][name], ref), (name, r)
+        same_on_all_ranks(name)
     x = synth.make_activation(1, 4096, 79)
     for key, seed, N in (("batch_a", 77, 512), ("batch_b", 78, 256)):
         ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, 4096, seed), x)
-        for r in range(world):
-            assert np.abs(results[r][key] - ref).max() <= 1e-4 * np.abs(ref).max()
+        for r in ranks:
+            assert close(results[r][key], ref)
             # fused delivery gives the very same bits as compute + NCCL
             assert (results[r]["f_" + key].view(np.uint32) == results[r][key].view(np.uint32)).all()
     for name, (N, K, M) in {"even": (4096, 4096, 1), "ragged": (1031, 4096, 3), "m8": (300, 512, 8)}.items():
         ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, K, 900 + N), synth.make_activation(M, K, 901 + N))
-        for r in range(world):
+        for r in ranks:
             for prefix in ("f_", "g_"):
-                y = results[r][prefix + name]
-                assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max(), (prefix, name, r)
+                assert close(results[r][prefix + name], ref), (prefix, name, r)
             assert (results[r]["f_" + name].view(np.uint32) == results[0]["g_" + name].view(np.uint32)).all()
         if name in ("even", "ragged"):
             assert (results[0]["f_" + name].view(np.uint32) == results[0][name].view(np.uint32)).all()
@@ -181,18 +213,44 @@ def test_two_gpu_shards_all_gathered_match_oracle(capi, oracle, tmp_path):
                                  float(np.float32(1e-5)), 0)
     for key, seed, N in (("n_a", 81, 4096), ("n_b", 82, 1024)):
         ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, 4096, seed), normed)
-        for r in range(world):
-            assert np.abs(results[r][key] - ref).max() <= 1e-4 * np.abs(ref).max(), (key, r)
-        assert (results[0][key].view(np.uint32) == results[1][key].view(np.uint32)).all()
+        for r in ranks:
+            assert close(results[r][key], ref), (key, r)
+        same_on_all_ranks(key)
     xr = synth.make_activation(2, 4096, 63)
     for key, seed, N in (("p_small", 61, 700), ("p_big", 62, 2048)):
         ref = oracle.mul_mat(po.Q8ACT_LANES, synth.make_weight(N, 4096, seed), xr)
-        for r in range(world):
-            assert np.abs(results[r][key] - ref).max() <= 1e-4 * np.abs(ref).max(), (key, r)
-        assert (results[0][key].view(np.uint32) == results[1][key].view(np.uint32)).all()
-    for r in range(world):
+        for r in ranks:
+            assert close(results[r][key], ref), (key, r)
+        same_on_all_ranks(key)
+    for r in ranks:
         assert results[r]["small_rows"] == (0, 700)  # whole on every rank
-        assert results[r]["big_rows"] == ((0, 1024), (1024, 2048))[r]
-        assert results[r]["policy_launches"] == 4  # two kernels per repetition, never a collective
-    # 3 single mul_mats (8 rows go in one pass) + 1 batch per repetition, and no NCCL launch at all
-    assert results[0]["fused_launches_per_rep"] == 4
+        assert results[r]["big_rows"] == capi.shard_rows(2048, world, r)
+        # per repetition: the mixed batch, the wait for its delivery, the replicated-only launch; never a collective
+        assert results[r]["policy_launches"] == 6
+    # per repetition 3 single mul_mats (8 rows go in one pass) + 1 batch, each followed by a one-warp wait; no NCCL launch
+    assert results[0]["fused_launches_per_rep"] == 8
+    # buffers reused every second delivering launch, a reader in between: every reader saw its own launch's rows, whole
+    wp = synth.make_weight(2048, 4096, 91)
+    for j in range(6):
+        ref = oracle.mul_mat(po.Q8ACT_LANES, wp, synth.make_activation(1, 4096, 92 + j))
+        for r in ranks:
+            assert close(results[r]["pingpong"][j], ref), (j, r)
+    # the chain: bit-identical on all ranks and to the same chain on ONE GPU (the definition of parity for the sharded path)
+    c1 = capi.Context(0)
+    c1.use_torch_stream()
+    dims = [(14336, 4096), (4096, 14336), (1024, 4096)]
+    ws = [synth.make_weight(n, k, 95 + i) for i, (n, k) in enumerate(dims)]
+    hs = [c1.upload(w) for w in ws]
+    v = torch.from_numpy(synth.make_activation(1, 4096, 99)).cuda()
+    one_gpu = []
+    for h in hs:
+        v = c1.mul_mat(h, v)
+        one_gpu.append(v)
+    c1.sync()
+    for i in range(3):
+        for r in ranks:
+            assert (results[r]["chain"][i].view(np.uint32) == one_gpu[i].cpu().numpy().view(np.uint32)).all(), (i, r)
+    assert close(one_gpu[0].cpu().numpy(), oracle.mul_mat(po.Q8ACT_LANES, ws[0], synth.make_activation(1, 4096, 99)))
+    for h in hs:
+        h.free()
+    c1.close()

@@ -1,4 +1,4 @@
-"""The allocation-free entry point, nhb_mul_mat_q8_0_noalloc, against the regular nhb_mul_mat (needs a B200).
+"""The allocation-free entry point, nhb_mul_mat_q8_0_noalloc, against the regular nhb_mul_mat and the CPU oracle (needs a B200).
 
 Collected last on purpose: a run that stops at the first failure has by then exercised every other test.
 
@@ -28,10 +28,11 @@ def _bind(capi):
     return fn, err
 
 
-def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row(capi):
+def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row(capi, oracle):
     import torch
 
     from nihilus_b200 import synth
+    from oracle import pyoracle as po
 
     fn, err = _bind(capi)
     ctx = capi.Context(0)
@@ -57,6 +58,9 @@ def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row(capi):
                 rel = float(np.abs(y.cpu().numpy() - ref).max() / max(np.abs(ref).max(), 1e-30))
                 assert rel <= TOL, (N, K, M, rel, y.cpu().numpy()[0, :4], ref[0, :4])
             assert not torch.equal(got[0], got[1])
+            # and against the CPU oracle, so that a fault shared with the regular entry point could not hide
+            ref = oracle.mul_mat(po.Q8ACT_LANES, w, xs[1].cpu().numpy())
+            assert float(np.abs(got[1].cpu().numpy() - ref).max() / np.abs(ref).max()) <= TOL
             h.free()
     finally:
         ctx.close()
@@ -81,6 +85,7 @@ def test_noalloc_rejects_what_does_not_fit_and_bad_arguments(capi):
     assert fn(None, d.data_ptr(), 32, 4096, x.data_ptr(), 65536, y.data_ptr(), 32, 1, s) == capi.ERR_ARG
     assert fn(q.data_ptr() + 16, d.data_ptr(), 32, 4096, x.data_ptr(), 65536, y.data_ptr(), 32, 1, s) == capi.ERR_ARG
     assert fn(q.data_ptr(), d.data_ptr(), 32, 4096, x.data_ptr(), 64, y.data_ptr(), 32, 1, s) == capi.ERR_ARG
+    assert fn(q.data_ptr(), d.data_ptr(), 32, 4096, x.data_ptr(), 65536, y.data_ptr() + 2, 32, 1, s) == capi.ERR_ARG  # misaligned output
     # nothing to do is not an error
     assert fn(q.data_ptr(), d.data_ptr(), 0, 4096, x.data_ptr(), 65536, y.data_ptr(), 32, 1, s) == 0
     assert fn(q.data_ptr(), d.data_ptr(), 32, 4096, x.data_ptr(), 65536, y.data_ptr(), 32, 0, s) == 0
