@@ -6,7 +6,11 @@
 // forward declaration; include/nihilus-incl/infra/monolithic_dispatcher.hpp:41-62 call site).  Its GPU
 // specialisations exist for arch index 4 only and are empty (include/nihilus-incl/cuda/cuda_12.hpp:803-952).
 // This header offers the same shapes in namespace nihilus_b200 with arch index 2 (compute capability 10) and
-// forwards each mul_mat to the C ABI of libnihilus_b200.so.  It is never seen by nvcc.
+// forwards each mul_mat to the C ABI of libnihilus_b200.so.  It is never seen by nvcc.  The dispatcher
+// specialisations themselves live in mega_dispatch.inc, written against the reference's six template parameters
+// and enumerator names, so that the same text can be included inside `namespace nihilus` behind the reference's
+// own headers (define NHB_DISPATCH_HOST_TYPES there: this header then leaves the enums and the primary template
+// to the host's declarations).
 //
 // What is mirrored, with the reference's meaning:
 //   core_trait_dims<d0,d1,d2,d3[,runtime]>   four extents, ne0 contiguous; `runtime` names the extent that is
@@ -15,7 +19,9 @@
 //                                             same static checks as the reference
 //   processing_phases                         eval_time (M = 1) / prompt_eval_time (M = sequence length); here
 //                                             the split is taken at run time from M by the library
-//   kernel_dispatcher_impl<...gpu, 2, ...>    impl(params) / impl(params, current_block)
+//   kernel_dispatcher_impl<config, core_traits, device_types::gpu, 2, core_types::mega_*, phase>
+//                                             impl(params, current_block) for the per-block cores, impl(params) for
+//                                             final_norm_and_sampling
 // Errors follow include/nihilus-incl/common/exception.hpp:65-108: a failing call throws (config::exceptions) or
 // logs and exits with -1.
 #pragma once
@@ -35,9 +41,28 @@
 
 namespace nihilus_b200 {
 
+#ifdef NHB_DISPATCH_HOST_TYPES
+	// behind the reference's own headers: its enums are the ones the dispatcher is keyed on
+	using ::nihilus::core_types;
+	using ::nihilus::device_types;
+	using ::nihilus::processing_phases;
+	enum class kernel_types : uint8_t { weights, rms_norm, mul, mul_mat };
+#else
 	enum class device_types : uint8_t { cpu, gpu };
 	enum class processing_phases { prompt_eval_time, eval_time };
 	enum class kernel_types : uint8_t { weights, rms_norm, mul, mul_mat };
+	// the cores of the reference's graph (include/nihilus-incl/common/config.hpp:214-223), same names, same order
+	enum class core_types : uint8_t {
+		weights,
+		global_inputs,
+		token_embeddings,
+		mega_qkv_prep_and_cache_publish,
+		mega_attention_apply,
+		mega_ffn,
+		final_norm_and_sampling,
+		count,
+	};
+#endif
 	enum class data_types : uint64_t { f32 = 0, f16 = 1, q8_0 = 8 };
 
 	// compute-capability major -> the reference's build-time arch index (cmake/detection/main.cpp:33-44): 10 -> 2
@@ -199,8 +224,9 @@ namespace nihilus_b200 {
 
 	// A core as the dispatcher sees it: the library context plus the independent mul_mats of one stage
 	// (q/k/v share one launch, gate/up share one launch).
-	template<typename... node_types> struct mul_mat_core {
-		nhb_ctx* ctx = nullptr;
+	template<core_types core_type_new, typename... node_types> struct mul_mat_core {
+		static constexpr core_types core_type = core_type_new;// which of the reference's cores this stage belongs to
+		nhb_ctx* ctx						  = nullptr;
 		std::tuple<node_types...> nodes;
 		static constexpr size_t node_count = sizeof...(node_types);
 	};
@@ -219,59 +245,59 @@ namespace nihilus_b200 {
 
 	// A stage whose mul_mats all read the normalised row: the norm is fused in front of them.  The mul_mat nodes'
 	// `activation` pointers are not read; their extents still carry the token count.
-	template<typename norm_node_type, typename... node_types> struct norm_mul_mat_core {
-		nhb_ctx* ctx = nullptr;
+	template<core_types core_type_new, typename norm_node_type, typename... node_types> struct norm_mul_mat_core {
+		static constexpr core_types core_type = core_type_new;
+		nhb_ctx* ctx						  = nullptr;
 		norm_node_type norm;
 		std::tuple<node_types...> nodes;
 		static constexpr size_t node_count = sizeof...(node_types);
 		static_assert(((node_types::traits_type::K == norm_node_type::rms_norm_traits::K) && ...), "every mul_mat of the stage must read the normalised row");
 	};
 
-	template<typename config_type, typename core_traits_type, device_types device_type, uint64_t arch_index, processing_phases processing_phase>
+	// What every specialisation in mega_dispatch.inc does: the independent mul_mats of the stage `params` describes, in one
+	// call of the C ABI.  `eval` = the reference's processing_phases::eval_time (one token).
+	template<typename config_type, bool eval, typename core_traits_type> inline void dispatch_stage(core_traits_type& params, int64_t current_block) {
+		std::array<nhb_mul_mat_op, core_traits_type::node_count> ops{};
+		[&]<size_t... i>(std::index_sequence<i...>) {
+			((ops[i] = std::get<i>(params.nodes).describe(static_cast<uint64_t>(current_block))), ...);
+		}(std::make_index_sequence<core_traits_type::node_count>{});
+		if constexpr (eval) {
+			for (const auto& op: ops)
+				if (op.M != 1)
+					raise<config_type::exceptions>(NHB_ERR_ARG, "eval_time dispatch with more than one token", params.ctx);
+		}
+		if constexpr (requires { params.norm; }) {
+			static_assert(config_type::act_mode == NHB_ACT_Q8, "the fused norm produces Q8_0 activations");
+			for (auto& op: ops)
+				op.x = static_cast<const float*>(params.norm.input.get_data());
+			const int rc = nhb_rms_norm_mul_mat_batch(params.ctx, ops.data(), static_cast<int>(ops.size()), static_cast<const float*>(params.norm.norm_weight.get_data()),
+				params.norm.eps, params.norm.sqrt_mode, NHB_KERNEL_AUTO);
+			if (rc != NHB_OK)
+				raise<config_type::exceptions>(rc, "nhb_rms_norm_mul_mat_batch", params.ctx);
+		} else {
+			const int rc = nhb_mul_mat_batch(params.ctx, ops.data(), static_cast<int>(ops.size()), config_type::act_mode, NHB_KERNEL_AUTO);
+			if (rc != NHB_OK)
+				raise<config_type::exceptions>(rc, "nhb_mul_mat_batch", params.ctx);
+		}
+	}
+
+#ifndef NHB_DISPATCH_HOST_TYPES
+	// the reference's forward declaration, parameter for parameter (include/nihilus-incl/common/kernel_traits.hpp:382-383)
+	template<typename config_type, typename core_traits_type, device_types devive_type, uint64_t, core_types core_type, processing_phases processing_phase>
 	struct kernel_dispatcher_impl;
 
-	template<typename config_type, typename core_traits_type, processing_phases processing_phase>
-	struct kernel_dispatcher_impl<config_type, core_traits_type, device_types::gpu, gpu_arch_index_sm100, processing_phase> {
-		// per-block cores (attention and FFN projections): one handle per transformer block
-		static void impl(core_traits_type& params, int64_t current_block) {
-			std::array<nhb_mul_mat_op, core_traits_type::node_count> ops{};
-			[&]<size_t... i>(std::index_sequence<i...>) {
-				((ops[i] = std::get<i>(params.nodes).describe(static_cast<uint64_t>(current_block))), ...);
-			}(std::make_index_sequence<core_traits_type::node_count>{});
-			if constexpr (processing_phase == processing_phases::eval_time) {
-				for (const auto& op: ops)
-					if (op.M != 1)
-						raise<config_type::exceptions>(NHB_ERR_ARG, "eval_time dispatch with more than one token", params.ctx);
-			}
-			if constexpr (requires { params.norm; }) {
-				static_assert(config_type::act_mode == NHB_ACT_Q8, "the fused norm produces Q8_0 activations");
-				for (auto& op: ops)
-					op.x = static_cast<const float*>(params.norm.input.get_data());
-				const int rc = nhb_rms_norm_mul_mat_batch(params.ctx, ops.data(), static_cast<int>(ops.size()),
-					static_cast<const float*>(params.norm.norm_weight.get_data()), params.norm.eps, params.norm.sqrt_mode, NHB_KERNEL_AUTO);
-				if (rc != NHB_OK)
-					raise<config_type::exceptions>(rc, "nhb_rms_norm_mul_mat_batch", params.ctx);
-			} else {
-				const int rc = nhb_mul_mat_batch(params.ctx, ops.data(), static_cast<int>(ops.size()), config_type::act_mode, NHB_KERNEL_AUTO);
-				if (rc != NHB_OK)
-					raise<config_type::exceptions>(rc, "nhb_mul_mat_batch", params.ctx);
-			}
-		}
-		// global cores (logits): block 0
-		static void impl(core_traits_type& params) {
-			impl(params, 0);
-		}
-	};
+#include "mega_dispatch.inc"
 
-	// the reference's entry (infra/monolithic_dispatcher.hpp:53-62) for a GPU configuration
+	// the reference's entry (infra/monolithic_dispatcher.hpp:53-62) for a GPU configuration: the core names its own core_type
 	template<typename config_type, processing_phases processing_phase, typename core_type> struct kernel_dispatcher {
 		static void impl(core_type& params, int64_t current_block) {
-			kernel_dispatcher_impl<config_type, core_type, config_type::device_type, gpu_arch_index_sm100, processing_phase>::impl(params, current_block);
+			kernel_dispatcher_impl<config_type, core_type, config_type::device_type, gpu_arch_index_sm100, core_type::core_type, processing_phase>::impl(params, current_block);
 		}
 		static void impl(core_type& params) {
-			kernel_dispatcher_impl<config_type, core_type, config_type::device_type, gpu_arch_index_sm100, processing_phase>::impl(params);
+			kernel_dispatcher_impl<config_type, core_type, config_type::device_type, gpu_arch_index_sm100, core_type::core_type, processing_phase>::impl(params);
 		}
 	};
+#endif
 
 	// ---- LLaMA-3-8B projection descriptors (infra/model_traits.hpp:49-65, infra/core_traits.hpp:145-209) ----
 	namespace llama3_8b {
@@ -292,13 +318,15 @@ namespace nihilus_b200 {
 		// attn_norm / ffn_norm in front of their stage
 		using norm_w_t = operand<core_trait_dims<E, 1, 1, 1>, float>;
 		using norm_node = norm_mul_node<kernel_traits<kernel_types::rms_norm, act_t<E>, act_t<E>>, kernel_traits<kernel_types::mul, act_t<E>, act_t<E>, norm_w_t>>;
-		using norm_qkv_core		= norm_mul_mat_core<norm_node, attn_q, attn_k, attn_v>;
-		using norm_gate_up_core = norm_mul_mat_core<norm_node, ffn_gate, ffn_up>;
-		using qkv_core	  = mul_mat_core<attn_q, attn_k, attn_v>;
-		using attn_out_core = mul_mat_core<attn_output>;
-		using gate_up_core	= mul_mat_core<ffn_gate, ffn_up>;
-		using down_core		= mul_mat_core<ffn_down>;
-		using logits_core	= mul_mat_core<output>;
+		// the stages of the reference's cores (infra/core_traits.hpp:575-594 q/k/v, :768-769 attn_out, :976-989 gate/up and down,
+		// :1192-1193 logits)
+		using norm_qkv_core		= norm_mul_mat_core<core_types::mega_qkv_prep_and_cache_publish, norm_node, attn_q, attn_k, attn_v>;
+		using norm_gate_up_core = norm_mul_mat_core<core_types::mega_ffn, norm_node, ffn_gate, ffn_up>;
+		using qkv_core			= mul_mat_core<core_types::mega_qkv_prep_and_cache_publish, attn_q, attn_k, attn_v>;
+		using attn_out_core		= mul_mat_core<core_types::mega_attention_apply, attn_output>;
+		using gate_up_core		= mul_mat_core<core_types::mega_ffn, ffn_gate, ffn_up>;
+		using down_core			= mul_mat_core<core_types::mega_ffn, ffn_down>;
+		using logits_core		= mul_mat_core<core_types::final_norm_and_sampling, output>;
 	}
 
 }

@@ -127,6 +127,11 @@ _sig("nhb_chain_launch", _i, _vp, _vp)
 _sig("nhb_chain_free", _i, _vp, _vp)
 
 
+def _ld(t) -> int:
+    """Leading dimension of a 2-D tensor; a single row may carry any stride (numpy's relaxed strides), which means nothing."""
+    return t.stride(0) if t.shape[0] > 1 else max(int(t.stride(0)), int(t.shape[1]), 1)
+
+
 def _tensor_from_ptr(ptr: int, nbytes: int, device: int, dtype):
     """A torch view of device memory this library owns (no copy; the caller keeps the allocation alive)."""
     import torch
@@ -355,15 +360,15 @@ class Context:
         M = x.shape[0]
         if y is None:
             y = torch.zeros((M, w.N), dtype=torch.float32, device=x.device)
-        _check(lib.nhb_mul_mat(self.handle, w.handle, x.data_ptr(), x.stride(0) if M > 0 else w.K, y.data_ptr(),
-                               y.stride(0) if M > 0 else max(w.N, 1), M, act_mode, kernel), self.handle)
+        _check(lib.nhb_mul_mat(self.handle, w.handle, x.data_ptr(), _ld(x) if M > 0 else w.K, y.data_ptr(),
+                               _ld(y) if M > 0 else max(w.N, 1), M, act_mode, kernel), self.handle)
         return y
 
     def mul_mat_batch(self, ops, act_mode: int = ACT_Q8, kernel: int = KERNEL_AUTO):
         """ops: list of (Weight, x, y) torch tensors."""
         arr = (MulMatOp * len(ops))()
         for i, (w, x, y) in enumerate(ops):
-            arr[i] = MulMatOp(w.handle, x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.shape[0])
+            arr[i] = MulMatOp(w.handle, x.data_ptr(), _ld(x), y.data_ptr(), _ld(y), x.shape[0])
         _check(lib.nhb_mul_mat_batch(self.handle, arr, len(ops), act_mode, kernel), self.handle)
 
     def mul_mat_host(self, w: Weight, x: np.ndarray, y: np.ndarray | None = None, act_mode: int = ACT_Q8, kernel: int = KERNEL_AUTO,
@@ -422,7 +427,7 @@ class Context:
         """ops: list of (Weight, x, y); x is the row before the norm, the same tensor in every op."""
         arr = (MulMatOp * len(ops))()
         for i, (w, x, y) in enumerate(ops):
-            arr[i] = MulMatOp(w.handle, x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.shape[0])
+            arr[i] = MulMatOp(w.handle, x.data_ptr(), _ld(x), y.data_ptr(), _ld(y), x.shape[0])
         _check(lib.nhb_rms_norm_mul_mat_batch(self.handle, arr, len(ops), norm_w.data_ptr(), eps, sqrt_mode, kernel), self.handle)
 
     def memcpy_h2d(self, dst_ptr: int, src_ptr: int, nbytes: int):
@@ -436,7 +441,7 @@ class Context:
         flat = [op for st in stages for op in st]
         arr = (MulMatOp * max(len(flat), 1))()
         for i, (w, x, y) in enumerate(flat):
-            arr[i] = MulMatOp(w.handle, x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.shape[0])
+            arr[i] = MulMatOp(w.handle, x.data_ptr(), _ld(x), y.data_ptr(), _ld(y), x.shape[0])
         counts = (_i * max(len(stages), 1))(*[len(st) for st in stages])
         h = _vp()
         _check(lib.nhb_chain_create(self.handle, arr, counts, len(stages), C.byref(h)), self.handle)

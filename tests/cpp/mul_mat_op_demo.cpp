@@ -34,7 +34,7 @@ static std::vector<char> slurp(const char* path) {
 
 static int check() {
 	// a dispatch without a context must surface as the library's error, through the exception convention
-	using core_t = mul_mat_core<llama3_8b::attn_k>;
+	using core_t = mul_mat_core<core_types::mega_qkv_prep_and_cache_publish, llama3_8b::attn_k>;
 	core_t core{};
 	std::get<0>(core.nodes).activation.get_seq_length_dim() = 1;
 	bool threw = false;
@@ -70,7 +70,7 @@ static int run(char** a, bool with_norm) {
 	if (wk.size() != size_t(N) * (K / 32) * 34 || wv.size() != wk.size() || x.size() != size_t(M) * K * 4)
 		throw std::runtime_error("input sizes do not match attn_k / attn_v and M");
 	using cfg	 = gpu_config<true>;
-	using core_t = mul_mat_core<llama3_8b::attn_k, llama3_8b::attn_v>;
+	using core_t = mul_mat_core<core_types::mega_qkv_prep_and_cache_publish, llama3_8b::attn_k, llama3_8b::attn_v>;
 	nhb_ctx* ctx = nullptr;
 	if (nhb_ctx_create(&ctx, 0, 0, 1) != NHB_OK)
 		raise<true>(NHB_ERR_CUDA, "nhb_ctx_create", nullptr);
@@ -103,7 +103,7 @@ static int run(char** a, bool with_norm) {
 		if (nhb_device_alloc(ctx, nw.size(), &nwd) != NHB_OK)
 			raise<true>(NHB_ERR_NOMEM, "nhb_device_alloc", ctx);
 		nhb_memcpy_h2d(ctx, nwd, nw.data(), nw.size());
-		using ncore_t = norm_mul_mat_core<llama3_8b::norm_node, llama3_8b::attn_k, llama3_8b::attn_v>;
+		using ncore_t = norm_mul_mat_core<core_types::mega_qkv_prep_and_cache_publish, llama3_8b::norm_node, llama3_8b::attn_k, llama3_8b::attn_v>;
 		ncore_t ncore{};
 		ncore.ctx					   = ctx;
 		ncore.norm.input.data[0]	   = xd;

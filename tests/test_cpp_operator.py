@@ -51,6 +51,35 @@ def test_static_checks_reject_a_mismatched_mul_mat(capi, tmp_path):
     assert "inner dimensions must match" in r.stderr
 
 
+# what the reference's cmake would define for an x86-64 Linux CPU build (cmake/flags_and_options.cmake:20-39 and
+# cmake/detection/nihilus_detect_cpu_properties.cmake:171-201); only needed to PARSE its headers
+REFERENCE_DEFINES = [
+    "-DNIHILUS_COMPILER_CUDA=0", "-DNIHILUS_ARCH_X64=1", "-DNIHILUS_ARCH_ARM64=0", "-DNIHILUS_PLATFORM_WINDOWS=0", "-DNIHILUS_PLATFORM_LINUX=1",
+    "-DNIHILUS_PLATFORM_MAC=0", "-DNIHILUS_COMPILER_CLANG=0", "-DNIHILUS_COMPILER_MSVC=0", "-DNIHILUS_COMPILER_GNUCXX=1", "-DNIHILUS_DEV=0",
+    "-DNIHILUS_CUDA_TENSOR_CORES=0", "-DNIHILUS_CUDA_MAX_REGISTERS=0", "-DNIHILUS_GLOBAL=", "-DNIHILUS_AVX2=1", "-DNIHILUS_AVX512=0", "-DNIHILUS_NEON=0",
+    "-DNIHILUS_SVE2=0", "-DNIHILUS_HOST=inline __attribute__((always_inline))", "-DNIHILUS_DEVICE=inline __attribute__((always_inline))",
+    "-DNIHILUS_HOST_DEVICE=inline __attribute__((always_inline))", "-mavx2", "-mfma", "-mf16c", "-mbmi", "-mbmi2", "-mlzcnt", "-mpopcnt",
+]
+
+
+def test_specialisations_fit_the_references_own_dispatcher_declaration():
+    """With the reference tree present: its kernel_traits.hpp is included in place (nothing copied), our specialisation
+    block goes into namespace nihilus unchanged, and dispatching through the reference's primary template reaches it."""
+    from oracle import pyoracle
+
+    ref = pyoracle.reference_root()
+    if not ref or not os.path.isfile(os.path.join(ref, "include", "nihilus-incl", "common", "kernel_traits.hpp")):
+        pytest.skip("reference source tree not present")
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("g++ not available")
+    src = os.path.join(ROOT, "tests", "cpp", "reference_dispatch_check.cpp")
+    cmd = [gxx, "-std=c++23", "-fsyntax-only", *REFERENCE_DEFINES, "-I" + os.path.join(ref, "include"), "-I" + os.path.join(ROOT, "include"),
+           "-I" + os.path.join(ROOT, "tests", "cpp"), src]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-4000:]
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("M", [1, 5, 40])
 def test_dispatch_through_the_cpp_interface_matches_the_oracle(demo, oracle, tmp_path, M):
