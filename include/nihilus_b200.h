@@ -153,6 +153,23 @@ int nhb_mul_mat_block_dots(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev
  * (the fp16-rounded d, widened) [M][K/32] */
 int nhb_quantize_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, int64_t M, int64_t K, int8_t* q_dev, float* d_dev);
 
+/* ---- the element-wise neighbours of the mul_mats in the reference's FFN and attention cores, fused ----
+ * The reference's chains are ffn_gate_mul_mat -> silu -> mul(ffn_up_mul_mat) -> ffn_down_mul_mat -> add(ffn_inp)
+ * (infra/core_traits.hpp:976-992) and attn_out_mul_mat -> add(inp_embd) (:768-772).  Its kernels for silu, mul and add are
+ * empty (cpu/avx_2.hpp:1946-2075, 5325-5330), the traits name the arithmetic: f32, silu(g) = g / (1 + exp(-g)).
+ *   nhb_mul_mat_swiglu_add   y = W . quantise(silu(gate) * up) [+ residual]      W = ffn_down; gate, up [M][ld] with K = W's K
+ *   nhb_mul_mat_add          y = W . quantise(x) + residual                      W = attn_output
+ * For decode (M <= gemv_max_m) SwiGLU runs inside the GEMV's activation prologue and the residual is added as the row is
+ * stored: no intermediate row, no extra launch.  For more tokens the element-wise kernels run around the tensor-core
+ * GEMM.  Q8 arithmetic; the values are those of the separate steps (nhb_swiglu, nhb_mul_mat, a float add), bit for bit.
+ * residual may be NULL in the first; residual[m * ld_residual + n] belongs to output column n (full width N). */
+int nhb_mul_mat_swiglu_add(nhb_ctx* ctx, const nhb_weight* w, const float* gate_dev, const float* up_dev, int64_t ld, const float* residual_dev,
+	int64_t ld_residual, float* y_dev, int64_t ldy, int64_t M);
+int nhb_mul_mat_add(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev, int64_t ldx, const float* residual_dev, int64_t ld_residual, float* y_dev, int64_t ldy,
+	int64_t M);
+/* h[m][k] = silu(gate[m][k]) * up[m][k] on its own (16-byte aligned rows, K, ld and ldh multiples of 4) */
+int nhb_swiglu(nhb_ctx* ctx, const float* gate_dev, const float* up_dev, int64_t ld, float* h_dev, int64_t ldh, int64_t M, int64_t K);
+
 /* ---- rms_norm x norm-weight: the producer of a projection's activations ----
  * Replaces the reference's rms_norm_mul kernel (cpu/avx_2.hpp:3875-3950) and its helpers simd_sum_squares
  * (:758-779), vec_scale_mul_f32 (:3621-3850) and quantize_row_q8_0_avx2 (:671-721), bit for bit:
@@ -173,6 +190,27 @@ int nhb_rms_norm_mul_q8_0(nhb_ctx* ctx, const float* x_dev, int64_t ldx, const f
  * and the GEMV stages it as is; for larger M the normalised rows go through a scratch buffer of the context. */
 int nhb_rms_norm_mul_mat_batch(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, const float* norm_w_dev, float eps, int sqrt_mode,
 	int kernel);
+
+/* ---- the Q8_0 consumers around the projections ---- */
+/* Token-embedding gather: y[m][k] = f32(d) * float(q) of row token_ids[m] of a Q8_0 table [N = vocabulary][K = embedding
+ * length], f32 rows out.  Stands in for the reference's two live GPU kernels (cuda/cuda_12.hpp:560-601 prompt, :691-722
+ * eval) with the prompt kernel's arithmetic in both phases: the reference's eval kernel ignores the token id and reads
+ * row 0 (:710).  The table must be whole on this rank; an id outside [0, N) leaves its row untouched and makes the next
+ * nhb_sync return NHB_ERR_ARG.  token_ids_dev: device int32 [M]; y_dev 16-byte aligned, ldy >= K and a multiple of 4. */
+int nhb_get_rows_q8_0(nhb_ctx* ctx, const nhb_weight* table, const int32_t* token_ids_dev, int64_t M, float* y_dev, int64_t ldy);
+/* The mul_mat side of final_norm_and_sampling (infra/core_traits.hpp:1184-1193): the last of seq_len hidden rows ->
+ * rms_norm x output_norm -> logits = W_output . quantise(row), one launch for decode shapes.  logits_dev: f32 [N]. */
+int nhb_last_token_logits(nhb_ctx* ctx, const nhb_weight* w_output, const float* hidden_dev, int64_t ld, int64_t seq_len, const float* norm_w_dev, float eps,
+	int sqrt_mode, float* logits_dev);
+
+/* ---- cache of repacked weights ---- */
+/* The two planes of this context's shard of a weight as one file (header with shape, rows, rank and world, a checksum, then
+ * the planes), and back: a later start reads the planes straight into device memory instead of reading, sharding and
+ * repacking the tensor's 34-byte blocks (the reference maps and copies the GGUF tensor at every start,
+ * infra/model_parser.hpp:897-940).  nhb_weight_load takes the weight's full shape and refuses a file whose rows are not the
+ * ones this context would own for it (another rank, world size or placement policy), a truncated file or a bad checksum. */
+int nhb_weight_save(nhb_ctx* ctx, const nhb_weight* w, const char* path);
+int nhb_weight_load(nhb_ctx* ctx, const char* path, int64_t N, int64_t K, nhb_weight** out);
 
 /* ---- GGUF reader in front of the upload ----
  * Stands in for the reference's model file parser on this path (infra/model_parser.hpp:635-671 header and metadata,

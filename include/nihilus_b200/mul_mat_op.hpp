@@ -241,6 +241,9 @@ namespace nihilus_b200 {
 		typename mul_traits::input_02_type norm_weight;
 		float eps	  = 1e-5f;// model_traits: layer_norm_rms_epsilon
 		int sqrt_mode = NHB_SQRT_IEEE;
+		// first row of `input` the stage reads: 0, or sequence length - 1 for the last-token view in front of the final norm
+		// (infra/core_traits.hpp:1184)
+		int64_t first_row = 0;
 	};
 
 	// A stage whose mul_mats all read the normalised row: the norm is fused in front of them.  The mul_mat nodes'
@@ -254,9 +257,54 @@ namespace nihilus_b200 {
 		static_assert(((node_types::traits_type::K == norm_node_type::rms_norm_traits::K) && ...), "every mul_mat of the stage must read the normalised row");
 	};
 
+	// ffn_silu -> ffn_gate_par -> ffn_down_mul_mat -> ffn_residual_add as ONE stage (infra/core_traits.hpp:982-992): the down
+	// projection reads silu(gate) * up and adds the residual stream as it stores.  `down.activation` is not read (its extents
+	// carry the token count); `residual.data[0] == nullptr` leaves the add out.
+	template<typename down_node_type> struct ffn_tail_core {
+		static constexpr core_types core_type = core_types::mega_ffn;
+		static constexpr size_t node_count	  = 1;
+		nhb_ctx* ctx						  = nullptr;
+		down_node_type down;
+		typename down_node_type::traits_type::input_02_type gate, up;// f32 [FF, tokens], the gate and up projections' outputs
+		typename down_node_type::traits_type::output_type residual;// ffn_inp, f32 [E, tokens]
+		int run_fused(int64_t block) const {
+			using t					= typename down_node_type::traits_type;
+			const nhb_mul_mat_op op = down.describe(static_cast<uint64_t>(block));
+			return nhb_mul_mat_swiglu_add(ctx, op.w, static_cast<const float*>(gate.get_data()), static_cast<const float*>(up.get_data()), t::K,
+				static_cast<const float*>(residual.get_data()), t::N, op.y, op.ldy, op.M);
+		}
+	};
+
+	// attn_out_mul_mat -> residual_add as one stage (infra/core_traits.hpp:768-772)
+	template<typename node_type> struct mul_mat_add_core {
+		static constexpr core_types core_type = core_types::mega_attention_apply;
+		static constexpr size_t node_count	  = 1;
+		nhb_ctx* ctx						  = nullptr;
+		node_type node;
+		typename node_type::traits_type::output_type residual;// inp_embd, f32 [E, tokens]
+		int run_fused(int64_t block) const {
+			const nhb_mul_mat_op op = node.describe(static_cast<uint64_t>(block));
+			return nhb_mul_mat_add(ctx, op.w, op.x, op.ldx, static_cast<const float*>(residual.get_data()), node_type::traits_type::N, op.y, op.ldy, op.M);
+		}
+	};
+
+	template<typename config_type, bool eval, typename core_traits_type> inline void dispatch_plain_stage(core_traits_type& params, int64_t current_block);
+
 	// What every specialisation in mega_dispatch.inc does: the independent mul_mats of the stage `params` describes, in one
 	// call of the C ABI.  `eval` = the reference's processing_phases::eval_time (one token).
 	template<typename config_type, bool eval, typename core_traits_type> inline void dispatch_stage(core_traits_type& params, int64_t current_block) {
+		if constexpr (requires { params.run_fused(current_block); }) {
+			static_assert(config_type::act_mode == NHB_ACT_Q8, "the fused element-wise stages use the Q8 arithmetic");
+			const int rc = params.run_fused(current_block);
+			if (rc != NHB_OK)
+				raise<config_type::exceptions>(rc, "fused mul_mat stage", params.ctx);
+			return;
+		} else {
+			dispatch_plain_stage<config_type, eval>(params, current_block);
+		}
+	}
+
+	template<typename config_type, bool eval, typename core_traits_type> inline void dispatch_plain_stage(core_traits_type& params, int64_t current_block) {
 		std::array<nhb_mul_mat_op, core_traits_type::node_count> ops{};
 		[&]<size_t... i>(std::index_sequence<i...>) {
 			((ops[i] = std::get<i>(params.nodes).describe(static_cast<uint64_t>(current_block))), ...);
@@ -269,7 +317,7 @@ namespace nihilus_b200 {
 		if constexpr (requires { params.norm; }) {
 			static_assert(config_type::act_mode == NHB_ACT_Q8, "the fused norm produces Q8_0 activations");
 			for (auto& op: ops)
-				op.x = static_cast<const float*>(params.norm.input.get_data());
+				op.x = static_cast<const float*>(params.norm.input.get_data()) + params.norm.first_row * op.ldx;
 			const int rc = nhb_rms_norm_mul_mat_batch(params.ctx, ops.data(), static_cast<int>(ops.size()), static_cast<const float*>(params.norm.norm_weight.get_data()),
 				params.norm.eps, params.norm.sqrt_mode, NHB_KERNEL_AUTO);
 			if (rc != NHB_OK)
@@ -327,6 +375,13 @@ namespace nihilus_b200 {
 		using gate_up_core		= mul_mat_core<core_types::mega_ffn, ffn_gate, ffn_up>;
 		using down_core			= mul_mat_core<core_types::mega_ffn, ffn_down>;
 		using logits_core		= mul_mat_core<core_types::final_norm_and_sampling, output>;
+		// last-token view -> final norm -> logits (infra/core_traits.hpp:1184-1193): set norm.first_row = sequence length - 1
+		using logits_act_t	   = operand<core_trait_dims<E, 1, 1, 1>, float>;// one token, whatever the sequence length
+		using last_token_output = mul_mat_node<kernel_traits<kernel_types::mul_mat, operand<core_trait_dims<V, 1, 1, 1>, float>, weight_t<E, V, 1>, logits_act_t>>;
+		using norm_logits_core = norm_mul_mat_core<core_types::final_norm_and_sampling, norm_node, last_token_output>;
+		// the fused tails of the FFN and attention cores
+		using ffn_tail	   = ffn_tail_core<ffn_down>;
+		using attn_out_add = mul_mat_add_core<attn_output>;
 	}
 
 }

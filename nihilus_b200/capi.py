@@ -39,7 +39,8 @@ EXPORTS = (
     "nhb_rms_norm_mul", "nhb_rms_norm_mul_q8_0", "nhb_rms_norm_mul_mat_batch",
     "nhb_gguf_open", "nhb_gguf_last_error", "nhb_gguf_close", "nhb_gguf_tensor_count", "nhb_gguf_find", "nhb_gguf_tensor_get",
     "nhb_gguf_get_number", "nhb_gguf_get_string", "nhb_gguf_upload_q8_0", "nhb_gguf_read_f32",
-    "nhb_chain_create", "nhb_chain_launch", "nhb_chain_free",
+    "nhb_chain_create", "nhb_chain_launch", "nhb_chain_free", "nhb_mul_mat_swiglu_add", "nhb_mul_mat_add", "nhb_swiglu",
+    "nhb_get_rows_q8_0", "nhb_last_token_logits", "nhb_weight_save", "nhb_weight_load",
 )
 
 
@@ -122,6 +123,13 @@ _sig("nhb_mul_mat_q8_0_noalloc", _i, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _i64,
 _sig("nhb_noalloc_max_bytes", _i64)
 _sig("nhb_noalloc_last_error", C.c_char_p)
 _sig("nhb_all_gather_batch", _i, _vp, C.POINTER(_vp), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), _i)
+_sig("nhb_mul_mat_swiglu_add", _i, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64)
+_sig("nhb_mul_mat_add", _i, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64)
+_sig("nhb_swiglu", _i, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64)
+_sig("nhb_get_rows_q8_0", _i, _vp, _vp, _vp, _i64, _vp, _i64)
+_sig("nhb_last_token_logits", _i, _vp, _vp, _vp, _i64, _i64, _vp, C.c_float, _i, _vp)
+_sig("nhb_weight_save", _i, _vp, _vp, C.c_char_p)
+_sig("nhb_weight_load", _i, _vp, C.c_char_p, _i64, _i64, C.POINTER(_vp))
 _sig("nhb_chain_create", _i, _vp, C.POINTER(MulMatOp), C.POINTER(_i), _i, C.POINTER(_vp))
 _sig("nhb_chain_launch", _i, _vp, _vp)
 _sig("nhb_chain_free", _i, _vp, _vp)
@@ -205,6 +213,10 @@ class Weight:
         _check(lib.nhb_weight_info_get(handle, C.byref(info)))
         self.N, self.K, self.n0, self.n1 = info.N, info.K, info.n0, info.n1
         self.q_ptr, self.d_ptr, self.bytes_q8 = info.q, info.d, info.bytes_q8
+
+    def save(self, path: str):
+        """This shard's repacked planes as a cache file (nhb_weight_save)."""
+        _check(lib.nhb_weight_save(self.ctx.handle, self.handle, os.fsencode(path)), self.ctx.handle)
 
     def download(self) -> np.ndarray:
         out = np.empty((self.n1 - self.n0, self.K // 32, 34), dtype=np.uint8)
@@ -352,6 +364,30 @@ class Context:
         _check(lib.nhb_weight_upload_q8_0(self.handle, blocks.ctypes.data, N, nb * 32, C.byref(h)), self.handle)
         return Weight(self, h.value)
 
+    def load_weight(self, path: str, N: int, K: int) -> Weight:
+        """A weight from its cache file (nhb_weight_load): the planes go straight to the device."""
+        h = _vp()
+        _check(lib.nhb_weight_load(self.handle, os.fsencode(path), N, K, C.byref(h)), self.handle)
+        return Weight(self, h.value)
+
+    def get_rows(self, table: Weight, token_ids, y=None):
+        """Token-embedding gather: token_ids torch cuda int32 [M] -> f32 [M, K]."""
+        import torch
+
+        M = token_ids.shape[0]
+        if y is None:
+            y = torch.zeros((M, table.K), dtype=torch.float32, device=token_ids.device)
+        _check(lib.nhb_get_rows_q8_0(self.handle, table.handle, token_ids.data_ptr(), M, y.data_ptr(), _ld(y) if M else table.K), self.handle)
+        return y
+
+    def last_token_logits(self, w: Weight, hidden, norm_w, eps: float, sqrt_mode: int = SQRT_IEEE):
+        import torch
+
+        seq = hidden.shape[0]
+        out = torch.zeros((1, w.N), dtype=torch.float32, device=hidden.device)
+        _check(lib.nhb_last_token_logits(self.handle, w.handle, hidden.data_ptr(), _ld(hidden), seq, norm_w.data_ptr(), eps, sqrt_mode, out.data_ptr()), self.handle)
+        return out
+
     # ---- device-pointer level (torch tensors supply the memory) ----
     def mul_mat(self, w: Weight, x, y=None, act_mode: int = ACT_Q8, kernel: int = KERNEL_AUTO):
         """x: torch cuda f32 [M, K] (row stride allowed) -> y f32 [M, N] (this shard's columns written)."""
@@ -384,6 +420,37 @@ class Context:
         if sync:
             self.sync()
         return y
+
+    def mul_mat_swiglu_add(self, w: Weight, gate, up, residual=None, y=None):
+        """y = W . quantise(silu(gate) * up) [+ residual] (the FFN tail of a block)."""
+        import torch
+
+        M = gate.shape[0]
+        if y is None:
+            y = torch.zeros((M, w.N), dtype=torch.float32, device=gate.device)
+        _check(lib.nhb_mul_mat_swiglu_add(self.handle, w.handle, gate.data_ptr(), up.data_ptr(), _ld(gate) if M else w.K,
+                                          residual.data_ptr() if residual is not None else None, _ld(residual) if residual is not None and M else max(w.N, 1),
+                                          y.data_ptr(), _ld(y) if M else max(w.N, 1), M), self.handle)
+        return y
+
+    def mul_mat_add(self, w: Weight, x, residual, y=None):
+        """y = W . quantise(x) + residual (attn_output and the residual stream)."""
+        import torch
+
+        M = x.shape[0]
+        if y is None:
+            y = torch.zeros((M, w.N), dtype=torch.float32, device=x.device)
+        _check(lib.nhb_mul_mat_add(self.handle, w.handle, x.data_ptr(), _ld(x) if M else w.K, residual.data_ptr(), _ld(residual) if M else max(w.N, 1),
+                                   y.data_ptr(), _ld(y) if M else max(w.N, 1), M), self.handle)
+        return y
+
+    def swiglu(self, gate, up):
+        import torch
+
+        M, K = gate.shape
+        h = torch.empty((M, K), dtype=torch.float32, device=gate.device)
+        _check(lib.nhb_swiglu(self.handle, gate.data_ptr(), up.data_ptr(), _ld(gate) if M else K, h.data_ptr(), K, M, K), self.handle)
+        return h
 
     def block_dots(self, w: Weight, x):
         import torch

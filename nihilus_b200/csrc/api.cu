@@ -13,7 +13,7 @@
 #include <string>
 #include <vector>
 
-#include "internal.h"
+#include "api_types.h"
 
 using namespace nhb;
 
@@ -23,7 +23,6 @@ using namespace nhb;
 // ---------------------------------------------------------------------------------------------------------------
 namespace {
 
-	typedef struct ncclComm* ncclComm_t;
 	struct nccl_uid {
 		char internal[128];
 	};
@@ -75,89 +74,7 @@ namespace {
 
 }
 
-struct nhb_ctx {
-	int device		   = 0;
-	int rank		   = 0;
-	int world		   = 1;
-	int sm_count	   = 148;
-	cudaStream_t own   = nullptr;
-	cudaStream_t stream = nullptr;
-	int* dev_status	   = nullptr;
-	int* host_status   = nullptr;// pinned
-	void* scratch	   = nullptr;
-	size_t scratch_cap = 0;
-	void* io		   = nullptr;
-	size_t io_cap	   = 0;
-	ncclComm_t comm	   = nullptr;
-	bool pdl		   = true;
-	int gemv_max_m	   = 8;
-	int ctas_per_sm	   = 1;// streaming GEMV: persistent CTAs per SM
-	int rows_cps	   = 3;// warp-per-row GEMV: grid cap in CTAs per SM
-	int preq		   = 0;// warp-per-row GEMV: quantise activations in a separate kernel
-	// set only while nhb_rms_norm_mul_mat_batch runs: the GEMV's activations come from the norm kernel, already quantised
-	const float* norm_w = nullptr;
-	float norm_eps		= 0.f;
-	int norm_sqrt		= 0;
-	void* norm_buf		= nullptr;// normalised f32 rows for the paths that quantise for themselves
-	size_t norm_cap		= 0;
-	int rows_db		   = -1;// warp-per-row GEMV: two items in flight per warp (1), one (0), or chosen per launch (-1)
-	int rows_cluster   = 1;// warp-per-row GEMV: CTAs per cluster sharing the activation quantisation
-	int rows_fat	   = 1;// warp-per-row GEMV: one 24-warp CTA per SM for launches with enough rows
-	int rows_split	   = 1;// ... and within those, the item-parallel kernel for rows longer than 4096
-	int gemv_default   = NHB_KERNEL_GEMV_ROWS;
-	bool capturing	   = false;
-	long long launches = 0;
-	std::string err;
-	// fused all-gather (decode GEMV): peer-mapped output regions, the flag array every rank can write, local counters
-	struct symm_region {
-		char* local	 = nullptr;
-		size_t bytes = 0;
-		char* peer[NHB_MAX_WORLD] = {};// this rank's own entry is `local`
-	};
-	// outputs whose rows are already whole on every rank (delivered by a fused launch, or computed from a replicated
-	// weight): nhb_all_gather has nothing to do for them.  Keyed by the output pointer the caller passes.
-	std::vector<const void*> complete;
-	int64_t replicate_below = 0;// bytes: smaller weights are kept whole on every rank instead of row-sharded
-	std::vector<symm_region> regions;
-	// upload staging: two pinned host buffers, two device buffers, an event each (kept for the next upload)
-	void* up_pinned[2]	   = { nullptr, nullptr };
-	void* up_dev[2]		   = { nullptr, nullptr };
-	cudaEvent_t up_done[2] = { nullptr, nullptr };
-	size_t up_cap		   = 0;
-	unsigned* push_local = nullptr;// [0] CTAs done in the running launch, [1] fused launches completed
-	int fused_gather	 = 1;
-	bool pending_wait	 = false;// a delivering launch was enqueued and no later launch of this context has waited for the peers yet
-	long long peer_wait_us = 2000000;// bound of a kernel's wait for the other ranks' announcements
-	int symm_loopback	 = 0;// test aid: "peer" mappings alias this rank's own memory, so no announcement ever arrives
-	unsigned long long err_seq = 0;
-};
-
-struct nhb_weight {
-	int64_t N = 0, K = 0, n0 = 0, n1 = 0;
-	int8_t* q	= nullptr;
-	__half* d	= nullptr;
-	__half* w16 = nullptr;// fp16 copy of the quants for the tensor-core GEMM, made on first use
-	float* wdT	= nullptr;// f32 block-major copy of the scales [K/32][gemm_tc_pad(rows)], made with it
-	int device	= 0;
-};
-
-// A recorded sequence of dependent decode stages (nhb_chain_*): one warp-per-row GEMV launch per stage, each told what the
-// next one will read first
-struct nhb_chain {
-	std::vector<rows_batch> stages;// launch descriptors, prefetch hints included
-	int M = 0;
-	std::vector<const void*> delivered;// outputs the launches complete on every rank
-	std::vector<const void*> written;// every output pointer they write
-	std::vector<char> delivers;// per stage: its rows go to the other ranks
-	int device = 0;
-};
-
-struct nhb_graph {
-	cudaGraph_t graph	 = nullptr;
-	cudaGraphExec_t exec = nullptr;
-};
-
-namespace {
+namespace nhb {
 
 	int fail(nhb_ctx* ctx, int code, const std::string& msg) {
 		g_err	  = msg;
@@ -173,35 +90,6 @@ namespace {
 		return fail(ctx, NHB_ERR_CUDA, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
 	}
 
-#define NHB_CUDA(ctx, call) \
-	do { \
-		cudaError_t e__ = (call); \
-		if (e__ != cudaSuccess) \
-			return fail_cuda(ctx, e__, #call); \
-	} while (0)
-
-	struct device_guard {
-		int prev = -1;
-		bool ok	 = true;
-		explicit device_guard(int dev) {
-			if (cudaGetDevice(&prev) != cudaSuccess) {
-				ok = false;
-				return;
-			}
-			if (prev != dev && cudaSetDevice(dev) != cudaSuccess)
-				ok = false;
-		}
-		~device_guard() {
-			if (prev >= 0)
-				cudaSetDevice(prev);
-		}
-	};
-
-	int env_int(const char* name, int dflt) {
-		const char* v = std::getenv(name);
-		return (v && *v) ? std::atoi(v) : dflt;
-	}
-
 	launch_cfg cfg_of(nhb_ctx* ctx) {
 		launch_cfg c;
 		c.stream	 = ctx->stream;
@@ -211,6 +99,18 @@ namespace {
 		return c;
 	}
 
+}
+
+namespace {
+
+	int env_int(const char* name, int dflt) {
+		const char* v = std::getenv(name);
+		return (v && *v) ? std::atoi(v) : dflt;
+	}
+
+}
+
+namespace nhb {
 	int ensure(nhb_ctx* ctx, void** buf, size_t* cap, size_t need, const char* what) {
 		if (need <= *cap)
 			return NHB_OK;
@@ -226,6 +126,10 @@ namespace {
 		*cap = need;
 		return NHB_OK;
 	}
+
+}
+
+namespace {
 
 	int check_mm_args(nhb_ctx* ctx, const nhb_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy, int64_t M) {
 		if (!ctx || !w)
@@ -441,6 +345,9 @@ namespace {
 		return bytes >= (int64_t(4) << 20) && bytes <= (int64_t(40) << 20);
 	}
 
+}
+
+namespace nhb {
 	// Rows delivered by a fused launch are whole on this rank only after the other ranks' announcements have arrived.  The
 	// decode GEMV kernels wait for them in their own prologue; in front of anything else that may read such rows this
 	// enqueues a one-warp kernel that does nothing but that (bounded) wait.
@@ -457,6 +364,9 @@ namespace {
 		ctx->pending_wait = false;
 		return NHB_OK;
 	}
+}
+
+namespace {
 
 	// GEMV family over M rows (looping over row groups the kernels support)
 	int run_gemv(nhb_ctx* ctx, const nhb_mul_mat_op* ops, int n_ops, int act_mode, int kernel) {
@@ -925,6 +835,8 @@ int nhb_sync(nhb_ctx* ctx) {
 		}
 		ctx->pending_wait = false;
 		cudaStreamSynchronize(ctx->stream);
+		if (code == DEV_BAD_INDEX)
+			return fail(ctx, NHB_ERR_ARG, "a token id outside the embedding table reached nhb_get_rows_q8_0; its output row was left untouched");
 		return fail(ctx, NHB_ERR_TIMEOUT, "a device-side wait ran out (code " + std::to_string(code) + "); results of the last launches are invalid");
 	}
 	return NHB_OK;
@@ -1204,6 +1116,122 @@ int nhb_mul_mat_host(nhb_ctx* ctx, const nhb_weight* w, const float* x_host, int
 		return rc;
 	if (rows > 0)
 		NHB_CUDA(ctx, cudaMemcpy2DAsync(y_host + w->n0, ldy * 4, yd + w->n0, w->N * 4, rows * 4, M, cudaMemcpyDeviceToHost, ctx->stream));
+	return NHB_OK;
+}
+
+namespace {
+	// y = W . act(x [, x2]) [+ res]: the GEMV family with the element-wise neighbours fused into its prologue and epilogue, or
+	// -- for more tokens than it takes -- the two element-wise kernels around the tensor-core GEMM.  Same values either way.
+	int run_fused(nhb_ctx* ctx, const nhb_weight* w, const float* x, const float* x2, int64_t ldx, const float* res, int64_t ldr, float* y, int64_t ldy, int64_t M,
+		const char* who) {
+		int rc = check_mm_args(ctx, w, x, ldx, y, ldy, M);
+		if (rc != NHB_OK)
+			return rc;
+		if (M == 0)
+			return NHB_OK;
+		if (x2 && (reinterpret_cast<uintptr_t>(x2) & 15))
+			return fail(ctx, NHB_ERR_ARG, std::string(who) + ": the up projection's rows must be 16-byte aligned");
+		if (res && ldr < w->N)
+			return fail(ctx, NHB_ERR_ARG, std::string(who) + ": residual leading dimension smaller than the row length");
+		device_guard g(ctx->device);
+		const int64_t rows = w->n1 - w->n0;
+		auto& c			   = ctx->complete;
+		if (ctx->world > 1) {
+			c.erase(std::remove(c.begin(), c.end(), static_cast<const void*>(y)), c.end());
+			if (rows == w->N)
+				c.push_back(y);
+		}
+		if (rows == 0)
+			return NHB_OK;
+		const bool gemv = M <= ctx->gemv_max_m && gemv_rows_supports(w->K, std::min<int64_t>(M, 4)) && gemv_rows_act_bytes(w->K, 1) <= 96 * 1024;
+		if (gemv) {
+			const launch_cfg cfg = cfg_of(ctx);
+			int launches		 = 0;
+			int mt_max			 = 4;
+			while (mt_max > 1 && gemv_rows_act_bytes(w->K, mt_max) > 96 * 1024)
+				--mt_max;
+			for (int64_t m0 = 0; m0 < M; m0 += mt_max) {
+				const int mt = static_cast<int>(std::min<int64_t>(mt_max, M - m0));
+				nhb_mul_mat_op op{ w, x, ldx, y, ldy, M };
+				rows_batch b{};
+				const nhb_mul_mat_op* src_ops[NHB_MAX_BATCH];
+				fill_rows_batch(&op, 1, m0, mt, false, b, src_ops);
+				b.op[0].x2	= x2 ? x2 + m0 * ldx : nullptr;
+				b.op[0].res = res ? res + m0 * ldr + w->n0 : nullptr;
+				b.op[0].ldr = ldr;
+				const bool pushed = ctx->rows_cluster <= 1 && w->N >= ctx->world && setup_push(ctx, b, src_ops, mt, m0);
+				if (pushed && m0 + mt >= M)
+					c.push_back(y);
+				setup_peer_wait(ctx, b.push);
+				cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, false, 1, ctx->rows_fat != 0, ctx->rows_split != 0);
+				if (e != cudaSuccess)
+					return fail_cuda(ctx, e, "gemv_q8_rows launch (fused element-wise)");
+				if (b.push.wait_world > 1)
+					ctx->pending_wait = pushed;
+			}
+			ctx->launches += launches;
+			return NHB_OK;
+		}
+		// the GEMM path: SwiGLU into a scratch row block, the contraction, then the residual on this rank's columns
+		if (!gemm_tc_supports(rows, w->K, M))
+			return fail(ctx, NHB_ERR_UNSUPPORTED, std::string(who) + ": shape not supported by the tensor-core GEMM (needs K % 64 == 0)");
+		const float* act = x;
+		int64_t ld_act	 = ldx;
+		if (x2) {
+			rc = ensure(ctx, &ctx->norm_buf, &ctx->norm_cap, static_cast<size_t>(M) * w->K * 4, "SwiGLU scratch");
+			if (rc == NHB_OK)
+				rc = wait_pending(ctx);
+			if (rc != NHB_OK)
+				return rc;
+			cudaError_t e = launch_swiglu(x, x2, ldx, static_cast<float*>(ctx->norm_buf), w->K, static_cast<int>(M), static_cast<int>(w->K), ctx->stream, ctx->pdl);
+			if (e != cudaSuccess)
+				return fail_cuda(ctx, e, "swiglu launch");
+			ctx->launches += 1;
+			act	   = static_cast<const float*>(ctx->norm_buf);
+			ld_act = w->K;
+		}
+		nhb_mul_mat_op op{ w, act, ld_act, y, ldy, M };
+		rc = run_gemm(ctx, op);
+		if (rc != NHB_OK)
+			return rc;
+		if (res) {
+			cudaError_t e = launch_add_rows(y + w->n0, ldy, res + w->n0, ldr, static_cast<int>(M), static_cast<int>(rows), ctx->stream, ctx->pdl);
+			if (e != cudaSuccess)
+				return fail_cuda(ctx, e, "residual add launch");
+			ctx->launches += 1;
+		}
+		return NHB_OK;
+	}
+}
+
+int nhb_mul_mat_swiglu_add(nhb_ctx* ctx, const nhb_weight* w, const float* gate_dev, const float* up_dev, int64_t ld, const float* residual_dev, int64_t ld_residual,
+	float* y_dev, int64_t ldy, int64_t M) {
+	if (M > 0 && !up_dev)
+		return fail(ctx, NHB_ERR_ARG, "nhb_mul_mat_swiglu_add: null up-projection pointer");
+	return run_fused(ctx, w, gate_dev, up_dev, ld, residual_dev, ld_residual, y_dev, ldy, M, "nhb_mul_mat_swiglu_add");
+}
+
+int nhb_mul_mat_add(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev, int64_t ldx, const float* residual_dev, int64_t ld_residual, float* y_dev, int64_t ldy,
+	int64_t M) {
+	if (M > 0 && !residual_dev)
+		return fail(ctx, NHB_ERR_ARG, "nhb_mul_mat_add: null residual pointer");
+	return run_fused(ctx, w, x_dev, nullptr, ldx, residual_dev, ld_residual, y_dev, ldy, M, "nhb_mul_mat_add");
+}
+
+int nhb_swiglu(nhb_ctx* ctx, const float* gate_dev, const float* up_dev, int64_t ld, float* h_dev, int64_t ldh, int64_t M, int64_t K) {
+	if (!ctx || M < 0 || K < 0 || K % 4 != 0 || ld < K || ldh < K || (ld & 3) || (ldh & 3) || M > INT32_MAX || K > INT32_MAX)
+		return fail(ctx, NHB_ERR_ARG, "nhb_swiglu: bad arguments (K, ld and ldh are multiples of 4)");
+	if (M == 0 || K == 0)
+		return NHB_OK;
+	if (!gate_dev || !up_dev || !h_dev || ((reinterpret_cast<uintptr_t>(gate_dev) | reinterpret_cast<uintptr_t>(up_dev) | reinterpret_cast<uintptr_t>(h_dev)) & 15))
+		return fail(ctx, NHB_ERR_ARG, "nhb_swiglu: null or misaligned pointer");
+	device_guard g(ctx->device);
+	if (int rc = wait_pending(ctx); rc != NHB_OK)
+		return rc;
+	cudaError_t e = launch_swiglu(gate_dev, up_dev, ld, h_dev, ldh, static_cast<int>(M), static_cast<int>(K), ctx->stream, ctx->pdl);
+	if (e != cudaSuccess)
+		return fail_cuda(ctx, e, "swiglu launch");
+	ctx->launches += 1;
 	return NHB_OK;
 }
 

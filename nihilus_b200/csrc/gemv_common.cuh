@@ -33,10 +33,11 @@ namespace nhb {
 
 	// Prologue of the GEMV kernels: quantise every distinct input of the batch into shared memory.  Run by `nthreads` threads
 	// (tid 0 .. nthreads-1) that meet at named barrier `bar_id` (0: the whole CTA).  COHERENT: read the activations past L1.
+	// SWIGLU: honour rows_op::x2 (the activation is silu(x) * x2).
 	// Layout of one input, per row m: the first 16 bytes of every block (uint4 [nb]), then the second 16 bytes
 	// (uint4 [nb]) -- two planes, so that a warp reading one block per lane touches consecutive 16-byte words (no bank
 	// conflicts) -- and after all MT rows the f32 scales [MT][nb].
-	template<int MT, bool NORM = false, bool COHERENT = false> __device__ __forceinline__ void quantize_inputs(const rows_batch& b, unsigned char* act_smem, int tid, int nthreads, int bar_id = 0) {
+	template<int MT, bool NORM = false, bool COHERENT = false, bool SWIGLU = false> __device__ __forceinline__ void quantize_inputs(const rows_batch& b, unsigned char* act_smem, int tid, int nthreads, int bar_id = 0) {
 		const uint32_t cn = cluster_size();
 		const uint32_t cr = cluster_rank();
 		for (int s = 0; s < b.n_slots; ++s) {
@@ -129,8 +130,18 @@ namespace nhb {
 					const int hb	= i >> 1;
 					const int m		= hb / nb;
 					const int blk	= hb - m * nb;
-					const float4* p = reinterpret_cast<const float4*>(x + static_cast<size_t>(m) * ldx + static_cast<size_t>(blk) * QK) + (i & 1) * 4;
-					const float4 v0 = ld_act4<COHERENT>(p), v1 = ld_act4<COHERENT>(p + 1), v2 = ld_act4<COHERENT>(p + 2), v3 = ld_act4<COHERENT>(p + 3);
+					const size_t at = static_cast<size_t>(m) * ldx + static_cast<size_t>(blk) * QK + (i & 1) * 16;
+					const float4* p = reinterpret_cast<const float4*>(x + at);
+					float4 v0 = ld_act4<COHERENT>(p), v1 = ld_act4<COHERENT>(p + 1), v2 = ld_act4<COHERENT>(p + 2), v3 = ld_act4<COHERENT>(p + 3);
+					if constexpr (SWIGLU) {
+						if (op->x2) {// SwiGLU in front of the quantiser: x holds the gate projection's rows, x2 the up projection's
+							const float4* u = reinterpret_cast<const float4*>(op->x2 + at);
+							v0				= swiglu4(v0, ld_act4<COHERENT>(u));
+							v1				= swiglu4(v1, ld_act4<COHERENT>(u + 1));
+							v2				= swiglu4(v2, ld_act4<COHERENT>(u + 2));
+							v3				= swiglu4(v3, ld_act4<COHERENT>(u + 3));
+						}
+					}
 					float amax		= absmax4(v0, absmax4(v1, absmax4(v2, absmax4(v3, 0.f))));
 					amax			= fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
 					const act_scale sc = q8_scales(amax);

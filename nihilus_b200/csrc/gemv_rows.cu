@@ -140,7 +140,9 @@ namespace nhb {
 
 		// NORM: the rms_norm x norm-weight producer runs inside the prologue (its own instantiation, so that the plain
 		// kernels keep their register allocation)
-		template<int MT, int OCC, int TPB = ROWS_TPB, bool F32 = false, bool NORM = false> __global__ void __launch_bounds__(TPB, OCC)
+		// EPI: the element-wise neighbours fused in -- SwiGLU in front of the quantiser (rows_op::x2) and the residual added to the
+		// output (rows_op::res); its own instantiations, so that the plain kernels keep their register allocation
+		template<int MT, int OCC, int TPB = ROWS_TPB, bool F32 = false, bool NORM = false, bool EPI = false> __global__ void __launch_bounds__(TPB, OCC)
 			gemv_q8_rows(const __grid_constant__ rows_batch b) {
 			constexpr int WARPS = TPB / 32;
 			extern __shared__ __align__(128) unsigned char act_smem[];
@@ -166,7 +168,7 @@ namespace nhb {
 			if constexpr (F32)
 				stage_inputs_f32<MT>(b, act_smem, tid);
 			else
-				quantize_inputs<MT, NORM>(b, act_smem, tid, TPB);
+				quantize_inputs<MT, NORM, false, EPI>(b, act_smem, tid, TPB);
 			// ---- rows ----
 			for (int row = row0; row < total_rows; row += W) {
 				while (cur + 1 < n_ops && row >= b.op[cur + 1].row_begin)
@@ -203,7 +205,7 @@ namespace nhb {
 				if (lane == 0) {
 #pragma unroll
 					for (int m = 0; m < MT; ++m)
-						yrow[static_cast<size_t>(m) * ldy] = rowacc[m];
+						yrow[static_cast<size_t>(m) * ldy] = (EPI && op->res) ? rowacc[m] + op->res[static_cast<size_t>(m) * op->ldr + lrow] : rowacc[m];
 				}
 			}
 			if (b.push.world > 1) {
@@ -241,7 +243,7 @@ namespace nhb {
 		// added per row in ascending order -- the same order, hence the same bits, as the one-warp-per-row kernels.
 		// All ops of the launch must share K.
 		constexpr int SPLIT_MAX_ROWS = 64;// rows per CTA the partial-sum array is sized for
-		template<int MT, bool F32 = false> __global__ void __launch_bounds__(ROWS_TPB_FAT, 1) gemv_q8_rows_split(const __grid_constant__ rows_batch b) {
+		template<int MT, bool F32 = false, bool EPI = false> __global__ void __launch_bounds__(ROWS_TPB_FAT, 1) gemv_q8_rows_split(const __grid_constant__ rows_batch b) {
 			constexpr int WARPS = ROWS_WARPS_FAT;
 			extern __shared__ __align__(128) unsigned char act_smem[];
 			__shared__ float part[SPLIT_MAX_ROWS * 8 * MT];// [row][item][m]
@@ -271,7 +273,7 @@ namespace nhb {
 			if constexpr (F32)
 				stage_inputs_f32<MT>(b, act_smem, tid);
 			else
-				quantize_inputs<MT>(b, act_smem, tid, ROWS_TPB_FAT);
+				quantize_inputs<MT, false, false, EPI>(b, act_smem, tid, ROWS_TPB_FAT);
 			for (int it = warp; it < n_items; it += WARPS) {
 				const int rl  = it / ipr;
 				const int b0  = (it - rl * ipr) * 32 * ITEM;
@@ -310,7 +312,11 @@ namespace nhb {
 				ocur			  = rows_find_op(b, row, 0);
 				const rows_op* op = &b.op[ocur];
 				const size_t off  = static_cast<size_t>(m) * op->ldy + (row - op->row_begin);
-				op->y[off]		  = v;
+				if constexpr (EPI) {
+					if (op->res)
+						v += op->res[static_cast<size_t>(m) * op->ldr + (row - op->row_begin)];
+				}
+				op->y[off] = v;
 				if (b.push.world > 1)
 					for (int r = 0; r < b.push.world; ++r)
 						if (r != b.push.rank && b.y_peer[ocur][r])
@@ -506,6 +512,16 @@ namespace nhb {
 				f.split_long_rows = false;
 				f.ctas_per_sm	  = 2;
 			}
+			bool epi = false;
+			for (int i = 0; i < b.n_ops; ++i)
+				epi = epi || b.op[i].x2 || b.op[i].res;
+			if (epi) {// fused SwiGLU / residual: the plain Q8 shapes at one 24-warp CTA or two 8-warp CTAs per SM
+				if (b.f32act || b.norm_w || b.preq || M > 4)
+					return false;
+				f.double_buffer = false;
+				f.cluster		= 1;
+				f.ctas_per_sm	= 2;
+			}
 			if (M > 4) {// 5 to 8 rows per pass: one kernel shape (more rows per pass means more shared-memory traffic per weight byte, not more HBM)
 				if (b.f32act || b.norm_w)
 					return false;
@@ -581,6 +597,11 @@ namespace nhb {
 		const size_t smem = b.norm_w ? static_cast<size_t>(b.norm_off) + gemv_rows_norm_bytes(b.op[0].K, M) : static_cast<size_t>(b.act_bytes);
 		if (smem > (b.norm_w ? gemv_rows_norm_smem_cap(fat) : 100 * 1024))
 			return cudaErrorInvalidValue;
+		bool epi = false;// a fused element-wise neighbour somewhere in the batch: the EPI instantiations (plain Q8 shapes only)
+		for (int i = 0; i < b.n_ops; ++i)
+			epi = epi || b.op[i].x2 || b.op[i].res;
+		if (epi && (b.f32act || b.norm_w || b.preq || double_buffer || cluster > 1 || M > 4))
+			return cudaErrorInvalidValue;
 		cudaError_t e = cudaErrorInvalidValue;
 		cudaLaunchConfig_t lc{};
 		lc.gridDim			= dim3(grid);
@@ -653,8 +674,36 @@ namespace nhb {
 		NHB_ROWS_F32_CASE(3)
 		NHB_ROWS_F32_CASE(4)
 #undef NHB_ROWS_F32_CASE
+#define NHB_ROWS_EPI_CASE(MT) \
+	if (epi && M == MT) { \
+		e = cudaSuccess; \
+		if (split) { \
+			auto kern = gemv_q8_rows_split<MT, false, true>; \
+			if (smem > 32 * 1024) \
+				e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+			if (e == cudaSuccess) \
+				e = cudaLaunchKernelEx(&lc, kern, b); \
+		} else if (fat) { \
+			auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT, false, false, true>; \
+			if (smem > 48 * 1024) \
+				e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+			if (e == cudaSuccess) \
+				e = cudaLaunchKernelEx(&lc, kern, b); \
+		} else { \
+			auto kern = gemv_q8_rows<MT, 2, ROWS_TPB, false, false, true>; \
+			if (smem > 48 * 1024) \
+				e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+			if (e == cudaSuccess) \
+				e = cudaLaunchKernelEx(&lc, kern, b); \
+		} \
+	}
+		NHB_ROWS_EPI_CASE(1)
+		NHB_ROWS_EPI_CASE(2)
+		NHB_ROWS_EPI_CASE(3)
+		NHB_ROWS_EPI_CASE(4)
+#undef NHB_ROWS_EPI_CASE
 #define NHB_ROWS_SPLIT_CASE(MT) \
-	if (!b.f32act && !b.norm_w && split && M == MT) { \
+	if (!epi && !b.f32act && !b.norm_w && split && M == MT) { \
 		auto kern = gemv_q8_rows_split<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 32 * 1024) /* the kernel also has static shared memory */ \
@@ -668,7 +717,7 @@ namespace nhb {
 		NHB_ROWS_SPLIT_CASE(4)
 #undef NHB_ROWS_SPLIT_CASE
 #define NHB_ROWS_FAT_CASE(MT) \
-	if (!b.f32act && !b.norm_w && fat && !split && M == MT) { \
+	if (!epi && !b.f32act && !b.norm_w && fat && !split && M == MT) { \
 		auto kern = gemv_q8_rows<MT, 1, ROWS_TPB_FAT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
@@ -682,7 +731,7 @@ namespace nhb {
 		NHB_ROWS_FAT_CASE(4)
 #undef NHB_ROWS_FAT_CASE
 #define NHB_ROWS_CASE(MT, OCC) \
-	if (!b.f32act && !b.norm_w && !fat && M == MT && occ == OCC) { \
+	if (!epi && !b.f32act && !b.norm_w && !fat && M == MT && occ == OCC) { \
 		auto kern = gemv_q8_rows<MT, OCC>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \
@@ -718,7 +767,7 @@ namespace nhb {
 		NHB_ROWS_WIDE_CASE(8)
 #undef NHB_ROWS_WIDE_CASE
 #define NHB_ROWS_DB_CASE(MT) \
-	if (!b.f32act && !b.norm_w && double_buffer && M == MT) { \
+	if (!epi && !b.f32act && !b.norm_w && double_buffer && M == MT) { \
 		auto kern = gemv_q8_rows_db<MT>; \
 		e		  = cudaSuccess; \
 		if (smem > 48 * 1024) \

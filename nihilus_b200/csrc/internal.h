@@ -14,8 +14,8 @@
 
 namespace nhb {
 
-	// device status word values (written by kernels whose bounded waits ran out)
-	enum : int { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_DRAIN = 3, DEV_TIMEOUT_MMA = 4, DEV_TIMEOUT_PEER = 5 };
+	// device status word values (written by kernels whose bounded waits ran out, or that met an index outside its table)
+	enum : int { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_DRAIN = 3, DEV_TIMEOUT_MMA = 4, DEV_TIMEOUT_PEER = 5, DEV_BAD_INDEX = 6 };
 
 	// one mul_mat as the streaming GEMV sees it: this context's row shard of the two planes
 	struct stream_op {
@@ -51,6 +51,10 @@ namespace nhb {
 		int act_off;// byte offset of this op's quantised activations in shared memory
 		int preq_off;// byte offset of the same data in the pre-quantised scratch (preq mode)
 		int pad;
+		// the element-wise neighbours of the reference's FFN and attention cores (infra/core_traits.hpp:768-772, 976-992), fused:
+		const float* x2;// not null: the activation is silu(x) * x2 (x = the gate projection's rows, x2 = the up projection's, same ldx)
+		const float* res;// not null: res[m * ldr + n] is added to the output (the residual stream; offset like y)
+		long long ldr;
 	};
 
 	// Fused all-gather of the decode GEMV.  A delivering launch (world > 1) stores its output values straight into all
@@ -135,6 +139,10 @@ namespace nhb {
 	bool rms_norm_supports(long long K);
 	cudaError_t launch_rms_norm(const float* x, long long ldx, const float* w, float eps, int sqrt_mode, int M, int K, const norm_out& o, cudaStream_t s,
 		bool pdl = false);
+
+	// elementwise.cu: h = silu(gate) * up, and y += res on `cols` columns
+	cudaError_t launch_swiglu(const float* gate, const float* up, long long ld, float* h, long long ldh, int M, int K, cudaStream_t s, bool pdl = false);
+	cudaError_t launch_add_rows(float* y, long long ldy, const float* res, long long ldr, int M, int cols, cudaStream_t s, bool pdl = false);
 
 	// repack.cu
 	cudaError_t launch_repack(const uint8_t* blocks34, int64_t rows, int64_t K, int8_t* q, __half* d, cudaStream_t s);

@@ -37,6 +37,16 @@ namespace nhb {
 		return fmaxf(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))), m);
 	}
 
+	// silu(g) * u, the reference's ffn_silu -> ffn_gate_par pair (include/nihilus-incl/infra/core_traits.hpp:982-986; its
+	// kernels for them are empty, the traits name the arithmetic): g / (1 + exp(-g)) in f32 with an IEEE divide, then one
+	// f32 multiply
+	__device__ __forceinline__ float swiglu(float g, float u) {
+		return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+	}
+	__device__ __forceinline__ float4 swiglu4(float4 g, float4 u) {
+		return make_float4(swiglu(g.x, u.x), swiglu(g.y, u.y), swiglu(g.z, u.z), swiglu(g.w, u.w));
+	}
+
 	// One lane of the reference's simd_sum_squares (include/nihilus-incl/cpu/avx_2.hpp:758-779): acc = fma(v, v, acc) over
 	// r[0], r[8], r[16], ... (`steps` values), strictly in that order.  The fmas depend on each other (4 cycles a step
 	// at best), so the only thing to hide is the latency of the shared-memory loads: a 16-entry register window, each

@@ -84,6 +84,11 @@ class Oracle:
         L.orc_unpack_planes.argtypes = [C.POINTER(C.c_int8), C.POINTER(C.c_uint16), C.c_int64, C.c_int64, _c_u8p]
         L.orc_quantize_matrix_q8_0.restype = None
         L.orc_quantize_matrix_q8_0.argtypes = [_c_f32p, C.c_int64, C.c_int64, _c_u8p, C.c_int]
+        for name in ("orc_swiglu", "orc_swiglu_f64", "orc_add"):
+            getattr(L, name).restype = None
+            getattr(L, name).argtypes = [_c_f32p, _c_f32p, _c_f32p, C.c_int64]
+        L.orc_get_rows_q8_0.restype = C.c_int
+        L.orc_get_rows_q8_0.argtypes = [_c_u8p, C.c_int64, C.c_int64, C.POINTER(C.c_int32), C.c_int64, _c_f32p, C.c_int64]
         L.orc_sum_squares.restype = C.c_float
         L.orc_sum_squares.argtypes = [_c_f32p, C.c_int64]
         L.orc_sqrtf_fast.restype = C.c_float
@@ -96,6 +101,33 @@ class Oracle:
     # scalars
     def fp32_to_fp16(self, f: float) -> int:
         return int(self.lib.orc_fp32_to_fp16(f))
+
+    # element-wise neighbours of the mul_mats
+    def swiglu(self, g: np.ndarray, u: np.ndarray, f64: bool = False) -> np.ndarray:
+        g = np.ascontiguousarray(g, dtype=np.float32)
+        u = np.ascontiguousarray(u, dtype=np.float32)
+        h = np.empty_like(g)
+        fn = self.lib.orc_swiglu_f64 if f64 else self.lib.orc_swiglu
+        fn(_ptr(g, _c_f32p), _ptr(u, _c_f32p), _ptr(h, _c_f32p), g.size)
+        return h
+
+    def get_rows(self, table: np.ndarray, ids: np.ndarray) -> np.ndarray:
+        """table: uint8 [N, K/32, 34]; ids: int32 [M] -> f32 [M, K]."""
+        table = np.ascontiguousarray(table, dtype=np.uint8)
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        N, nb, _ = table.shape
+        y = np.zeros((ids.size, nb * QK), dtype=np.float32)
+        rc = self.lib.orc_get_rows_q8_0(_ptr(table, _c_u8p), N, nb * QK, _ptr(ids, C.POINTER(C.c_int32)), ids.size, _ptr(y, _c_f32p), nb * QK)
+        if rc != 0:
+            raise ValueError("orc_get_rows_q8_0: token id outside the table")
+        return y
+
+    def add(self, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        y = np.empty_like(a)
+        self.lib.orc_add(_ptr(a, _c_f32p), _ptr(b, _c_f32p), _ptr(y, _c_f32p), a.size)
+        return y
 
     def fp32_to_fp16_bittrick(self, f: float) -> int:
         return int(self.lib.orc_fp32_to_fp16_bittrick(f))

@@ -641,3 +641,40 @@ int orc_rms_norm_mul_q8_0(const float* x, int64_t ldx, const float* w, float eps
 	free(row);
 	return 0;
 }
+
+/* ---- element-wise neighbours of the mul_mats (infra/core_traits.hpp:771-772, 982-992: trait declarations only) ---- */
+void orc_swiglu(const float* g, const float* u, float* h, int64_t n) {
+	for (int64_t i = 0; i < n; ++i) {
+		const float s = g[i] / (1.0f + expf(-g[i]));
+		h[i]		  = s * u[i];
+	}
+}
+
+void orc_swiglu_f64(const float* g, const float* u, float* h, int64_t n) {
+	for (int64_t i = 0; i < n; ++i)
+		h[i] = (float)(((double)g[i] / (1.0 + exp(-(double)g[i]))) * (double)u[i]);
+}
+
+void orc_add(const float* a, const float* b, float* y, int64_t n) {
+	for (int64_t i = 0; i < n; ++i)
+		y[i] = a[i] + b[i];
+}
+
+/* cuda/cuda_12.hpp:560-601 */
+int orc_get_rows_q8_0(const uint8_t* table_blocks, int64_t N, int64_t K, const int32_t* ids, int64_t M, float* y, int64_t ldy) {
+	const int64_t nb = K / ORC_QK;
+	for (int64_t m = 0; m < M; ++m) {
+		if (ids[m] < 0 || ids[m] >= N)
+			return -1;
+		const uint8_t* row = table_blocks + (int64_t)ids[m] * nb * ORC_BLOCK_BYTES;
+		for (int64_t b = 0; b < nb; ++b) {
+			uint16_t dbits;
+			memcpy(&dbits, row + b * ORC_BLOCK_BYTES, 2);
+			const float scale = orc_fp16_to_fp32(dbits);
+			const int8_t* q	  = (const int8_t*)(row + b * ORC_BLOCK_BYTES + 2);
+			for (int j = 0; j < ORC_QK; ++j)
+				y[m * ldy + b * ORC_QK + j] = scale * (float)q[j];
+		}
+	}
+	return 0;
+}

@@ -75,6 +75,20 @@ float orc_rms_norm_scale(const float* x, int64_t k, float eps, int sqrt_mode);
 int orc_rms_norm_mul(const float* x, int64_t ldx, const float* w, float eps, int sqrt_mode, float* y, int64_t ldy, int64_t M, int64_t K);
 int orc_rms_norm_mul_q8_0(const float* x, int64_t ldx, const float* w, float eps, int sqrt_mode, uint8_t* blocks, int64_t M, int64_t K);
 
+/* The element-wise ops between the mul_mats of the FFN and attention cores.  The reference declares them as traits only
+ * (ffn_silu, ffn_gate_par, residual_add: infra/core_traits.hpp:771-772, 982-992); its kernels for silu and mul are empty
+ * (cpu/avx_2.hpp:1946-2075, 5325-5330), so what is restated here is the arithmetic the trait names fix:
+ *   h = silu(g) * u with silu(g) = g / (1 + exp(-g)), f32 (orc_swiglu), or fp64 throughout, rounded once (orc_swiglu_f64);
+ *   y = a + b in f32. */
+void orc_swiglu(const float* g, const float* u, float* h, int64_t n);
+void orc_swiglu_f64(const float* g, const float* u, float* h, int64_t n);
+void orc_add(const float* a, const float* b, float* y, int64_t n);
+
+/* Token-embedding gather: y[m][k] = fp16_to_fp32(d) * (float)q of row ids[m] of a Q8_0 table, the arithmetic of the
+ * reference's live GPU kernel (cuda/cuda_12.hpp:587-598; the eval-time twin at :691-722 computes the same products but
+ * reads row 0 whatever the token id, :710).  Returns -1 when an id lies outside [0, N). */
+int orc_get_rows_q8_0(const uint8_t* table_blocks, int64_t N, int64_t K, const int32_t* ids, int64_t M, float* y, int64_t ldy);
+
 #ifdef __cplusplus
 }
 #endif

@@ -139,6 +139,57 @@ static int run(char** a, bool with_norm) {
 	return 0;
 }
 
+// ffn tail through the dispatcher: gate.bin up.bin res.bin wdown.bin M y.bin, with a small ffn_down stand-in of 256 rows
+static int run_tail(char** a) {
+	constexpr uint64_t FF = 14336, E = 256;
+	using w_t	 = operand<core_trait_dims<FF, E, 1, 1>, block_q8_0, 2>;
+	using act_t	 = operand<core_trait_dims<FF, 1, 1, 1, 1>, float>;
+	using out_t	 = operand<core_trait_dims<E, 1, 1, 1, 1>, float>;
+	using node_t = mul_mat_node<kernel_traits<kernel_types::mul_mat, out_t, w_t, act_t>>;
+	using core_t = ffn_tail_core<node_t>;
+	static_assert(core_t::core_type == core_types::mega_ffn);
+	const auto gate = slurp(a[0]), up = slurp(a[1]), res = slurp(a[2]), wd = slurp(a[3]);
+	const int64_t M = std::atoll(a[4]);
+	if (gate.size() != size_t(M) * FF * 4 || up.size() != gate.size() || res.size() != size_t(M) * E * 4 || wd.size() != size_t(E) * (FF / 32) * 34)
+		throw std::runtime_error("input sizes do not match the ffn tail stand-in");
+	nhb_ctx* ctx = nullptr;
+	if (nhb_ctx_create(&ctx, 0, 0, 1) != NHB_OK)
+		raise<true>(NHB_ERR_CUDA, "nhb_ctx_create", nullptr);
+	nhb_weight* h = nullptr;
+	if (nhb_weight_upload_q8_0(ctx, wd.data(), E, FF, &h) != NHB_OK)
+		raise<true>(NHB_ERR_CUDA, "nhb_weight_upload_q8_0", ctx);
+	void *gd = nullptr, *ud = nullptr, *rd = nullptr, *yd = nullptr;
+	if (nhb_device_alloc(ctx, gate.size(), &gd) != NHB_OK || nhb_device_alloc(ctx, up.size(), &ud) != NHB_OK || nhb_device_alloc(ctx, res.size(), &rd) != NHB_OK ||
+		nhb_device_alloc(ctx, res.size(), &yd) != NHB_OK)
+		raise<true>(NHB_ERR_NOMEM, "nhb_device_alloc", ctx);
+	nhb_memcpy_h2d(ctx, gd, gate.data(), gate.size());
+	nhb_memcpy_h2d(ctx, ud, up.data(), up.size());
+	nhb_memcpy_h2d(ctx, rd, res.data(), res.size());
+	core_t core{};
+	core.ctx				 = ctx;
+	core.down.weight.data[1] = h;
+	core.down.output.data[0] = yd;
+	core.down.activation.get_seq_length_dim() = static_cast<uint64_t>(M);
+	core.gate.data[0]		 = gd;
+	core.up.data[0]			 = ud;
+	core.residual.data[0]	 = rd;
+	if (M == 1)
+		kernel_dispatcher<gpu_config<true>, processing_phases::eval_time, core_t>::impl(core, 1);
+	else
+		kernel_dispatcher<gpu_config<true>, processing_phases::prompt_eval_time, core_t>::impl(core, 1);
+	std::vector<float> y(size_t(M) * E);
+	nhb_memcpy_d2h(ctx, y.data(), yd, y.size() * 4);
+	if (nhb_sync(ctx) != NHB_OK)
+		raise<true>(NHB_ERR_CUDA, "nhb_sync", ctx);
+	std::ofstream(a[5], std::ios::binary).write(reinterpret_cast<const char*>(y.data()), y.size() * 4);
+	nhb_weight_free(ctx, h);
+	for (void* p: { gd, ud, rd, yd })
+		nhb_device_free(ctx, p);
+	nhb_ctx_destroy(ctx);
+	std::cout << "run ok\n";
+	return 0;
+}
+
 int main(int argc, char** argv) {
 	try {
 		if (argc == 2 && !std::strcmp(argv[1], "check"))
@@ -147,6 +198,8 @@ int main(int argc, char** argv) {
 			return run(argv + 2, false);
 		if (argc == 9 && !std::strcmp(argv[1], "run_norm"))
 			return run(argv + 2, true);
+		if (argc == 8 && !std::strcmp(argv[1], "run_tail"))
+			return run_tail(argv + 2);
 	} catch (const std::exception& e) {
 		std::cerr << "error: " << e.what() << "\n";
 		return 2;

@@ -142,3 +142,25 @@ def test_norm_stage_through_the_cpp_interface_matches_the_oracle(demo, oracle, t
         y = np.fromfile(p[name], dtype=np.float32).reshape(M, N)
         ref = oracle.mul_mat(po.Q8ACT_LANES, w, normed)
         assert float(np.abs(y - ref).max() / np.abs(ref).max()) <= 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 20])
+def test_ffn_tail_through_the_cpp_interface_matches_the_oracle(demo, oracle, tmp_path, M):
+    """silu(gate) * up -> ffn_down -> + residual as one core of type mega_ffn (infra/core_traits.hpp:982-992)."""
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    FF, E = 14336, 256
+    w = synth.make_weight(E, FF, 921)
+    gate = (synth.make_activation(M, FF, 922 + M) * 2).astype(np.float32)
+    up = synth.make_activation(M, FF, 923 + M)
+    res = synth.make_activation(M, E, 924 + M)
+    p = {n: str(tmp_path / n) for n in ("gate", "up", "res", "w", "y")}
+    for name, arr in (("gate", gate), ("up", up), ("res", res), ("w", w)):
+        arr.tofile(p[name])
+    r = subprocess.run([demo, "run_tail", p["gate"], p["up"], p["res"], p["w"], str(M), p["y"]], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    y = np.fromfile(p["y"], dtype=np.float32).reshape(M, E)
+    ref = oracle.add(oracle.mul_mat(po.Q8ACT_LANES, w, oracle.swiglu(gate, up)), res)
+    assert float(np.abs(y - ref).max() / np.abs(ref).max()) <= 3e-4  # exp() of the two sides differs in the last bits (see test_gpu_ffn_fusion.py)
