@@ -384,6 +384,9 @@ def main():
                     help="N > 1 placement policy: weights smaller than this many MiB stay whole on every rank (no exchange); 0 shards all")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
                     help="N > 1: outputs completed by the GEMV's own peer stores (fused) or by a grouped NCCL all-gather per stage")
+    ap.add_argument("--peer-window", type=int, default=4,
+                    help="N > 1, fused gather: a launch waits for the other ranks only if it reads rows they deliver, or to stay within this "
+                         "many delivering launches of the slowest rank; 0 = every launch waits for every earlier delivery")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 512-token GEMM, the rms_norm and the no-alloc figures that ride along in the JSON line")
@@ -419,6 +422,7 @@ def main():
     ctx.capi = capi
     if world > 1:
         ctx.set_option("replicate_below_mb", args.replicate_mb)
+        ctx.set_option("peer_window", args.peer_window)
     stream = torch.cuda.Stream()
     ctx.set_stream(stream.cuda_stream)
     if world > 1:
@@ -550,6 +554,22 @@ def main():
     sampler.stop()
     y_after = y_host.numpy().copy()  # the outputs of the last end-to-end step, as the host received them
 
+    # ---- the same step with every launch waiting for every earlier delivery (what a step costs when each stage reads the
+    #      rows the stage before it gathered); the stages of the timed workload read independent synthetic vectors ----
+    lockstep_ms = None
+    if fused and graph is not None and args.peer_window != 0:
+        ctx.set_option("peer_window", 0)
+        ctx.graph_begin()
+        enqueue_step()
+        g0 = ctx.graph_end()
+        for _ in range(5):
+            g0.launch()
+        ctx.sync()
+        n0 = max(20, args.steps // 4)
+        lockstep_ms = timed(g0.launch, n0) / n0
+        g0.free()
+        ctx.set_option("peer_window", args.peer_window)
+
     total_bytes = sum(shapes.mul_mat_bytes(n, k, 1) for _, _, n, k in ops)
     weight_bytes = sum(n * (k // 32) * 34 for _, _, n, k in ops)
     value = total_bytes / (ms_step * 1e-3) / 1e9
@@ -611,7 +631,8 @@ def main():
             "launch_grouping": "one launch per stage (the independent projections of a stage together), recorded as a stage chain" if chain is not None else "one launch per stage",
             "cuda_graph": graph is not None,
             "parallelism": "row-shard x%d" % world + ("" if world == 1 or not args.replicate_mb else " (weights under %d MiB replicated)" % args.replicate_mb) +
-                           ("" if world == 1 else (" + all-gather fused into the GEMV (peer stores over NVLink, the next launch waits for the peers)" if fused else " + NCCL all-gather per stage")),
+                           ("" if world == 1 else (" + all-gather fused into the GEMV (peer stores over NVLink; a launch waits for the peers when it reads delivered rows, "
+                                                   "the step ends with a wait for every delivery; window %d)" % args.peer_window if fused else " + NCCL all-gather per stage")),
             "l2": "inputs larger than L2 (this rank streams %.2f GB of weights per step vs 126 MB)" % (rank_weight_bytes / 1e9),
         })
         line = {
@@ -632,6 +653,7 @@ def main():
                 "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms,
                 "note": "per GPU: the bytes this rank streams under the placement policy; launch gaps inside the graph are included in the duration",
             },
+            "every_launch_waits_ms_per_step": lockstep_ms,
             "parity": {"all_ranks_hold_the_same_outputs": all_equal, "bit_identical_to_one_gpu": one_gpu_equal},
             "prefill": prefill,
             "rms_norm": norm,

@@ -240,10 +240,14 @@ namespace {
 		if (ctx->world <= 1 || ctx->regions.empty() || !ctx->push_local)
 			return;
 		pc.wait_world  = ctx->world;
+		pc.peers	   = ctx->world;
 		pc.rank		   = ctx->rank;
 		pc.wait_ns	   = static_cast<unsigned long long>(ctx->peer_wait_us) * 1000ull;
 		pc.epoch	   = ctx->push_local + 1;
+		pc.announced   = ctx->push_local + 2;
 		pc.flags_local = reinterpret_cast<unsigned*>(ctx->regions[0].local);
+		for (int r = 0; r < ctx->world; ++r)
+			pc.flags_peer[r] = reinterpret_cast<unsigned*>(ctx->regions[0].peer[r]);
 	}
 
 	bool setup_push(nhb_ctx* ctx, rows_batch& b, const nhb_mul_mat_op* const* src_ops, int mt, int64_t m0) {
@@ -326,6 +330,32 @@ namespace {
 		return off;
 	}
 
+	// The byte ranges a warp-per-row launch reads (activations, the second SwiGLU operand, the residual) and, when it delivers,
+	// the rows it completes on every rank.
+	struct batch_spans {
+		nhb_span in[3 * NHB_MAX_BATCH];
+		nhb_span out[NHB_MAX_BATCH];
+		int n_in = 0, n_out = 0;
+	};
+	void spans_of(const rows_batch& b, const nhb_mul_mat_op* const* src_ops, int mt, int64_t m0, batch_spans& sp) {
+		sp.n_in = sp.n_out = 0;
+		for (int i = 0; i < b.n_ops; ++i) {
+			const rows_op& ro = b.op[i];
+			const size_t xb	  = (static_cast<size_t>(mt - 1) * ro.ldx + ro.K) * sizeof(float);
+			sp.in[sp.n_in++]  = nhb_span{ reinterpret_cast<const char*>(ro.x), reinterpret_cast<const char*>(ro.x) + xb, 0 };
+			if (ro.x2)
+				sp.in[sp.n_in++] = nhb_span{ reinterpret_cast<const char*>(ro.x2), reinterpret_cast<const char*>(ro.x2) + xb, 0 };
+			if (ro.res)
+				sp.in[sp.n_in++] = nhb_span{ reinterpret_cast<const char*>(ro.res),
+					reinterpret_cast<const char*>(ro.res) + (static_cast<size_t>(mt - 1) * ro.ldr + ro.rows) * sizeof(float), 0 };
+			if (b.y_peer[i][0]) {
+				const nhb_mul_mat_op* op = src_ops[i];
+				const char* y0			 = reinterpret_cast<const char*>(op->y + m0 * op->ldy);
+				sp.out[sp.n_out++]		 = nhb_span{ y0, y0 + (static_cast<size_t>(mt - 1) * op->ldy + op->w->N) * sizeof(float), 0 };
+			}
+		}
+	}
+
 	// Which register-fed kernel a launch takes.  A short launch (a q/k/v or attn_output stage: a few rows of one 4 KB item
 	// per warp) is over before a single-buffered warp has hidden one memory latency, so it runs the variant with two
 	// items in flight per warp, at two 8-warp CTAs per SM: everything it needs is then requested before it waits for
@@ -347,21 +377,99 @@ namespace {
 
 }
 
+namespace {
+
+	bool spans_overlap(const nhb_span& a, const nhb_span& b) {
+		return a.b < b.e && b.b < a.e;
+	}
+	bool in_symmetric(const nhb_ctx* ctx, const nhb_span& s) {
+		for (size_t i = 1; i < ctx->regions.size(); ++i) {// regions[0] holds the flags
+			const nhb_span r{ ctx->regions[i].local, ctx->regions[i].local + ctx->regions[i].bytes, 0 };
+			if (spans_overlap(r, s))
+				return true;
+		}
+		return false;
+	}
+	void note_span(std::vector<nhb_span>& v, const nhb_span& s) {
+		for (nhb_span& o: v)
+			if (o.b == s.b && o.e == s.e) {
+				o.seq = std::max(o.seq, s.seq);
+				return;
+			}
+		if (v.size() >= 4096)
+			v.erase(v.begin());// the oldest entry: long confirmed by the window unless nothing has been delivered since
+		v.push_back(s);
+	}
+	void drop_confirmed(std::vector<nhb_span>& v, unsigned long long target) {
+		v.erase(std::remove_if(v.begin(), v.end(), [target](const nhb_span& s) { return s.seq <= target; }), v.end());
+	}
+	// "any symmetric memory": stands for what happened before a capture began
+	const nhb_span ALL_MEMORY{ reinterpret_cast<const char*>(uintptr_t(1)), reinterpret_cast<const char*>(~uintptr_t(0)), 0 };
+
+}
+
 namespace nhb {
+	// A launch waits for the peers only as far as it must:
+	//   - it reads rows a fused launch delivers: until every peer has announced that launch;
+	//   - it delivers into rows an earlier launch of this context read: until every peer has announced the first delivering
+	//     launch enqueued after that reader (the peers' copies of those rows are then no longer being read).  If there is no
+	//     such launch yet, the best it can ask for is the latest one;
+	//   - always: until every peer is within `peer_window` delivering launches of this rank, which bounds how far ranks
+	//     drift apart and with it what readers this library does not know of (other kernels on the stream) may assume.
+	// Everything else proceeds while the exchange is still in flight.  What the wait confirms is forgotten.
+	void plan_peer_wait(nhb_ctx* ctx, push_ctl& pc, const nhb_span* in, int n_in, const nhb_span* out, int n_out, bool delivers) {
+		setup_peer_wait(ctx, pc);
+		pc.wait_lag = 0;
+		if (pc.wait_world <= 1)
+			return;
+		nhb_deliveries& d		= ctx->dl;
+		unsigned long long need = 0;
+		for (int i = 0; i < n_in; ++i) {
+			if (!in_symmetric(ctx, in[i]))
+				continue;
+			for (const nhb_span& p: d.pending)
+				if (spans_overlap(p, in[i]))
+					need = std::max(need, p.seq);
+		}
+		if (delivers)
+			for (int i = 0; i < n_out; ++i)
+				for (const nhb_span& r: d.reads)
+					if (spans_overlap(r, out[i]))
+						need = std::max(need, std::min(r.seq, d.seq));
+		const unsigned long long window = static_cast<unsigned long long>(ctx->peer_window < 0 ? 0 : ctx->peer_window);
+		const unsigned long long target = std::max(need, d.seq > window ? d.seq - window : 0ull);
+		if (target == 0)
+			pc.wait_world = 0;// nothing has been delivered that this launch could depend on
+		else
+			pc.wait_lag = static_cast<int>(d.seq - target);
+		drop_confirmed(d.pending, target);
+		drop_confirmed(d.reads, target);
+		for (int i = 0; i < n_in; ++i)
+			if (in_symmetric(ctx, in[i]))
+				note_span(d.reads, nhb_span{ in[i].b, in[i].e, d.seq + 1 });
+		if (delivers) {
+			++d.seq;
+			for (int i = 0; i < n_out; ++i)
+				note_span(d.pending, nhb_span{ out[i].b, out[i].e, d.seq });
+		}
+	}
+
 	// Rows delivered by a fused launch are whole on this rank only after the other ranks' announcements have arrived.  The
-	// decode GEMV kernels wait for them in their own prologue; in front of anything else that may read such rows this
-	// enqueues a one-warp kernel that does nothing but that (bounded) wait.
+	// decode GEMV kernels wait for what they read in their own prologue; in front of anything else that may read such rows
+	// (other kernels, copies to the host, the end of nhb_sync) this enqueues a one-warp kernel that waits for everything.
 	int wait_pending(nhb_ctx* ctx) {
-		if (!ctx->pending_wait)
+		if (ctx->dl.pending.empty())
 			return NHB_OK;
 		push_ctl pc{};
 		setup_peer_wait(ctx, pc);
+		pc.wait_lag	  = 0;
 		int launches  = 0;
 		cudaError_t e = launch_peer_wait(pc, cfg_of(ctx), &launches);
 		if (e != cudaSuccess)
 			return fail_cuda(ctx, e, "peer-wait launch");
 		ctx->launches += launches;
-		ctx->pending_wait = false;
+		ctx->dl.pending.clear();
+		drop_confirmed(ctx->dl.reads, ctx->dl.seq);
 		return NHB_OK;
 	}
 }
@@ -453,13 +561,13 @@ namespace {
 						for (int i = 0; i < b.n_ops; ++i)
 							if (b.y_peer[i][0])
 								ctx->complete.push_back(src_ops[i]->y);
-					setup_peer_wait(ctx, b.push);
+					batch_spans sp;
+					spans_of(b, src_ops, mt, m0, sp);
+					plan_peer_wait(ctx, b.push, sp.in, sp.n_in, sp.out, sp.n_out, pushed);
 					const bool db = pick_double_buffer(ctx, b, mt, pushed);
 					cudaError_t e = launch_gemv_rows(b, mt, cfg, db && ctx->rows_db < 0 ? 2 : ctx->rows_cps, &launches, db, ctx->rows_cluster, ctx->rows_fat != 0, ctx->rows_split != 0);
 					if (e != cudaSuccess)
 						return fail_cuda(ctx, e, "gemv_q8_rows launch");
-					if (b.push.wait_world > 1)
-						ctx->pending_wait = pushed;// this launch waited for everything before it; its own rows are the next launch's to wait for
 				}
 				ctx->launches += launches;
 				return NHB_OK;
@@ -785,6 +893,8 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 		ctx->rows_cps = value < 1 ? 1 : (value > 8 ? 8 : value);
 	else if (!std::strcmp(name, "prequantize"))
 		ctx->preq = value != 0;
+	else if (!std::strcmp(name, "peer_window"))
+		ctx->peer_window = value < 0 ? 0 : value;
 	else if (!std::strcmp(name, "rows_double_buffer"))
 		ctx->rows_db = value < 0 ? -1 : (value != 0);
 	else if (!std::strcmp(name, "rows_cluster"))
@@ -830,10 +940,10 @@ int nhb_sync(nhb_ctx* ctx) {
 		cudaMemsetAsync(ctx->dev_status, 0, NHB_STATUS_WORDS * sizeof(int), ctx->stream);
 		if (ctx->push_local) {
 			// the exchange starts over: no launch counted, no announcement seen (every rank that saw the timeout does the same)
-			cudaMemsetAsync(ctx->push_local, 0, 2 * sizeof(unsigned), ctx->stream);
+			cudaMemsetAsync(ctx->push_local, 0, 3 * sizeof(unsigned), ctx->stream);
 			cudaMemsetAsync(ctx->regions[0].local, 0, ctx->regions[0].bytes, ctx->stream);
 		}
-		ctx->pending_wait = false;
+		ctx->dl = nhb_deliveries();
 		cudaStreamSynchronize(ctx->stream);
 		if (code == DEV_BAD_INDEX)
 			return fail(ctx, NHB_ERR_ARG, "a token id outside the embedding table reached nhb_get_rows_q8_0; its output row was left untouched");
@@ -1162,12 +1272,12 @@ namespace {
 				const bool pushed = ctx->rows_cluster <= 1 && w->N >= ctx->world && setup_push(ctx, b, src_ops, mt, m0);
 				if (pushed && m0 + mt >= M)
 					c.push_back(y);
-				setup_peer_wait(ctx, b.push);
+				batch_spans sp;
+				spans_of(b, src_ops, mt, m0, sp);
+				plan_peer_wait(ctx, b.push, sp.in, sp.n_in, sp.out, sp.n_out, pushed);
 				cudaError_t e = launch_gemv_rows(b, mt, cfg, ctx->rows_cps, &launches, false, 1, ctx->rows_fat != 0, ctx->rows_split != 0);
 				if (e != cudaSuccess)
 					return fail_cuda(ctx, e, "gemv_q8_rows launch (fused element-wise)");
-				if (b.push.wait_world > 1)
-					ctx->pending_wait = pushed;
 			}
 			ctx->launches += launches;
 			return NHB_OK;
@@ -1430,6 +1540,10 @@ int nhb_chain_create(nhb_ctx* ctx, const nhb_mul_mat_op* ops, const int* ops_per
 			all_ranks_have_rows = all_ranks_have_rows && op[i].w->N >= ctx->world;
 		const bool pushed = b.n_ops > 0 && all_ranks_have_rows && setup_push(ctx, b, src_ops, static_cast<int>(M), 0);
 		setup_peer_wait(ctx, b.push);
+		batch_spans sp;
+		spans_of(b, src_ops, static_cast<int>(M), 0, sp);
+		ch->in.emplace_back(sp.in, sp.in + sp.n_in);
+		ch->out.emplace_back(sp.out, sp.out + sp.n_out);
 		for (int i = 0; i < n; ++i) {
 			ch->written.push_back(op[i].y);
 			if (op[i].w->n1 - op[i].w->n0 == op[i].w->N && ctx->world > 1)
@@ -1466,11 +1580,11 @@ int nhb_chain_launch(nhb_ctx* ctx, nhb_chain* ch) {
 	int launches		 = 0;
 	for (size_t s = 0; s < ch->stages.size(); ++s) {
 		const bool db = pick_double_buffer(ctx, ch->stages[s], ch->M, ch->delivers[s] != 0);
+		plan_peer_wait(ctx, ch->stages[s].push, ch->in[s].data(), static_cast<int>(ch->in[s].size()), ch->out[s].data(), static_cast<int>(ch->out[s].size()),
+			ch->delivers[s] != 0);
 		cudaError_t e = launch_gemv_rows(ch->stages[s], ch->M, cfg, db && ctx->rows_db < 0 ? 2 : ctx->rows_cps, &launches, db, 1, ctx->rows_fat != 0, ctx->rows_split != 0);
 		if (e != cudaSuccess)
 			return fail_cuda(ctx, e, "gemv_q8_rows launch (chain)");
-		if (ch->stages[s].push.wait_world > 1)
-			ctx->pending_wait = ch->delivers[s] != 0;
 	}
 	ctx->launches += launches;
 	return NHB_OK;
@@ -1490,6 +1604,13 @@ int nhb_graph_begin(nhb_ctx* ctx) {
 	device_guard g(ctx->device);
 	NHB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
 	ctx->capturing = true;
+	// A replay may follow anything: the recorded launches must take every earlier delivery for unconfirmed and every
+	// symmetric row for just read, whatever the bookkeeping says at this moment.
+	ctx->cap_seq0 = ctx->dl.seq;
+	if (ctx->world > 1 && ctx->dl.seq > 0) {
+		note_span(ctx->dl.pending, nhb_span{ ALL_MEMORY.b, ALL_MEMORY.e, ctx->dl.seq });
+		note_span(ctx->dl.reads, nhb_span{ ALL_MEMORY.b, ALL_MEMORY.e, ctx->dl.seq });
+	}
 	return NHB_OK;
 }
 
@@ -1510,6 +1631,14 @@ int nhb_graph_end(nhb_ctx* ctx, nhb_graph** out) {
 		delete gr;
 		return fail_cuda(ctx, e, "graph capture");
 	}
+	// what a replay leaves behind, relative to where it starts
+	gr->n_deliver = ctx->dl.seq - ctx->cap_seq0;
+	for (const nhb_span& p: ctx->dl.pending)
+		if (p.seq > ctx->cap_seq0)
+			gr->pending.push_back(nhb_span{ p.b, p.e, p.seq - ctx->cap_seq0 });
+	for (const nhb_span& r: ctx->dl.reads)
+		if (r.seq > ctx->cap_seq0)
+			gr->reads.push_back(nhb_span{ r.b, r.e, r.seq - ctx->cap_seq0 });
 	*out = gr;
 	return NHB_OK;
 }
@@ -1519,6 +1648,12 @@ int nhb_graph_launch(nhb_ctx* ctx, nhb_graph* gr) {
 		return fail(ctx, NHB_ERR_ARG, "nhb_graph_launch: null argument");
 	device_guard g(ctx->device);
 	NHB_CUDA(ctx, cudaGraphLaunch(gr->exec, ctx->stream));
+	const unsigned long long base = ctx->dl.seq;
+	ctx->dl.seq += gr->n_deliver;
+	for (const nhb_span& p: gr->pending)
+		note_span(ctx->dl.pending, nhb_span{ p.b, p.e, base + p.seq });
+	for (const nhb_span& r: gr->reads)
+		note_span(ctx->dl.reads, nhb_span{ r.b, r.e, base + r.seq });
 	return NHB_OK;
 }
 

@@ -8,6 +8,21 @@
 
 typedef struct ncclComm* ncclComm_t;
 
+// Bookkeeping of the fused all-gather's deliveries, in enqueue order on one context.  Every rank enqueues the same
+// sequence of delivering launches, so "delivering launch number n" names the same launch everywhere, and a rank's
+// announcement counter reaching n means its rows of launches 1..n have landed and everything it enqueued before its
+// launch n has run.
+struct nhb_span {
+	const char* b = nullptr;
+	const char* e = nullptr;
+	unsigned long long seq = 0;
+};
+struct nhb_deliveries {
+	unsigned long long seq = 0;// delivering launches enqueued so far
+	std::vector<nhb_span> pending;// rows the peers deliver with launch `seq`: whole here once every peer has announced `seq`
+	std::vector<nhb_span> reads;// symmetric rows read by a launch enqueued before delivering launch `seq`: the peers' copies may be rewritten once they have announced `seq`
+};
+
 struct nhb_ctx {
 	int device		   = 0;
 	int rank		   = 0;
@@ -57,9 +72,11 @@ struct nhb_ctx {
 	void* up_dev[2]		   = { nullptr, nullptr };
 	cudaEvent_t up_done[2] = { nullptr, nullptr };
 	size_t up_cap		   = 0;
-	unsigned* push_local = nullptr;// [0] CTAs done in the running launch, [1] fused launches completed
+	unsigned* push_local = nullptr;// [0] CTAs done in the running launch, [1] delivering launches completed, [2] the count last announced to the peers
 	int fused_gather	 = 1;
-	bool pending_wait	 = false;// a delivering launch was enqueued and no later launch of this context has waited for the peers yet
+	nhb_deliveries dl;
+	unsigned long long cap_seq0 = 0;// dl.seq when the open capture began
+	int peer_window		 = 4;// a launch never runs further ahead of the slowest rank than this many delivering launches
 	long long peer_wait_us = 2000000;// bound of a kernel's wait for the other ranks' announcements
 	int symm_loopback	 = 0;// test aid: "peer" mappings alias this rank's own memory, so no announcement ever arrives
 	unsigned long long err_seq = 0;
@@ -82,12 +99,16 @@ struct nhb_chain {
 	std::vector<const void*> delivered;// outputs the launches complete on every rank
 	std::vector<const void*> written;// every output pointer they write
 	std::vector<char> delivers;// per stage: its rows go to the other ranks
+	std::vector<std::vector<nhb_span>> in, out;// per stage: what it reads, what it completes on every rank
 	int device = 0;
 };
 
 struct nhb_graph {
 	cudaGraph_t graph	 = nullptr;
 	cudaGraphExec_t exec = nullptr;
+	// what one replay adds to the context's delivery bookkeeping (sequence numbers relative to the replay's start)
+	unsigned long long n_deliver = 0;
+	std::vector<nhb_span> pending, reads;
 };
 
 namespace nhb {
@@ -126,5 +147,8 @@ namespace nhb {
 	int ensure(nhb_ctx* ctx, void** buf, size_t* cap, size_t need, const char* what);
 	// in front of work that reads rows another rank may still be delivering: a one-warp kernel that waits for the peers
 	int wait_pending(nhb_ctx* ctx);
+	// Decides what a warp-per-row launch waits for in its prologue and records what it reads and delivers.
+	// in / out: the byte ranges it reads (activations, residual) and, when `delivers`, the rows it completes on every rank.
+	void plan_peer_wait(nhb_ctx* ctx, nhb::push_ctl& pc, const nhb_span* in, int n_in, const nhb_span* out, int n_out, bool delivers);
 
 }

@@ -190,38 +190,48 @@ namespace nhb {
 		return t;
 	}
 
-	// End of a launch that delivered its rows to the other ranks.  Every CTA orders its stores (CTA barrier, then a
-	// device-scope fence by thread 0) and counts itself done; the last one issues the launch's single system-scope
-	// fence -- it waits for the stores that crossed NVLink to be acknowledged -- and tells every rank "this rank has
-	// finished launch number e".  Nobody waits here: the kernel retires, and whoever reads the rows next waits in
-	// push_wait_peers, after its own weight stream is under way.
-	__device__ __forceinline__ void push_announce(const push_ctl& pc, int tid) {
+	// End of a launch that delivered its rows to the other ranks: the CTAs count themselves done and the last one bumps
+	// this rank's count of completed delivering launches.  No fence and no announcement here -- a fence at this point
+	// would have every CTA wait for its NVLink stores to be acknowledged before the kernel may end.  The kernel boundary
+	// orders the stores; the next launch of the context announces them (push_publish).
+	__device__ __forceinline__ void push_done(const push_ctl& pc, int tid) {
 		__syncthreads();
 		if (tid != 0)
 			return;
-		asm volatile("fence.acq_rel.gpu;" ::: "memory");
 		const unsigned prev = atomicAdd(pc.done_ctas, 1u);
-		if (prev != gridDim.x - 1)
+		if (prev != gridDim.x * gridDim.y * gridDim.z - 1)
 			return;
-		asm volatile("fence.acq_rel.sys;" ::: "memory");
-		const unsigned e = *reinterpret_cast<volatile unsigned*>(pc.epoch) + 1u;
-		for (int r = 0; r < pc.world; ++r)
-			st_relaxed_sys(pc.flags_peer[r] + pc.rank, e);
 		*reinterpret_cast<volatile unsigned*>(pc.done_ctas) = 0u;
-		*reinterpret_cast<volatile unsigned*>(pc.epoch)	   = e;
+		*reinterpret_cast<volatile unsigned*>(pc.epoch)	   = *reinterpret_cast<volatile unsigned*>(pc.epoch) + 1u;
 	}
 
-	// Start of every launch of a context that shares outputs with other ranks, after the wait for the previous kernel of
-	// this stream: until every rank has announced as many delivering launches as this rank has completed, rows written
-	// by those launches may still be on their way.  One thread per CTA polls this rank's own flag array (local memory,
-	// written by the peers) for at most wait_ns nanoseconds, then records DEV_TIMEOUT_PEER and carries on, so that the
-	// kernel always ends and the host learns of it from nhb_sync.  A flag only depends on the writing rank's own
-	// earlier kernels, so ranks cannot wait on each other in a cycle.  Called by the `nthreads` threads that go on to read
-	// the activations; ends with their barrier (group_sync).
+	// Start of every launch of a context that shares outputs with other ranks, after the wait for the previous kernels of
+	// this stream (whose stores, the ones that crossed NVLink included, are then complete): one thread tells every rank
+	// "this rank has finished delivering launch number e" if that is news.  The system-scope fence orders those kernels'
+	// stores before the flag stores for every observer.
+	__device__ __forceinline__ void push_publish(const push_ctl& pc, int tid) {
+		if (pc.peers > 1 && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+			const unsigned e = *reinterpret_cast<volatile unsigned*>(pc.epoch);
+			if (*reinterpret_cast<volatile unsigned*>(pc.announced) != e) {
+				asm volatile("fence.acq_rel.sys;" ::: "memory");
+				for (int r = 0; r < pc.peers; ++r)
+					st_relaxed_sys(pc.flags_peer[r] + pc.rank, e);
+				*reinterpret_cast<volatile unsigned*>(pc.announced) = e;
+			}
+		}
+	}
+
+	// Then the launch waits for the peers as far as the host found it must (plan_peer_wait): until every rank has announced
+	// delivering launch number (this rank's completed count - wait_lag).  One thread per CTA polls this rank's own flag
+	// array (local memory, written by the peers) for at most wait_ns nanoseconds, then records DEV_TIMEOUT_PEER and carries
+	// on, so that the kernel always ends and the host learns of it from nhb_sync.  A rank announces before it waits, and an
+	// announcement only depends on that rank's own earlier kernels, so ranks cannot wait on each other in a cycle.  Called
+	// by the `nthreads` threads that go on to read the activations; ends with their barrier (group_sync).
 	__device__ __forceinline__ void push_wait_peers(const push_ctl& pc, int tid, int nthreads = 0, int bar_id = 0) {
+		push_publish(pc, tid);
 		if (pc.wait_world > 1) {
 			if (tid == 0) {
-				const unsigned e = *reinterpret_cast<volatile unsigned*>(pc.epoch);
+				const unsigned e = *reinterpret_cast<volatile unsigned*>(pc.epoch) - static_cast<unsigned>(pc.wait_lag);
 				bool ok			 = true;
 				unsigned long long t0 = 0;
 				for (int r = 0; r < pc.wait_world && ok; ++r) {

@@ -230,7 +230,7 @@ namespace nhb {
 						}
 					}
 				}
-				push_announce(b.push, tid);
+				push_done(b.push, tid);
 			}
 		}
 
@@ -323,7 +323,7 @@ namespace nhb {
 							b.y_peer[ocur][r][off] = v;
 			}
 			if (b.push.world > 1)
-				push_announce(b.push, tid);
+				push_done(b.push, tid);
 		}
 
 		// ---- double-buffered variant: two 4 KB items in flight per warp ----

@@ -58,17 +58,20 @@ namespace nhb {
 	};
 
 	// Fused all-gather of the decode GEMV.  A delivering launch (world > 1) stores its output values straight into all
-	// ranks' copies of the output (peer-mapped memory) and its last CTA announces "this rank has finished launch e" in a
-	// flag array on every rank.  Every launch of such a context (wait_world > 1) first waits, for a bounded time, until all
-	// ranks have announced the launches this rank has completed, so the rows it reads are whole.
+	// ranks' copies of the output (peer-mapped memory) and counts itself completed.  The next launch of the context
+	// (peers > 1) announces that count in a flag array on every rank, and every launch waits, for a bounded time, until the
+	// other ranks have announced as much as the host found this launch depends on (wait_world > 1, wait_lag).
 	struct push_ctl {
 		int world;// > 1: this launch delivers its rows to the other ranks
 		int wait_world;// > 1: wait for the other ranks' announcements before reading activations
 		int rank;
+		int wait_lag;// the wait is for every rank's announcement number (this rank's completed delivering launches - wait_lag)
+		int peers;// > 1: the context exchanges rows: announce this rank's completed delivering launches first
 		int pad;
 		unsigned long long wait_ns;// bound of that wait
 		unsigned* done_ctas;// local: CTAs of this grid that have stored everything
 		unsigned* epoch;// local: number of delivering launches completed on this rank
+		unsigned* announced;// local: the count this rank last announced
 		unsigned* flags_local;// [world], written by the peers: their epoch after their matching launch
 		unsigned* flags_peer[NHB_MAX_WORLD];// the same array on every rank (this rank's own included)
 		int* status;// the context's device status word

@@ -146,7 +146,7 @@ def _worker(rank, world, uid_path, q):
         xc = torch.from_numpy(synth.make_activation(1, 4096, 99)).cuda()
         yc = [ctx.symm_empty((1, n)) for n, _ in dims]
         ch = ctx.chain([[(hc[0], xc, yc[0])], [(hc[1], yc[0], yc[1])], [(hc[2], yc[1], yc[2])]])
-        for _ in range(3):
+        for _ in range(10):  # every round rewrites what the round before read: the launches wait for exactly that
             ch.launch()
         ctx.all_gather(yc[2])
         ctx.sync()

@@ -1,9 +1,9 @@
 """The bounded waits of the fused all-gather, on one GPU and without any fault (needs a B200).
 
 A context that believes it is rank 0 of 2 gets "symmetric" memory whose peer mappings alias its own allocation
-(option symm_loopback), so no other rank ever announces a launch.  The next launch's wait for the peers then runs
-into its time limit, records a status word and carries on: the kernel ends normally, nhb_sync reports
-NHB_ERR_TIMEOUT, and the context keeps working.  Nothing traps, nothing hangs.
+(option symm_loopback), so no other rank ever announces a launch.  Whoever then waits for the peers -- nhb_sync, or a
+launch that reads the rows they were to deliver -- runs into its time limit, records a status word and carries on:
+the kernel ends normally, nhb_sync reports NHB_ERR_TIMEOUT, and the context keeps working.  Nothing traps, nothing hangs.
 """
 import numpy as np
 import pytest
@@ -41,14 +41,27 @@ def test_a_peer_that_never_announces_ends_in_a_timeout_status_not_a_hang(capi, o
     assert np.abs(got[:, : N // 2] - ref[:, : N // 2]).max() <= 1e-4 * np.abs(ref).max()  # this rank's own columns are right
     assert (got[:, N // 2:] == 0).all()  # the peer's were never delivered
     c.sync()  # the status was cleared and the exchange reset: a second sync is clean
-    # a GEMV launch right after a delivering one runs into the same limit in its own prologue and still finishes
-    y2 = c.symm_empty((1, N))
+    # a GEMV launch that reads the rows the peer was to deliver runs into the same limit in its own prologue and still finishes
+    w2 = synth.make_weight(512, N, 13)
+    h2 = c.upload(w2)
+    y2 = c.symm_empty((1, 512))
     c.mul_mat(h, xd, y)
-    c.mul_mat(h, xd, y2)
+    c.mul_mat(h2, y, y2)
     with pytest.raises(capi.NhbError) as e:
         c.sync()
     assert e.value.code == capi.ERR_TIMEOUT
-    assert np.abs(y2.cpu().numpy()[:, : N // 2] - ref[:, : N // 2]).max() <= 1e-4 * np.abs(ref).max()
+    ref2 = oracle.mul_mat(po.Q8ACT_LANES, w2, y.cpu().numpy())
+    assert np.abs(y2.cpu().numpy()[:, :256] - ref2[:, :256]).max() <= 1e-4 * np.abs(ref2).max()
+    # with no window every launch keeps in step with the peers, whatever it reads: the limit is met in its prologue again
+    c.set_option("peer_window", 0)
+    y3 = c.symm_empty((1, N))
+    c.mul_mat(h, xd, y)
+    c.mul_mat(h, xd, y3)
+    with pytest.raises(capi.NhbError) as e:
+        c.sync()
+    assert e.value.code == capi.ERR_TIMEOUT
+    assert np.abs(y3.cpu().numpy()[:, : N // 2] - ref[:, : N // 2]).max() <= 1e-4 * np.abs(ref).max()
+    h2.free()
     # the context is still good for work that needs no peer: a weight kept whole on every rank
     c.set_option("replicate_below_mb", 1000)
     hw = c.upload(w)
