@@ -114,7 +114,8 @@ int nhb_sync(nhb_ctx* ctx);
 int nhb_ctx_set_gemv_max_m(nhb_ctx* ctx, int max_m);
 /* tuning knobs: "pdl" (programmatic dependent launch, default 1), "gemv_kernel" (1, 2 or 4: what AUTO uses for
  * small M), "rows_ctas_per_sm", "prequantize", "ctas_per_sm" (streaming GEMV, 1 or 2), "gemv_max_m", "rows_fat_ctas",
- * "rows_split_long", "fused_gather", and the placement policy "replicate_below_mb": with world > 1, a weight smaller
+ * "rows_split_long", "rows_double_buffer" (-1 chooses per launch), "fused_gather", "peer_window" and "peer_wait_us" (see
+ * nhb_symm_alloc), and the placement policy "replicate_below_mb": with world > 1, a weight smaller
  * than that many MiB is kept whole on every rank (n0 = 0, n1 = N; every rank computes every row, no exchange) instead of
  * row-sharded -- set it before uploading; 0 (default) shards everything */
 int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value);
@@ -260,18 +261,23 @@ int nhb_mul_mat_q8_0_noalloc(const void* q_plane, const void* d_plane, int64_t r
 int64_t nhb_noalloc_max_bytes(void);
 const char* nhb_noalloc_last_error(void);
 
-/* ---- a token's whole sequence of dependent decode stages as ONE persistent kernel ----
+/* ---- a token's whole sequence of decode stages, recorded once ----
  * Stands in for what thread_pool<gpu>::execute_tasks does per token (cuda/thread_pool.hpp:46-67: the input core, the
  * per-block cores of every layer, the output core, one after the other) on the mul_mat side of those cores.
  * `ops` lists the stages back to back, ops_per_stage[s] (1..8) independent mul_mats each (q/k/v; o; gate/up; down; ...
- * lm_head); every op of stage s+1 may read any output of stage s: a stage starts once the one before it has ended on
- * the whole GPU (a device-side grid barrier with bounded waits), while the weight stream of the following stages is
- * already running.  Q8 arithmetic, 1 <= M <= 4 (the same M in every op), K % 256 == 0, K <= 16384
- * (NHB_ERR_UNSUPPORTED otherwise: run such stages with nhb_mul_mat_batch).  Results are bit-identical to
- * nhb_mul_mat_batch stage by stage.  The op list is read at create time; the activations and outputs it names must stay
- * valid for every launch.  One launch runs alone on the GPU (cooperative launch: one CTA per SM).  With world > 1 the rules
- * of nhb_symm_alloc apply per stage: outputs in symmetric memory are delivered to every rank and the next stage waits
- * for all ranks; the outputs of the LAST stage are whole after nhb_all_gather (or nhb_sync). */
+ * lm_head); ops of one stage that read the same activations quantise them once.  Every op of stage s+1 may read any
+ * output of stage s.  nhb_chain_create checks the arguments and builds the launch descriptors once; nhb_chain_launch
+ * enqueues one warp-per-row GEMV launch per stage with programmatic dependent launch between them (a stage's weight
+ * stream starts while the stage before it drains), without per-call argument checks, and can itself be captured with
+ * nhb_graph_begin.  Q8 arithmetic, 1 <= M <= 4 (the same M in every op), K % 32 == 0 and M rows of every distinct input
+ * of a stage within 96 KB of shared memory (NHB_ERR_UNSUPPORTED otherwise: run such stages with nhb_mul_mat_batch).
+ * Results are bit-identical to nhb_mul_mat_batch stage by stage.  The op list is read at create time; the activations
+ * and outputs it names must stay valid for every launch.  With world > 1 the rules of nhb_symm_alloc apply per stage:
+ * outputs in symmetric memory are delivered to every rank, a stage that reads them waits for the ranks that deliver
+ * them, and the outputs of the LAST stage are whole after nhb_all_gather (or nhb_sync).
+ * (A single persistent kernel for the whole sequence, with a device-side barrier between stages, was built and measured
+ * slower than these launches -- the barrier and the per-stage prologue cost more than a launch boundary -- and is not
+ * part of the library.) */
 int nhb_chain_create(nhb_ctx* ctx, const nhb_mul_mat_op* ops, const int* ops_per_stage, int n_stages, nhb_chain** out);
 int nhb_chain_launch(nhb_ctx* ctx, nhb_chain* chain);
 int nhb_chain_free(nhb_ctx* ctx, nhb_chain* chain);
@@ -289,10 +295,34 @@ int nhb_comm_init(nhb_ctx* ctx, const void* id128);
 /* Output memory for the fused all-gather of the decode GEMV.  Collective: every rank calls it after nhb_comm_init, with
  * the same size, in the same order; each rank gets its own allocation and a mapping of every other rank's (CUDA IPC, so
  * one process per GPU and peer access between the GPUs are required).  When every output of a GEMV launch (M <= 8) lies
- * in such memory at the same offset on every rank, the kernel stores each value into all ranks' copies and trades
- * completion flags with the peers before it finishes -- the output row is whole on every rank when the kernel is, and
- * nhb_all_gather on it is a no-op.  All ranks must then issue the same sequence of such launches.  A peer that never
- * shows up ends the bounded wait with NHB_ERR_TIMEOUT from nhb_sync.  Option "fused_gather" = 0 keeps NCCL. */
+ * in such memory at the same offset on every rank, the kernel stores each value into all ranks' copies (plain stores
+ * over NVLink) and counts itself a completed "delivering launch"; nhb_all_gather on such an output enqueues no collective.
+ * All ranks must issue the same sequence of delivering launches.
+ *
+ * When the rows are whole.  Delivery is asynchronous: the NEXT launch of the context (any nhb_mul_mat*, nhb_chain_launch,
+ * nhb_all_gather*, nhb_sync) first announces this rank's completed deliveries to every rank, and a launch waits for the
+ * other ranks' announcements only as far as it must:
+ *   - a GEMV launch that READS delivered rows (activations, SwiGLU operand, residual in symmetric memory) waits in its
+ *     prologue, after its weight stream has started, until every rank has announced the launch that delivers them;
+ *   - every other entry point that may read them (the GEMM path, rms_norm, nhb_get_rows_q8_0, nhb_memcpy_d2h,
+ *     nhb_all_gather*, nhb_sync) waits for everything delivered so far;
+ *   - kernels of the caller's own on the same stream must be preceded by nhb_all_gather* on the outputs they read.
+ * Everything else runs on while the exchange is in flight.
+ *
+ * When a buffer may be written again.  A delivering launch writes into the peers' copies, so the peers must be done
+ * reading the previous contents.  Reads by this library's own GEMV launches are tracked: a delivering launch that
+ * rewrites rows an earlier launch of this context read waits until every rank has announced the first delivering launch
+ * enqueued at or after that reader.  So a reader that delivers rows itself may be followed directly by the launch that
+ * rewrites what it read (a stage sequence that ping-pongs between two buffers); after a reader that delivers nothing, at
+ * least one other delivering launch must come first.  Independently, no launch runs more than "peer_window" (option,
+ * default 4) delivering launches ahead of the slowest rank; rows read by kernels this library does not know of may
+ * therefore be rewritten once peer_window + 1 further delivering launches have been enqueued after that reader, or once
+ * the ranks have met on the host after their nhb_sync.  "peer_window" = 0 makes every launch wait for every earlier
+ * delivery (ranks in lock step).
+ *
+ * Every wait is bounded by option "peer_wait_us" (default 2 000 000): a peer that never shows up ends it, the kernel
+ * carries on and finishes, and nhb_sync returns NHB_ERR_TIMEOUT and resets the exchange (all ranks must then sync
+ * before they continue).  Option "fused_gather" = 0 keeps NCCL. */
 int nhb_symm_alloc(nhb_ctx* ctx, size_t bytes, void** out_dev);
 int nhb_symm_free(nhb_ctx* ctx, void* dev);
 /* complete Y[M][N] (ldy) on every rank from the column slices each rank wrote */
