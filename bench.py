@@ -33,7 +33,7 @@ NOMINAL_HBM_GBS = 8000.0
 DTYPE = "i8xi8->i32, f32 scales"
 # dram__bytes_read.sum + dram__bytes_write.sum of one full step (129 GEMV launches), from an ncu capture of one layer +
 # lm_head scaled to 32 layers (every layer repeats the captured shapes): profiles/gemv_q8_rows_decode_set.md
-NCU_DRAM_BYTES_PER_STEP = 8094.8e6
+NCU_DRAM_BYTES_PER_STEP = 8152.0e6
 
 
 def measured_peaks():
