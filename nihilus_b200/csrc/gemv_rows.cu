@@ -256,33 +256,15 @@ namespace nhb {
 			// this CTA's rows: an even contiguous split of the batch-wide row list
 			const int r_lo	  = static_cast<int>(static_cast<long long>(total_rows) * blockIdx.x / gridDim.x);
 			const int r_hi	  = static_cast<int>(static_cast<long long>(total_rows) * (blockIdx.x + 1) / gridDim.x);
-			const int n_rows  = r_hi - r_lo;
-			const int n_items = n_rows * ipr;
-			// Dealing order: the CTA's full items first (row by row), then the rows' last, shorter items (K = 14336: three
-			// items of 128 blocks and one of 64 per row), round-robin over the warps.  Row-major dealing would hand warp w
-			// item w % 4 of every row, i.e. a quarter of the warps nothing but the short items: 20 KB on the busiest warp
-			// against 18 KB here.  Which warp computes an item never shows in the result.
-			const int nfull	  = (nb % (32 * ITEM)) ? ipr - 1 : ipr;// full items per row
-			const int n_full  = n_rows * nfull;
-			auto item_of = [&](int j, int& rl, int& k) {
-				if (j < n_full) {
-					rl = j / nfull;
-					k  = j - rl * nfull;
-				} else {
-					rl = j - n_full;
-					k  = nfull;
-				}
-			};
+			const int n_items = (r_hi - r_lo) * ipr;
 			item_regs regs;
 			bool pre = false;
 			int cur	 = 0;
 			// ---- weights first: they never depend on the previous kernel ----
 			if (warp < n_items) {
-				int rl, k;
-				item_of(warp, rl, k);
-				const int row = r_lo + rl;
+				const int row = r_lo + warp / ipr;
 				cur			  = rows_find_op(b, row, 0);
-				load_item(regs, make_row(&b.op[cur], row - b.op[cur].row_begin), k * 32 * ITEM, lane);
+				load_item(regs, make_row(&b.op[cur], row - b.op[cur].row_begin), (warp % ipr) * 32 * ITEM, lane);
 				pre = true;
 			}
 			pdl_launch_dependents();
@@ -293,11 +275,10 @@ namespace nhb {
 			else
 				quantize_inputs<MT, false, false, EPI>(b, act_smem, tid, ROWS_TPB_FAT);
 			for (int it = warp; it < n_items; it += WARPS) {
-				int rl, k;
-				item_of(it, rl, k);
-				const int b0  = k * 32 * ITEM;
+				const int rl  = it / ipr;
+				const int b0  = (it - rl * ipr) * 32 * ITEM;
 				const int row = r_lo + rl;
-				cur			  = rows_find_op(b, row, 0);
+				cur			  = rows_find_op(b, row, cur);
 				const rows_op* op = &b.op[cur];
 				const row_desc rd = make_row(op, row - op->row_begin);
 				if (!pre)
@@ -315,7 +296,7 @@ namespace nhb {
 				for (int m = 0; m < MT; ++m) {
 					const float v = warp_sum(acc[m]);
 					if (lane == 0)
-						part[(rl * 8 + k) * MT + m] = v;
+						part[(rl * 8 + (it - rl * ipr)) * MT + m] = v;
 				}
 			}
 			__syncthreads();
