@@ -325,6 +325,19 @@ int nhb_comm_init(nhb_ctx* ctx, const void* id128);
  * before they continue).  Option "fused_gather" = 0 keeps NCCL. */
 int nhb_symm_alloc(nhb_ctx* ctx, size_t bytes, void** out_dev);
 int nhb_symm_free(nhb_ctx* ctx, void* dev);
+/* The same for ONE process that drives several GPUs from one thread, as the reference's host does (one process, one
+ * thread per model: cuda/thread_pool.hpp:46-67): ctxs[i] is rank i of a world of n, all created in this process on
+ * distinct devices with peer access.  nhb_symm_alloc_local allocates `bytes` on every context's device and gives every
+ * context plain pointers to the others' allocations (no IPC handles, no NCCL); out_dev[i] is rank i's buffer.  The fused
+ * all-gather of the decode GEMV then works as described above; enqueue each step's calls for all contexts (rank 0, rank
+ * 1, ...) before blocking on any of them, and block with nhb_sync_all, which first enqueues every context's wait for its
+ * peers and only then synchronises -- nhb_sync on one context alone would wait for announcements the other contexts have
+ * not been asked to make yet.  nhb_all_gather_local completes Y[M][N] on every rank for outputs that were not delivered
+ * by a fused launch (the GEMM path): peer copies of every rank's column slice (nhb_shard_rows) ordered by events across
+ * the contexts' streams; y_dev[i] is rank i's buffer, all with the same ldy.  Free with nhb_symm_free per context. */
+int nhb_symm_alloc_local(nhb_ctx* const* ctxs, int n, size_t bytes, void** out_dev);
+int nhb_all_gather_local(nhb_ctx* const* ctxs, int n, float* const* y_dev, int64_t ldy, int64_t M, int64_t N);
+int nhb_sync_all(nhb_ctx* const* ctxs, int n);
 /* complete Y[M][N] (ldy) on every rank from the column slices each rank wrote */
 int nhb_all_gather(nhb_ctx* ctx, float* y_dev, int64_t ldy, int64_t M, int64_t N);
 /* several outputs in one grouped collective (q/k/v, gate/up) */

@@ -35,7 +35,7 @@ EXPORTS = (
     "nhb_weight_upload_q8_0", "nhb_weight_free", "nhb_weight_info_get", "nhb_weight_download_q8_0", "nhb_mul_mat",
     "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
-    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_place_rows", "nhb_gemm_tile_plan",
+    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_symm_alloc_local", "nhb_all_gather_local", "nhb_sync_all", "nhb_place_rows", "nhb_gemm_tile_plan",
     "nhb_rms_norm_mul", "nhb_rms_norm_mul_q8_0", "nhb_rms_norm_mul_mat_batch",
     "nhb_gguf_open", "nhb_gguf_last_error", "nhb_gguf_close", "nhb_gguf_tensor_count", "nhb_gguf_find", "nhb_gguf_tensor_get",
     "nhb_gguf_get_number", "nhb_gguf_get_string", "nhb_gguf_upload_q8_0", "nhb_gguf_read_f32",
@@ -102,6 +102,9 @@ _sig("nhb_memcpy_d2h", _i, _vp, _vp, _vp, C.c_size_t)
 _sig("nhb_device_alloc", _i, _vp, C.c_size_t, C.POINTER(_vp))
 _sig("nhb_device_free", _i, _vp, _vp)
 _sig("nhb_symm_alloc", _i, _vp, C.c_size_t, C.POINTER(_vp))
+_sig("nhb_symm_alloc_local", _i, C.POINTER(_vp), _i, C.c_size_t, C.POINTER(_vp))
+_sig("nhb_all_gather_local", _i, C.POINTER(_vp), _i, C.POINTER(_vp), _i64, _i64, _i64)
+_sig("nhb_sync_all", _i, C.POINTER(_vp), _i)
 _sig("nhb_symm_free", _i, _vp, _vp)
 _sig("nhb_weight_upload_q8_0", _i, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("nhb_weight_free", _i, _vp, _vp)
@@ -558,3 +561,32 @@ class Context:
         ms = (_i64 * n)(*[y.shape[0] for y in ys])
         ns = (_i64 * n)(*[y.shape[1] for y in ys])
         _check(lib.nhb_all_gather_batch(self.handle, ptrs, ld, ms, ns, n), self.handle)
+
+
+# ---- one process driving several GPUs: ctxs[i] is rank i of a world of len(ctxs) ----
+def _handles(ctxs):
+    return (_vp * len(ctxs))(*[c.handle for c in ctxs])
+
+
+def symm_empty_local(ctxs, shape, dtype=None):
+    """One zeroed torch tensor per context, the same symmetric allocation on every context's device."""
+    import torch
+
+    dtype = dtype or torch.float32
+    n = 1
+    for d in shape:
+        n *= int(d)
+    nbytes = max(n, 1) * torch.empty((), dtype=dtype).element_size()
+    out = (_vp * len(ctxs))()
+    _check(lib.nhb_symm_alloc_local(_handles(ctxs), len(ctxs), nbytes, out), ctxs[0].handle)
+    return [_tensor_from_ptr(out[i], nbytes, c.device, dtype).view(*shape) for i, c in enumerate(ctxs)]
+
+
+def all_gather_local(ctxs, ys):
+    M, N = ys[0].shape
+    ptrs = (_vp * len(ys))(*[y.data_ptr() for y in ys])
+    _check(lib.nhb_all_gather_local(_handles(ctxs), len(ctxs), ptrs, ys[0].stride(0), M, N), ctxs[0].handle)
+
+
+def sync_all(ctxs):
+    _check(lib.nhb_sync_all(_handles(ctxs), len(ctxs)), ctxs[0].handle)

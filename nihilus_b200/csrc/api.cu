@@ -224,7 +224,7 @@ namespace {
 	}
 
 	void symm_release(nhb_ctx* ctx, nhb_ctx::symm_region& reg) {
-		for (int r = 0; r < ctx->world; ++r)
+		for (int r = 0; r < ctx->world && reg.ipc; ++r)
 			if (r != ctx->rank && reg.peer[r] && reg.peer[r] != reg.local)
 				cudaIpcCloseMemHandle(reg.peer[r]);
 		if (reg.local)
@@ -846,6 +846,8 @@ int nhb_ctx_destroy(nhb_ctx* ctx) {
 			cudaFree(ctx->up_dev[i]);
 		if (ctx->up_done[i])
 			cudaEventDestroy(ctx->up_done[i]);
+		if (ctx->group_ev[i])
+			cudaEventDestroy(ctx->group_ev[i]);
 	}
 	if (ctx->push_local)
 		cudaFree(ctx->push_local);
@@ -924,16 +926,19 @@ long long nhb_ctx_launch_count(const nhb_ctx* ctx) {
 	return ctx ? ctx->launches : 0;
 }
 
-int nhb_sync(nhb_ctx* ctx) {
-	if (!ctx)
-		return fail(nullptr, NHB_ERR_ARG, "null context");
-	device_guard g(ctx->device);
+// nhb_sync in two halves, so that one host thread driving several contexts can enqueue every context's wait for its
+// peers before it blocks on any of them
+static int sync_enqueue(nhb_ctx* ctx) {
 	if (!ctx->capturing) {
 		int rc = wait_pending(ctx);// rows other ranks are still delivering belong to "everything enqueued so far"
 		if (rc != NHB_OK)
 			return rc;
 	}
 	NHB_CUDA(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, NHB_STATUS_WORDS * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+	return NHB_OK;
+}
+
+static int sync_finish(nhb_ctx* ctx) {
 	NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
 	if (ctx->host_status[0] != DEV_OK) {
 		const int code = ctx->host_status[0];
@@ -950,6 +955,36 @@ int nhb_sync(nhb_ctx* ctx) {
 		return fail(ctx, NHB_ERR_TIMEOUT, "a device-side wait ran out (code " + std::to_string(code) + "); results of the last launches are invalid");
 	}
 	return NHB_OK;
+}
+
+int nhb_sync(nhb_ctx* ctx) {
+	if (!ctx)
+		return fail(nullptr, NHB_ERR_ARG, "null context");
+	device_guard g(ctx->device);
+	int rc = sync_enqueue(ctx);
+	return rc != NHB_OK ? rc : sync_finish(ctx);
+}
+
+int nhb_sync_all(nhb_ctx* const* ctxs, int n) {
+	if (!ctxs || n < 1)
+		return fail(nullptr, NHB_ERR_ARG, "nhb_sync_all: bad arguments");
+	for (int i = 0; i < n; ++i)
+		if (!ctxs[i])
+			return fail(nullptr, NHB_ERR_ARG, "nhb_sync_all: null context");
+	int first = NHB_OK;
+	for (int i = 0; i < n; ++i) {
+		device_guard g(ctxs[i]->device);
+		const int rc = sync_enqueue(ctxs[i]);
+		if (rc != NHB_OK && first == NHB_OK)
+			first = rc;
+	}
+	for (int i = 0; i < n; ++i) {
+		device_guard g(ctxs[i]->device);
+		const int rc = sync_finish(ctxs[i]);
+		if (rc != NHB_OK && first == NHB_OK)
+			first = rc;
+	}
+	return first;
 }
 
 int nhb_memcpy_h2d(nhb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
@@ -1737,6 +1772,168 @@ int nhb_symm_alloc(nhb_ctx* ctx, size_t bytes, void** out_dev) {
 	return NHB_OK;
 }
 
+// ---- one process driving several GPUs ----
+static int check_group(nhb_ctx* const* ctxs, int n, const char* who) {
+	if (!ctxs || n < 1 || n > NHB_MAX_WORLD)
+		return fail(nullptr, NHB_ERR_ARG, std::string(who) + ": 1 to 8 contexts");
+	for (int i = 0; i < n; ++i) {
+		if (!ctxs[i])
+			return fail(nullptr, NHB_ERR_ARG, std::string(who) + ": null context");
+		if (ctxs[i]->world != n || ctxs[i]->rank != i)
+			return fail(ctxs[i], NHB_ERR_ARG, std::string(who) + ": ctxs[i] must be rank i of a world of n");
+		for (int j = 0; j < i; ++j)
+			if (ctxs[j]->device == ctxs[i]->device)
+				return fail(ctxs[i], NHB_ERR_ARG, std::string(who) + ": two contexts share a device");
+	}
+	return NHB_OK;
+}
+
+// the same allocation on every context's device, each context holding plain pointers to the others' (peer access)
+static int symm_alloc_group(nhb_ctx* const* ctxs, int n, size_t bytes, nhb_ctx::symm_region* regs) {
+	for (int i = 0; i < n; ++i)
+		regs[i] = nhb_ctx::symm_region();
+	cudaError_t e = cudaSuccess;
+	for (int i = 0; i < n && e == cudaSuccess; ++i) {
+		device_guard g(ctxs[i]->device);
+		void* p = nullptr;
+		e		= cudaMalloc(&p, bytes);
+		if (e == cudaSuccess) {
+			regs[i].local = static_cast<char*>(p);
+			regs[i].bytes = bytes;
+			regs[i].ipc	  = false;
+			e			  = cudaMemsetAsync(p, 0, bytes, ctxs[i]->stream);
+		}
+		if (e == cudaSuccess)
+			e = cudaStreamSynchronize(ctxs[i]->stream);
+	}
+	if (e != cudaSuccess) {
+		for (int i = 0; i < n; ++i)
+			if (regs[i].local) {
+				device_guard g(ctxs[i]->device);
+				cudaFree(regs[i].local);
+			}
+		return fail_cuda(ctxs[0], e, "nhb_symm_alloc_local");
+	}
+	for (int i = 0; i < n; ++i)
+		for (int r = 0; r < n; ++r)
+			regs[i].peer[r] = regs[r].local;
+	return NHB_OK;
+}
+
+int nhb_symm_alloc_local(nhb_ctx* const* ctxs, int n, size_t bytes, void** out_dev) {
+	int rc = check_group(ctxs, n, "nhb_symm_alloc_local");
+	if (rc != NHB_OK)
+		return rc;
+	if (!out_dev || bytes == 0)
+		return fail(ctxs[0], NHB_ERR_ARG, "nhb_symm_alloc_local: bad arguments");
+	for (int i = 0; i < n; ++i) {
+		out_dev[i] = nullptr;
+		if (ctxs[i]->capturing)
+			return fail(ctxs[i], NHB_ERR_UNSUPPORTED, "allocation during graph capture");
+		if (ctxs[i]->regions.empty() != ctxs[0]->regions.empty())
+			return fail(ctxs[i], NHB_ERR_ARG, "nhb_symm_alloc_local: the contexts must have made the same symmetric allocations so far");
+	}
+	// every device must be able to store into every other
+	for (int i = 0; i < n; ++i) {
+		device_guard g(ctxs[i]->device);
+		for (int j = 0; j < n; ++j) {
+			if (j == i)
+				continue;
+			int can = 0;
+			cudaError_t e = cudaDeviceCanAccessPeer(&can, ctxs[i]->device, ctxs[j]->device);
+			if (e != cudaSuccess || !can)
+				return fail(ctxs[i], NHB_ERR_UNSUPPORTED, "nhb_symm_alloc_local: no peer access between the contexts' devices");
+			e = cudaDeviceEnablePeerAccess(ctxs[j]->device, 0);
+			if (e == cudaErrorPeerAccessAlreadyEnabled)
+				cudaGetLastError();
+			else if (e != cudaSuccess)
+				return fail_cuda(ctxs[i], e, "cudaDeviceEnablePeerAccess");
+		}
+	}
+	nhb_ctx::symm_region regs[NHB_MAX_WORLD];
+	if (ctxs[0]->regions.empty()) {
+		// first use: the flag array every rank writes into (region 0) and each rank's counters
+		rc = symm_alloc_group(ctxs, n, 256, regs);
+		if (rc != NHB_OK)
+			return rc;
+		for (int i = 0; i < n; ++i) {
+			device_guard g(ctxs[i]->device);
+			cudaError_t e = cudaMalloc(&ctxs[i]->push_local, 256);
+			if (e == cudaSuccess)
+				e = cudaMemset(ctxs[i]->push_local, 0, 256);
+			if (e != cudaSuccess)
+				return fail_cuda(ctxs[i], e, "nhb_symm_alloc_local: control block");
+			ctxs[i]->regions.reserve(64);
+			ctxs[i]->regions.push_back(regs[i]);
+		}
+	}
+	rc = symm_alloc_group(ctxs, n, (bytes + 255) & ~size_t(255), regs);
+	if (rc != NHB_OK)
+		return rc;
+	for (int i = 0; i < n; ++i) {
+		ctxs[i]->regions.push_back(regs[i]);
+		out_dev[i] = regs[i].local;
+	}
+	return NHB_OK;
+}
+
+int nhb_all_gather_local(nhb_ctx* const* ctxs, int n, float* const* y_dev, int64_t ldy, int64_t M, int64_t N) {
+	int rc = check_group(ctxs, n, "nhb_all_gather_local");
+	if (rc != NHB_OK)
+		return rc;
+	if (!y_dev || M < 0 || N < 0 || ldy < N)
+		return fail(ctxs[0], NHB_ERR_ARG, "nhb_all_gather_local: bad arguments");
+	if (n == 1 || M == 0 || N == 0)
+		return NHB_OK;
+	bool all_complete = true;
+	for (int i = 0; i < n; ++i) {
+		if (!y_dev[i])
+			return fail(ctxs[i], NHB_ERR_ARG, "nhb_all_gather_local: null output");
+		const auto& c = ctxs[i]->complete;
+		all_complete  = all_complete && std::find(c.begin(), c.end(), static_cast<const void*>(y_dev[i])) != c.end();
+	}
+	if (all_complete) {
+		// delivered by fused launches: whole once every rank's announcements are in
+		for (int i = 0; i < n; ++i) {
+			device_guard g(ctxs[i]->device);
+			rc = wait_pending(ctxs[i]);
+			if (rc != NHB_OK)
+				return rc;
+		}
+		return NHB_OK;
+	}
+	// Peer copies of every rank's column slice into every other rank's buffer, on the owning rank's stream.  Two rounds of
+	// events order them: no copy starts before every rank has finished what it had enqueued (its buffer may still be read),
+	// and no rank goes on before every copy into its buffer has landed.
+	for (int i = 0; i < n; ++i) {
+		device_guard g(ctxs[i]->device);
+		for (int k = 0; k < 2; ++k)
+			if (!ctxs[i]->group_ev[k])
+				NHB_CUDA(ctxs[i], cudaEventCreateWithFlags(&ctxs[i]->group_ev[k], cudaEventDisableTiming));
+		NHB_CUDA(ctxs[i], cudaEventRecord(ctxs[i]->group_ev[0], ctxs[i]->stream));
+	}
+	for (int i = 0; i < n; ++i) {
+		device_guard g(ctxs[i]->device);
+		for (int j = 0; j < n; ++j)
+			if (j != i)
+				NHB_CUDA(ctxs[i], cudaStreamWaitEvent(ctxs[i]->stream, ctxs[j]->group_ev[0], 0));
+		int64_t a, b;
+		nhb_shard_rows(N, n, i, &a, &b);
+		for (int j = 0; j < n && b > a; ++j)
+			if (j != i)
+				NHB_CUDA(ctxs[i], cudaMemcpy2DAsync(y_dev[j] + a, static_cast<size_t>(ldy) * sizeof(float), y_dev[i] + a, static_cast<size_t>(ldy) * sizeof(float),
+										static_cast<size_t>(b - a) * sizeof(float), static_cast<size_t>(M), cudaMemcpyDeviceToDevice, ctxs[i]->stream));
+		NHB_CUDA(ctxs[i], cudaEventRecord(ctxs[i]->group_ev[1], ctxs[i]->stream));
+	}
+	for (int i = 0; i < n; ++i) {
+		device_guard g(ctxs[i]->device);
+		for (int j = 0; j < n; ++j)
+			if (j != i)
+				NHB_CUDA(ctxs[i], cudaStreamWaitEvent(ctxs[i]->stream, ctxs[j]->group_ev[1], 0));
+	}
+	return NHB_OK;
+}
+
 int nhb_symm_free(nhb_ctx* ctx, void* dev) {
 	if (!ctx)
 		return fail(nullptr, NHB_ERR_ARG, "null context");
@@ -1759,8 +1956,6 @@ int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, 
 		return fail(ctx, NHB_ERR_ARG, "nhb_all_gather_batch: bad arguments");
 	if (ctx->world == 1 || n == 0)
 		return NHB_OK;
-	if (!ctx->comm)
-		return fail(ctx, NHB_ERR_NCCL, "nhb_comm_init has not been called");
 	device_guard g(ctx->device);
 	// outputs a fused GEMV launch has already completed on every rank need no collective
 	auto is_complete = [&](const void* y) { return std::find(ctx->complete.begin(), ctx->complete.end(), y) != ctx->complete.end(); };
@@ -1778,6 +1973,8 @@ int nhb_all_gather_batch(nhb_ctx* ctx, float* const* y_dev, const int64_t* ldy, 
 	}
 	if (!any_left)
 		return NHB_OK;
+	if (!ctx->comm)
+		return fail(ctx, NHB_ERR_NCCL, "nhb_comm_init has not been called (contexts of one process complete their rows with nhb_all_gather_local)");
 	nccl_api& nc = nccl();
 	int rc		 = nc.GroupStart();
 	for (int i = 0; i < n && rc == nccl_success; ++i) {

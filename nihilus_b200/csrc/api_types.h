@@ -61,6 +61,7 @@ struct nhb_ctx {
 		char* local	 = nullptr;
 		size_t bytes = 0;
 		char* peer[NHB_MAX_WORLD] = {};// this rank's own entry is `local`
+		bool ipc = true;// the other ranks' entries are CUDA IPC mappings (to be closed); false: plain pointers of this process
 	};
 	// outputs whose rows are already whole on every rank (delivered by a fused launch, or computed from a replicated
 	// weight): nhb_all_gather has nothing to do for them.  Keyed by the output pointer the caller passes.
@@ -80,6 +81,7 @@ struct nhb_ctx {
 	long long peer_wait_us = 2000000;// bound of a kernel's wait for the other ranks' announcements
 	int symm_loopback	 = 0;// test aid: "peer" mappings alias this rank's own memory, so no announcement ever arrives
 	unsigned long long err_seq = 0;
+	cudaEvent_t group_ev[2] = { nullptr, nullptr };// cross-stream ordering of nhb_all_gather_local
 };
 
 struct nhb_weight {
