@@ -387,6 +387,8 @@ def main():
     ap.add_argument("--peer-window", type=int, default=4,
                     help="N > 1, fused gather: a launch waits for the other ranks only if it reads rows they deliver, or to stay within this "
                          "many delivering launches of the slowest rank; 0 = every launch waits for every earlier delivery")
+    ap.add_argument("--stage-times", action="store_true",
+                    help="also time each stage type on its own (graphs of one launch per layer) and add `stage_us` to the JSON line")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 512-token GEMM, the rms_norm and the no-alloc figures that ride along in the JSON line")
@@ -570,6 +572,37 @@ def main():
         g0.free()
         ctx.set_option("peer_window", args.peer_window)
 
+    # ---- each stage type on its own: one launch per layer, recorded and replayed like the step ----
+    stage_us = None
+    if args.stage_times and act_mode == capi.ACT_Q8 and args.gather != "nccl":
+        stage_us = {}
+        per_layer = len(shapes.LAYER_STAGES)
+        peak_gbs = measured_peaks()[0]
+        for t, label in enumerate("+".join(n.replace("attn_", "").replace("ffn_", "") for n in st) for st in shapes.LAYER_STAGES):
+            idx = [per_layer * layer + t for layer in range(args.layers)]
+            ch = ctx.chain([[(weights[j], xs[s], ys[j]) for j in stages[s]] for s in idx])
+
+            def enqueue_stage(ch=ch, last=stages[idx[-1]]):
+                ch.launch()
+                if fused:
+                    ctx.all_gather_batch([ys[j] for j in last])
+
+            enqueue_stage()
+            ctx.sync()
+            ctx.graph_begin()
+            enqueue_stage()
+            g = ctx.graph_end()
+            for _ in range(5):
+                g.launch()
+            ctx.sync()
+            reps = 50
+            us = timed(g.launch, reps) / reps * 1e3 / len(idx)
+            g.free()
+            ch.free()
+            nb = sum(weights[j].bytes_q8 + 4 * ops[j][3] + 4 * (weights[j].n1 - weights[j].n0) for j in stages[idx[0]])
+            stage_us[label] = {"us_per_launch": us, "rank_mb": nb / 1e6, "bytes_over_peak_us": nb / peak_gbs / 1e3,
+                               "delivers": bool(fused and any(weights[j].n1 - weights[j].n0 < ops[j][2] for j in stages[idx[0]]))}
+
     total_bytes = sum(shapes.mul_mat_bytes(n, k, 1) for _, _, n, k in ops)
     weight_bytes = sum(n * (k // 32) * 34 for _, _, n, k in ops)
     value = total_bytes / (ms_step * 1e-3) / 1e9
@@ -654,6 +687,7 @@ def main():
                 "note": "per GPU: the bytes this rank streams under the placement policy; launch gaps inside the graph are included in the duration",
             },
             "every_launch_waits_ms_per_step": lockstep_ms,
+            "stage_us": stage_us,
             "parity": {"all_ranks_hold_the_same_outputs": all_equal, "bit_identical_to_one_gpu": one_gpu_equal},
             "prefill": prefill,
             "rms_norm": norm,

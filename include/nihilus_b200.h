@@ -314,11 +314,11 @@ int nhb_comm_init(nhb_ctx* ctx, const void* id128);
  * rewrites rows an earlier launch of this context read waits until every rank has announced the first delivering launch
  * enqueued at or after that reader.  So a reader that delivers rows itself may be followed directly by the launch that
  * rewrites what it read (a stage sequence that ping-pongs between two buffers); after a reader that delivers nothing, at
- * least one other delivering launch must come first.  Independently, no launch runs more than "peer_window" (option,
- * default 4) delivering launches ahead of the slowest rank; rows read by kernels this library does not know of may
- * therefore be rewritten once peer_window + 1 further delivering launches have been enqueued after that reader, or once
- * the ranks have met on the host after their nhb_sync.  "peer_window" = 0 makes every launch wait for every earlier
- * delivery (ranks in lock step).
+ * least one other delivering launch must come first.  Independently, every second delivering launch checks that the
+ * slowest rank is within "peer_window" (option, default 4) delivering launches, so no launch runs more than
+ * peer_window + 1 ahead; rows read by kernels this library does not know of may therefore be rewritten once
+ * peer_window + 2 further delivering launches have been enqueued after that reader, or once the ranks have met on the
+ * host after their nhb_sync.  "peer_window" = 0 makes every launch wait for every earlier delivery (ranks in lock step).
  *
  * Every wait is bounded by option "peer_wait_us" (default 2 000 000): a peer that never shows up ends it, the kernel
  * carries on and finishes, and nhb_sync returns NHB_ERR_TIMEOUT and resets the exchange (all ranks must then sync

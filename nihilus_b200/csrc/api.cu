@@ -414,8 +414,9 @@ namespace nhb {
 	//   - it delivers into rows an earlier launch of this context read: until every peer has announced the first delivering
 	//     launch enqueued after that reader (the peers' copies of those rows are then no longer being read).  If there is no
 	//     such launch yet, the best it can ask for is the latest one;
-	//   - always: until every peer is within `peer_window` delivering launches of this rank, which bounds how far ranks
-	//     drift apart and with it what readers this library does not know of (other kernels on the stream) may assume.
+	//   - every second delivering launch: until every peer is within `peer_window` delivering launches of this rank, which
+	//     bounds how far ranks drift apart (peer_window + 1) and with it what readers this library does not know of (other
+	//     kernels on the stream) may assume.
 	// Everything else proceeds while the exchange is still in flight.  What the wait confirms is forgotten.
 	void plan_peer_wait(nhb_ctx* ctx, push_ctl& pc, const nhb_span* in, int n_in, const nhb_span* out, int n_out, bool delivers) {
 		setup_peer_wait(ctx, pc);
@@ -436,8 +437,11 @@ namespace nhb {
 				for (const nhb_span& r: d.reads)
 					if (spans_overlap(r, out[i]))
 						need = std::max(need, std::min(r.seq, d.seq));
+		// the window is checked by every second delivering launch (by all of them when it is 0: lock step); launches that
+		// deliver nothing cannot run away from the peers on their own
 		const unsigned long long window = static_cast<unsigned long long>(ctx->peer_window < 0 ? 0 : ctx->peer_window);
-		const unsigned long long target = std::max(need, d.seq > window ? d.seq - window : 0ull);
+		const bool check_window			= window == 0 || (delivers && (d.seq & 1) == 0);
+		const unsigned long long target = std::max(need, check_window && d.seq > window ? d.seq - window : 0ull);
 		if (target == 0)
 			pc.wait_world = 0;// nothing has been delivered that this launch could depend on
 		else

@@ -1,4 +1,4 @@
-// Device code shared by the decode GEMV kernels (gemv_rows.cu, gemv_chain.cu): the activation prologue that every CTA
+// Device code shared by the decode GEMV kernels (gemv_rows.cu): the activation prologue that every CTA
 // runs (quantize_row_q8_0 of the reference, include/nihilus-incl/cpu/avx_2.hpp:4439-4489, optionally behind the
 // rms_norm x norm-weight producer) and the two halves of the fused all-gather: announcing a finished launch to
 // the other ranks, and waiting for theirs before activations are read.
@@ -230,21 +230,19 @@ namespace nhb {
 	__device__ __forceinline__ void push_wait_peers(const push_ctl& pc, int tid, int nthreads = 0, int bar_id = 0) {
 		push_publish(pc, tid);
 		if (pc.wait_world > 1) {
-			if (tid == 0) {
+			if (tid < 32) {
+				// lane r watches rank r's flag: one round trip to L2 for all peers together when the flags are already there
 				const unsigned e = *reinterpret_cast<volatile unsigned*>(pc.epoch) - static_cast<unsigned>(pc.wait_lag);
 				bool ok			 = true;
-				unsigned long long t0 = 0;
-				for (int r = 0; r < pc.wait_world && ok; ++r) {
-					if (r == pc.rank)
-						continue;
-					for (unsigned i = 0;; ++i) {
-						if (static_cast<int>(ld_relaxed_sys(pc.flags_local + r) - e) >= 0) {
-							ok = static_cast<int>(ld_acquire_sys(pc.flags_local + r) - e) >= 0;
-							break;
-						}
-						if (i == 64)
-							t0 = t0 ? t0 : global_timer_ns();
-						if (i > 64) {
+				if (tid < pc.wait_world && tid != pc.rank) {
+					const unsigned* flag = pc.flags_local + tid;
+					if (static_cast<int>(ld_acquire_sys(flag) - e) < 0) {
+						const unsigned long long t0 = global_timer_ns();
+						for (;;) {
+							if (static_cast<int>(ld_relaxed_sys(flag) - e) >= 0) {
+								ok = static_cast<int>(ld_acquire_sys(flag) - e) >= 0;
+								break;
+							}
 							__nanosleep(20);
 							if (global_timer_ns() - t0 > pc.wait_ns) {
 								ok = false;
@@ -253,7 +251,7 @@ namespace nhb {
 						}
 					}
 				}
-				if (!ok)
+				if (!__all_sync(0xffffffffu, ok) && tid == 0)
 					atomicExch(pc.status, DEV_TIMEOUT_PEER);
 			}
 			group_sync(bar_id, nthreads);
