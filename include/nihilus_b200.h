@@ -310,11 +310,13 @@ int nhb_comm_init(nhb_ctx* ctx, const void* id128);
  * Everything else runs on while the exchange is in flight.
  *
  * When a buffer may be written again.  A delivering launch writes into the peers' copies, so the peers must be done
- * reading the previous contents.  Reads by this library's own GEMV launches are tracked: a delivering launch that
- * rewrites rows an earlier launch of this context read waits until every rank has announced the first delivering launch
- * enqueued at or after that reader.  So a reader that delivers rows itself may be followed directly by the launch that
- * rewrites what it read (a stage sequence that ping-pongs between two buffers); after a reader that delivers nothing, at
- * least one other delivering launch must come first.  Independently, every second delivering launch checks that the
+ * with the previous contents.  What this library's own GEMV launches read and write is tracked: a delivering launch that
+ * rewrites rows an earlier launch of this context read (or wrote without delivering them: a weight kept whole on every
+ * rank) waits until every rank has announced the first delivering launch enqueued at or after that launch, and any
+ * launch that writes rows still being delivered waits for that delivery.  So a reader that delivers rows itself may be
+ * followed directly by the launch that rewrites what it read (a stage sequence that ping-pongs between two buffers);
+ * after a launch that delivers nothing, at least one other delivering launch must come before its rows are delivered
+ * into.  Independently, every second delivering launch checks that the
  * slowest rank is within "peer_window" (option, default 4) delivering launches, so no launch runs more than
  * peer_window + 1 ahead; rows read by kernels this library does not know of may therefore be rewritten once
  * peer_window + 2 further delivering launches have been enqueued after that reader, or once the ranks have met on the
@@ -338,6 +340,20 @@ int nhb_symm_free(nhb_ctx* ctx, void* dev);
 int nhb_symm_alloc_local(nhb_ctx* const* ctxs, int n, size_t bytes, void** out_dev);
 int nhb_all_gather_local(nhb_ctx* const* ctxs, int n, float* const* y_dev, int64_t ldy, int64_t M, int64_t N);
 int nhb_sync_all(nhb_ctx* const* ctxs, int n);
+/* The decisions behind "a launch waits only as far as it must", on their own and without a GPU: feed the planner the
+ * symmetric allocations and then, in enqueue order, what every warp-per-row launch reads and (if it delivers) completes
+ * on every rank; it answers whether that launch polls the peers' announcements and with which lag (it waits until every
+ * peer has announced this rank's completed delivering launches minus lag).  nhb_wait_planner_wait_all stands for nhb_sync /
+ * nhb_all_gather* (returns 1 if a wait was needed).  The library runs the same code; tests replay programs against a
+ * model of ranks that drift apart (tests/test_wait_planner.py). */
+typedef struct nhb_wait_planner nhb_wait_planner;
+nhb_wait_planner* nhb_wait_planner_create(int peer_window);
+void nhb_wait_planner_destroy(nhb_wait_planner* p);
+int nhb_wait_planner_add_region(nhb_wait_planner* p, const void* base, size_t bytes);
+int nhb_wait_planner_launch(nhb_wait_planner* p, const void* const* in, const size_t* in_bytes, int n_in, const void* const* out, const size_t* out_bytes,
+	int n_out, int delivers, int* waits, int* lag);
+int nhb_wait_planner_wait_all(nhb_wait_planner* p);
+long long nhb_wait_planner_seq(const nhb_wait_planner* p);
 /* complete Y[M][N] (ldy) on every rank from the column slices each rank wrote */
 int nhb_all_gather(nhb_ctx* ctx, float* y_dev, int64_t ldy, int64_t M, int64_t N);
 /* several outputs in one grouped collective (q/k/v, gate/up) */

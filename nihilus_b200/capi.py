@@ -35,7 +35,8 @@ EXPORTS = (
     "nhb_weight_upload_q8_0", "nhb_weight_free", "nhb_weight_info_get", "nhb_weight_download_q8_0", "nhb_mul_mat",
     "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
-    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_symm_alloc_local", "nhb_all_gather_local", "nhb_sync_all", "nhb_place_rows", "nhb_gemm_tile_plan",
+    "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_symm_alloc_local", "nhb_all_gather_local", "nhb_sync_all", "nhb_wait_planner_create", "nhb_wait_planner_destroy", "nhb_wait_planner_add_region",
+    "nhb_wait_planner_launch", "nhb_wait_planner_wait_all", "nhb_wait_planner_seq", "nhb_place_rows", "nhb_gemm_tile_plan",
     "nhb_rms_norm_mul", "nhb_rms_norm_mul_q8_0", "nhb_rms_norm_mul_mat_batch",
     "nhb_gguf_open", "nhb_gguf_last_error", "nhb_gguf_close", "nhb_gguf_tensor_count", "nhb_gguf_find", "nhb_gguf_tensor_get",
     "nhb_gguf_get_number", "nhb_gguf_get_string", "nhb_gguf_upload_q8_0", "nhb_gguf_read_f32",
@@ -105,6 +106,12 @@ _sig("nhb_symm_alloc", _i, _vp, C.c_size_t, C.POINTER(_vp))
 _sig("nhb_symm_alloc_local", _i, C.POINTER(_vp), _i, C.c_size_t, C.POINTER(_vp))
 _sig("nhb_all_gather_local", _i, C.POINTER(_vp), _i, C.POINTER(_vp), _i64, _i64, _i64)
 _sig("nhb_sync_all", _i, C.POINTER(_vp), _i)
+_sig("nhb_wait_planner_create", _vp, _i)
+_sig("nhb_wait_planner_destroy", None, _vp)
+_sig("nhb_wait_planner_add_region", _i, _vp, _vp, C.c_size_t)
+_sig("nhb_wait_planner_launch", _i, _vp, C.POINTER(_vp), C.POINTER(C.c_size_t), _i, C.POINTER(_vp), C.POINTER(C.c_size_t), _i, _i, C.POINTER(_i), C.POINTER(_i))
+_sig("nhb_wait_planner_wait_all", _i, _vp)
+_sig("nhb_wait_planner_seq", C.c_longlong, _vp)
 _sig("nhb_symm_free", _i, _vp, _vp)
 _sig("nhb_weight_upload_q8_0", _i, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("nhb_weight_free", _i, _vp, _vp)
@@ -590,3 +597,35 @@ def all_gather_local(ctxs, ys):
 
 def sync_all(ctxs):
     _check(lib.nhb_sync_all(_handles(ctxs), len(ctxs)), ctxs[0].handle)
+
+
+class WaitPlanner:
+    """The wait decisions of the fused all-gather without a GPU (nhb_wait_planner_*): buffers are (address, bytes) pairs."""
+
+    def __init__(self, peer_window: int = 4):
+        self.handle = lib.nhb_wait_planner_create(peer_window)
+
+    def add_region(self, base: int, nbytes: int):
+        _check(lib.nhb_wait_planner_add_region(self.handle, base, nbytes))
+
+    def launch(self, reads, writes, delivers: bool):
+        """reads / writes: lists of (address, bytes).  Returns (waits, lag)."""
+        ri = (_vp * max(len(reads), 1))(*[a for a, _ in reads])
+        rb = (C.c_size_t * max(len(reads), 1))(*[b for _, b in reads])
+        wi = (_vp * max(len(writes), 1))(*[a for a, _ in writes])
+        wb = (C.c_size_t * max(len(writes), 1))(*[b for _, b in writes])
+        waits, lag = _i(), _i()
+        _check(lib.nhb_wait_planner_launch(self.handle, ri, rb, len(reads), wi, wb, len(writes), int(delivers), C.byref(waits), C.byref(lag)))
+        return bool(waits.value), lag.value
+
+    def wait_all(self) -> bool:
+        return bool(lib.nhb_wait_planner_wait_all(self.handle))
+
+    @property
+    def seq(self) -> int:
+        return int(lib.nhb_wait_planner_seq(self.handle))
+
+    def close(self):
+        if self.handle:
+            lib.nhb_wait_planner_destroy(self.handle)
+            self.handle = None

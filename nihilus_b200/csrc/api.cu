@@ -330,8 +330,8 @@ namespace {
 		return off;
 	}
 
-	// The byte ranges a warp-per-row launch reads (activations, the second SwiGLU operand, the residual) and, when it delivers,
-	// the rows it completes on every rank.
+	// The byte ranges a warp-per-row launch reads (activations, the second SwiGLU operand, the residual) and the rows it
+	// writes (whole rows: in a delivering launch they are completed on every rank).
 	struct batch_spans {
 		nhb_span in[3 * NHB_MAX_BATCH];
 		nhb_span out[NHB_MAX_BATCH];
@@ -348,11 +348,9 @@ namespace {
 			if (ro.res)
 				sp.in[sp.n_in++] = nhb_span{ reinterpret_cast<const char*>(ro.res),
 					reinterpret_cast<const char*>(ro.res) + (static_cast<size_t>(mt - 1) * ro.ldr + ro.rows) * sizeof(float), 0 };
-			if (b.y_peer[i][0]) {
-				const nhb_mul_mat_op* op = src_ops[i];
-				const char* y0			 = reinterpret_cast<const char*>(op->y + m0 * op->ldy);
-				sp.out[sp.n_out++]		 = nhb_span{ y0, y0 + (static_cast<size_t>(mt - 1) * op->ldy + op->w->N) * sizeof(float), 0 };
-			}
+			const nhb_mul_mat_op* op = src_ops[i];
+			const char* y0			 = reinterpret_cast<const char*>(op->y + m0 * op->ldy);
+			sp.out[sp.n_out++]		 = nhb_span{ y0, y0 + (static_cast<size_t>(mt - 1) * op->ldy + op->w->N) * sizeof(float), 0 };
 		}
 	}
 
@@ -379,83 +377,26 @@ namespace {
 
 namespace {
 
-	bool spans_overlap(const nhb_span& a, const nhb_span& b) {
-		return a.b < b.e && b.b < a.e;
-	}
-	bool in_symmetric(const nhb_ctx* ctx, const nhb_span& s) {
-		for (size_t i = 1; i < ctx->regions.size(); ++i) {// regions[0] holds the flags
-			const nhb_span r{ ctx->regions[i].local, ctx->regions[i].local + ctx->regions[i].bytes, 0 };
-			if (spans_overlap(r, s))
-				return true;
-		}
-		return false;
-	}
-	void note_span(std::vector<nhb_span>& v, const nhb_span& s) {
-		for (nhb_span& o: v)
-			if (o.b == s.b && o.e == s.e) {
-				o.seq = std::max(o.seq, s.seq);
-				return;
-			}
-		if (v.size() >= 4096)
-			v.erase(v.begin());// the oldest entry: long confirmed by the window unless nothing has been delivered since
-		v.push_back(s);
-	}
-	void drop_confirmed(std::vector<nhb_span>& v, unsigned long long target) {
-		v.erase(std::remove_if(v.begin(), v.end(), [target](const nhb_span& s) { return s.seq <= target; }), v.end());
-	}
 	// "any symmetric memory": stands for what happened before a capture began
 	const nhb_span ALL_MEMORY{ reinterpret_cast<const char*>(uintptr_t(1)), reinterpret_cast<const char*>(~uintptr_t(0)), 0 };
 
 }
 
 namespace nhb {
-	// A launch waits for the peers only as far as it must:
-	//   - it reads rows a fused launch delivers: until every peer has announced that launch;
-	//   - it delivers into rows an earlier launch of this context read: until every peer has announced the first delivering
-	//     launch enqueued after that reader (the peers' copies of those rows are then no longer being read).  If there is no
-	//     such launch yet, the best it can ask for is the latest one;
-	//   - every second delivering launch: until every peer is within `peer_window` delivering launches of this rank, which
-	//     bounds how far ranks drift apart (peer_window + 1) and with it what readers this library does not know of (other
-	//     kernels on the stream) may assume.
-	// Everything else proceeds while the exchange is still in flight.  What the wait confirms is forgotten.
+	// What a warp-per-row launch waits for in its prologue (deliveries.h: plan_wait), and the record of what it reads and delivers
 	void plan_peer_wait(nhb_ctx* ctx, push_ctl& pc, const nhb_span* in, int n_in, const nhb_span* out, int n_out, bool delivers) {
 		setup_peer_wait(ctx, pc);
 		pc.wait_lag = 0;
 		if (pc.wait_world <= 1)
 			return;
-		nhb_deliveries& d		= ctx->dl;
-		unsigned long long need = 0;
-		for (int i = 0; i < n_in; ++i) {
-			if (!in_symmetric(ctx, in[i]))
-				continue;
-			for (const nhb_span& p: d.pending)
-				if (spans_overlap(p, in[i]))
-					need = std::max(need, p.seq);
-		}
-		if (delivers)
-			for (int i = 0; i < n_out; ++i)
-				for (const nhb_span& r: d.reads)
-					if (spans_overlap(r, out[i]))
-						need = std::max(need, std::min(r.seq, d.seq));
-		// the window is checked by every second delivering launch (by all of them when it is 0: lock step); launches that
-		// deliver nothing cannot run away from the peers on their own
-		const unsigned long long window = static_cast<unsigned long long>(ctx->peer_window < 0 ? 0 : ctx->peer_window);
-		const bool check_window			= window == 0 || (delivers && (d.seq & 1) == 0);
-		const unsigned long long target = std::max(need, check_window && d.seq > window ? d.seq - window : 0ull);
-		if (target == 0)
-			pc.wait_world = 0;// nothing has been delivered that this launch could depend on
+		std::vector<nhb_span> regions;
+		for (size_t i = 1; i < ctx->regions.size(); ++i)// regions[0] holds the flags
+			regions.push_back(nhb_span{ ctx->regions[i].local, ctx->regions[i].local + ctx->regions[i].bytes, 0 });
+		const wait_plan plan = plan_wait(ctx->dl, ctx->peer_window, regions.data(), static_cast<int>(regions.size()), in, n_in, out, n_out, delivers);
+		if (plan.wait)
+			pc.wait_lag = plan.lag;
 		else
-			pc.wait_lag = static_cast<int>(d.seq - target);
-		drop_confirmed(d.pending, target);
-		drop_confirmed(d.reads, target);
-		for (int i = 0; i < n_in; ++i)
-			if (in_symmetric(ctx, in[i]))
-				note_span(d.reads, nhb_span{ in[i].b, in[i].e, d.seq + 1 });
-		if (delivers) {
-			++d.seq;
-			for (int i = 0; i < n_out; ++i)
-				note_span(d.pending, nhb_span{ out[i].b, out[i].e, d.seq });
-		}
+			pc.wait_world = 0;// nothing has been delivered that this launch could depend on
 	}
 
 	// Rows delivered by a fused launch are whole on this rank only after the other ranks' announcements have arrived.  The
@@ -472,8 +413,7 @@ namespace nhb {
 		if (e != cudaSuccess)
 			return fail_cuda(ctx, e, "peer-wait launch");
 		ctx->launches += launches;
-		ctx->dl.pending.clear();
-		drop_confirmed(ctx->dl.reads, ctx->dl.seq);
+		plan_wait_all(ctx->dl);
 		return NHB_OK;
 	}
 }

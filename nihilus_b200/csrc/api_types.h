@@ -4,24 +4,10 @@
 #include <string>
 #include <vector>
 
+#include "deliveries.h"
 #include "internal.h"
 
 typedef struct ncclComm* ncclComm_t;
-
-// Bookkeeping of the fused all-gather's deliveries, in enqueue order on one context.  Every rank enqueues the same
-// sequence of delivering launches, so "delivering launch number n" names the same launch everywhere, and a rank's
-// announcement counter reaching n means its rows of launches 1..n have landed and everything it enqueued before its
-// launch n has run.
-struct nhb_span {
-	const char* b = nullptr;
-	const char* e = nullptr;
-	unsigned long long seq = 0;
-};
-struct nhb_deliveries {
-	unsigned long long seq = 0;// delivering launches enqueued so far
-	std::vector<nhb_span> pending;// rows the peers deliver with launch `seq`: whole here once every peer has announced `seq`
-	std::vector<nhb_span> reads;// symmetric rows read by a launch enqueued before delivering launch `seq`: the peers' copies may be rewritten once they have announced `seq`
-};
 
 struct nhb_ctx {
 	int device		   = 0;
@@ -150,7 +136,7 @@ namespace nhb {
 	// in front of work that reads rows another rank may still be delivering: a one-warp kernel that waits for the peers
 	int wait_pending(nhb_ctx* ctx);
 	// Decides what a warp-per-row launch waits for in its prologue and records what it reads and delivers.
-	// in / out: the byte ranges it reads (activations, residual) and, when `delivers`, the rows it completes on every rank.
+	// in / out: the byte ranges it reads (activations, residual) and writes; `delivers`: the rows in `out` are completed on every rank.
 	void plan_peer_wait(nhb_ctx* ctx, nhb::push_ctl& pc, const nhb_span* in, int n_in, const nhb_span* out, int n_out, bool delivers);
 
 }

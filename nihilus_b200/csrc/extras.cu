@@ -211,3 +211,54 @@ int nhb_weight_load(nhb_ctx* ctx, const char* path, int64_t N, int64_t K, nhb_we
 	return NHB_OK;
 }
 }
+
+// ---- the wait planner on its own (host only): the decisions of the fused all-gather for a sequence of launches, so that
+//      they can be checked on a machine without a GPU ----
+struct nhb_wait_planner {
+	nhb_deliveries d;
+	std::vector<nhb_span> regions;
+	int window = 4;
+};
+
+extern "C" {
+
+nhb_wait_planner* nhb_wait_planner_create(int peer_window) {
+	nhb_wait_planner* p = new nhb_wait_planner();
+	p->window			= peer_window < 0 ? 0 : peer_window;
+	return p;
+}
+
+void nhb_wait_planner_destroy(nhb_wait_planner* p) {
+	delete p;
+}
+
+int nhb_wait_planner_add_region(nhb_wait_planner* p, const void* base, size_t bytes) {
+	if (!p || !base || bytes == 0)
+		return NHB_ERR_ARG;
+	p->regions.push_back(nhb_span{ static_cast<const char*>(base), static_cast<const char*>(base) + bytes, 0 });
+	return NHB_OK;
+}
+
+int nhb_wait_planner_launch(nhb_wait_planner* p, const void* const* in, const size_t* in_bytes, int n_in, const void* const* out, const size_t* out_bytes, int n_out,
+	int delivers, int* waits, int* lag) {
+	if (!p || n_in < 0 || n_out < 0 || (n_in > 0 && (!in || !in_bytes)) || (n_out > 0 && (!out || !out_bytes)) || !waits || !lag)
+		return NHB_ERR_ARG;
+	std::vector<nhb_span> si, so;
+	for (int i = 0; i < n_in; ++i)
+		si.push_back(nhb_span{ static_cast<const char*>(in[i]), static_cast<const char*>(in[i]) + in_bytes[i], 0 });
+	for (int i = 0; i < n_out; ++i)
+		so.push_back(nhb_span{ static_cast<const char*>(out[i]), static_cast<const char*>(out[i]) + out_bytes[i], 0 });
+	const nhb::wait_plan plan = nhb::plan_wait(p->d, p->window, p->regions.data(), static_cast<int>(p->regions.size()), si.data(), n_in, so.data(), n_out, delivers != 0);
+	*waits = plan.wait ? 1 : 0;
+	*lag   = plan.lag;
+	return NHB_OK;
+}
+
+int nhb_wait_planner_wait_all(nhb_wait_planner* p) {
+	return p && nhb::plan_wait_all(p->d) ? 1 : 0;
+}
+
+long long nhb_wait_planner_seq(const nhb_wait_planner* p) {
+	return p ? static_cast<long long>(p->d.seq) : 0;
+}
+}
