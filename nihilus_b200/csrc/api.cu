@@ -586,8 +586,15 @@ namespace {
 		const int rows		= static_cast<int>(w->n1 - w->n0);
 		if (rows == 0)
 			return NHB_OK;
-		const size_t need = gemm_tc_scratch_bytes(w->K, op.M);
+		const size_t need = gemm_tc_scratch_bytes(w->K, op.M, rows, ctx->sm_count);
 		int rc			  = ensure(ctx, &ctx->scratch, &ctx->scratch_cap, need, "GEMM scratch");
+		if (rc == NHB_OK && !ctx->gemm_counters) {
+			// the arrival counters of split tiles: zero now, and zero again after every launch that used them
+			if (ctx->capturing)
+				return fail(ctx, NHB_ERR_UNSUPPORTED, "the GEMM's counters must exist before graph capture; run the GEMM once first");
+			NHB_CUDA(ctx, cudaMalloc(&ctx->gemm_counters, gemm_tc_counter_bytes()));
+			NHB_CUDA(ctx, cudaMemsetAsync(ctx->gemm_counters, 0, gemm_tc_counter_bytes(), ctx->stream));
+		}
 		if (rc == NHB_OK)
 			rc = wait_pending(ctx);
 		if (rc != NHB_OK)
@@ -619,7 +626,7 @@ namespace {
 		}
 		std::string err;
 		cudaError_t e = launch_gemm_tc(w->w16, w->wdT, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
-			cfg_of(ctx), &launches, &err, same_input);
+			ctx->gemm_counters, cfg_of(ctx), &launches, &err, same_input);
 		ctx->launches += launches;
 		if (e != cudaSuccess)
 			return fail_cuda(ctx, e, err.empty() ? "gemm_q8_tc launch" : err.c_str());
@@ -798,6 +805,8 @@ int nhb_ctx_destroy(nhb_ctx* ctx) {
 
 	if (ctx->scratch)
 		cudaFree(ctx->scratch);
+	if (ctx->gemm_counters)
+		cudaFree(ctx->gemm_counters);
 	if (ctx->norm_buf)
 		cudaFree(ctx->norm_buf);
 	if (ctx->io)
@@ -893,6 +902,8 @@ static int sync_finish(nhb_ctx* ctx) {
 			cudaMemsetAsync(ctx->regions[0].local, 0, ctx->regions[0].bytes, ctx->stream);
 		}
 		ctx->dl = nhb_deliveries();
+		if (ctx->gemm_counters)
+			cudaMemsetAsync(ctx->gemm_counters, 0, gemm_tc_counter_bytes(), ctx->stream);// a GEMM that gave up may have left its tiles' counters half-way
 		cudaStreamSynchronize(ctx->stream);
 		if (code == DEV_BAD_INDEX)
 			return fail(ctx, NHB_ERR_ARG, "a token id outside the embedding table reached nhb_get_rows_q8_0; its output row was left untouched");

@@ -20,6 +20,7 @@ struct nhb_ctx {
 	int* host_status   = nullptr;// pinned
 	void* scratch	   = nullptr;
 	size_t scratch_cap = 0;
+	unsigned* gemm_counters = nullptr;// arrival counters of the GEMM's split tiles
 	void* io		   = nullptr;
 	size_t io_cap	   = 0;
 	ncclComm_t comm	   = nullptr;

@@ -46,6 +46,13 @@ namespace nhb {
 			return n_t >= 224 ? 12 : (n_t >= 208 ? 8 : (n_t >= 144 ? 12 : 16));
 		}
 		constexpr int GM_LDU = 2;// 8-column units fetched per TMEM load
+		// Up to 32 tokens (tiles of 16 or 32 columns) sum K in chunks of 16 slices = 1024 values: a chunk is accumulated from
+		// zero and the chunk totals are added in ascending order.  That order does not depend on how many CTAs share a tile, so
+		// a tile's chunks can be dealt to several CTAs (K = 4096 walked by one CTA is 128 Q8 blocks in series, about 30 us
+		// whatever the tile holds) and the result stays the same bits for every split, shard and GPU count.
+		constexpr int GM_CHUNK_SLICES	  = 16;
+		constexpr int GM_CHUNK_MAX_TOKENS = 32;
+		constexpr size_t GM_COUNTER_BYTES = 16 * 1024;// one counter per tile of a split launch (fewer tiles than SMs)
 
 		// ---- PTX: TMA, tcgen05 ----
 		__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -162,6 +169,12 @@ namespace nhb {
 			int K;
 			int swapped;// 0: lanes = weight rows, columns = tokens; 1: lanes = tokens, columns = weight rows
 			int stages;
+			// up to 32 tokens only (see GM_CHUNK_SLICES): K slices per CTA (a whole number of chunks), the scratch for
+			// the chunk totals [chunk][tile][128][N_T] and one arrival counter per tile
+			int chunked;// 1: at most 32 tokens
+			int kb_per_cta;
+			float* partial;
+			unsigned* counters;
 		};
 
 		struct gemm_head {
@@ -171,6 +184,7 @@ namespace nhb {
 			uint64_t tmem_empty[8];
 			uint32_t tmem_base;
 			int abort_flag;
+			int last_cta;// split tiles: this CTA was the last of its tile to deliver its chunk totals
 		};
 
 		constexpr int GM_HEAD_BYTES = 1024;
@@ -189,6 +203,11 @@ namespace nhb {
 		}
 		__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
 			asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+		}
+		__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+			uint64_t r;
+			asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+			return r;
 		}
 		__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
 			uint64_t r;
@@ -259,7 +278,13 @@ namespace nhb {
 			const int S		= p.stages;
 			const int lane0 = blockIdx.x * GM_ROWS;// first lane-side row of this tile
 			const int col0	= blockIdx.y * N_T;// first column-side row of this tile
-			const int n_kb	= p.K / GM_KSLICE;
+			constexpr bool CAN_CHUNK = N_T <= GM_CHUNK_MAX_TOKENS;
+			// chunked summation is a property of the token count alone (at most 32 tokens, which always sit on the columns), never
+			// of the tile a shard happens to get: p.chunked is the host's (M <= 32)
+			const bool chunked	 = CAN_CHUNK && p.chunked != 0;
+			const int n_kb_all	 = p.K / GM_KSLICE;
+			const int kb0		 = chunked ? static_cast<int>(blockIdx.z) * p.kb_per_cta : 0;// this CTA's first K slice
+			const int n_kb		 = chunked ? min(p.kb_per_cta, n_kb_all - kb0) : n_kb_all;
 
 			if (tid == 0) {
 				for (int s = 0; s < S; ++s) {
@@ -290,8 +315,8 @@ namespace nhb {
 					// ---------------- TMA producer ----------------
 					if (lane == 0) {
 						constexpr uint32_t tx = static_cast<uint32_t>(GM_A_BYTES + B_BYTES + 2 * SC_FLOATS * 4);
-						const float* rsrc	  = p.row_scale + lane0;
-						const float* csrc	  = p.col_scale + col0;
+						const float* rsrc	  = p.row_scale + lane0 + static_cast<size_t>(2 * kb0) * p.lanes_pad;
+						const float* csrc	  = p.col_scale + col0 + static_cast<size_t>(2 * kb0) * p.cols_pad;
 						const uint32_t full0  = smem_u32(&hd->full[0]);
 						const uint32_t empty0 = smem_u32(&hd->empty[0]);
 						int s				  = 0;
@@ -303,8 +328,8 @@ namespace nhb {
 							}
 							const uint32_t st = ring + static_cast<uint32_t>(s) * STAGE_BYTES;
 							mbar_expect_tx(&hd->full[s], tx);
-							tma_load_2d(st, &map_a, kb * GM_KSLICE, lane0, &hd->full[s]);
-							tma_load_2d(st + GM_A_BYTES, &map_b, kb * GM_KSLICE, col0, &hd->full[s]);
+							tma_load_2d(st, &map_a, (kb0 + kb) * GM_KSLICE, lane0, &hd->full[s]);
+							tma_load_2d(st + GM_A_BYTES, &map_b, (kb0 + kb) * GM_KSLICE, col0, &hd->full[s]);
 							const uint32_t sc = st + GM_A_BYTES + B_BYTES;
 #pragma unroll
 							for (int j = 0; j < 2; ++j) {
@@ -402,11 +427,19 @@ namespace nhb {
 				const uint32_t rs_off = static_cast<uint32_t>(GM_A_BYTES + B_BYTES + r0 * 4);
 				const uint32_t cs_off = static_cast<uint32_t>(GM_A_BYTES + B_BYTES + (GM_ROWS + col_off + 2 * t4) * 4);
 				uint64_t acc[4][MAXU > 0 ? MAXU : 1];
+				uint64_t tot[4][(CAN_CHUNK && MAXU > 0) ? MAXU : 1];// chunk totals added up (narrow tiles walked by one CTA)
 #pragma unroll
 				for (int j = 0; j < 4; ++j)
 #pragma unroll
-					for (int i = 0; i < MAXU; ++i)
+					for (int i = 0; i < MAXU; ++i) {
 						acc[j][i] = 0ull;
+						if constexpr (CAN_CHUNK)
+							tot[j][i] = 0ull;
+					}
+				// split tiles: where this thread's values sit inside a [128][N_T] tile of the scratch, and the tile's number
+				const size_t n_tiles  = static_cast<size_t>(gridDim.x) * gridDim.y;
+				const size_t tile_id  = static_cast<size_t>(blockIdx.x) * gridDim.y + blockIdx.y;
+				const bool split_tile = chunked && gridDim.z > 1;
 				const uint32_t full0	   = smem_u32(&hd->full[0]);
 				const uint32_t empty0	   = smem_u32(&hd->empty[0]);
 				const uint32_t tmem_full0  = smem_u32(&hd->tmem_full[0]);
@@ -414,7 +447,11 @@ namespace nhb {
 				bool ok		= true;
 				int s		= 0;
 				uint32_t ph = 0;
-				for (int kb = 0; kb < n_kb && ok; ++kb) {
+				// (two loops: the chunk boundary sits outside the loop over K slices, so that it is a branch taken once per chunk
+				// and not a set of predicated moves in every slice)
+				for (int kb = 0; kb < n_kb && ok;) {
+				const int k_end = chunked ? min(n_kb, kb + GM_CHUNK_SLICES) : n_kb;
+				for (; kb < k_end && ok; ++kb) {
 					// the scales of this K slice were written by the async proxy: acquire them
 					if (!mbar_wait_a(full0 + 8 * s, ph)) {
 						ok = false;
@@ -489,10 +526,83 @@ namespace nhb {
 						ph ^= 1;
 					}
 				}
-				if (!ok) {
+					if constexpr (CAN_CHUNK) {
+						if (chunked && ok) {
+							// a chunk is complete: its total joins the running sum, or goes to the scratch for the CTA that sums the tile
+							const size_t at = (static_cast<size_t>((kb0 + kb - 1) / GM_CHUNK_SLICES) * n_tiles + tile_id) * (GM_ROWS * N_T);
+#pragma unroll
+							for (int j = 0; j < 4; ++j)
+#pragma unroll
+								for (int un = 0; un < MAXU; ++un) {
+									if (un < my_units) {
+										if (split_tile)
+											*reinterpret_cast<uint64_t*>(p.partial + at + (r0 + 8 * j) * N_T + col_off + 8 * un + 2 * t4) = acc[j][un];
+										else
+											tot[j][un] = add2(tot[j][un], acc[j][un]);
+									}
+									acc[j][un] = 0ull;
+								}
+						}
+					}
+				}
+				const bool failed = !ok;
+				bool writer		  = true;// this CTA stores the tile
+				if constexpr (CAN_CHUNK) {
+					if (split_tile) {
+						// Every CTA of the tile has stored its chunk totals; the last one to arrive adds all chunks of the tile in
+						// ascending order.  All epilogue warps pass both barriers whatever happened before (no early exit).
+						__threadfence();
+						asm volatile("bar.sync 1, %0;" ::"n"(GM_EPI_WARPS * 32) : "memory");
+						if (tid == 128) {
+							const unsigned prev = atomicAdd(p.counters + tile_id, 1u);
+							const int last		= prev == gridDim.z - 1 ? 1 : 0;
+							if (last)
+								p.counters[tile_id] = 0u;// ready for the next launch
+							hd->last_cta = last;
+						}
+						asm volatile("bar.sync 1, %0;" ::"n"(GM_EPI_WARPS * 32) : "memory");
+						writer = *reinterpret_cast<volatile int*>(&hd->last_cta) != 0;
+						if (writer) {
+							__threadfence();
+							const int n_chunks = (n_kb_all + GM_CHUNK_SLICES - 1) / GM_CHUNK_SLICES;
+							constexpr int RB   = MAXU <= 1 ? 4 : 2;// chunks fetched together: the loads of a batch are all in flight before the first add
+							for (int c0 = 0; c0 < n_chunks; c0 += RB) {
+								float2 v[RB][4][MAXU > 0 ? MAXU : 1];
+#pragma unroll
+								for (int cc = 0; cc < RB; ++cc) {
+									const float* src = p.partial + (static_cast<size_t>(min(c0 + cc, n_chunks - 1)) * n_tiles + tile_id) * (GM_ROWS * N_T);
+#pragma unroll
+									for (int j = 0; j < 4; ++j)
+#pragma unroll
+										for (int un = 0; un < MAXU; ++un)
+											if (un < my_units)
+												v[cc][j][un] = __ldcg(reinterpret_cast<const float2*>(src + (r0 + 8 * j) * N_T + col_off + 8 * un + 2 * t4));
+								}
+#pragma unroll
+								for (int cc = 0; cc < RB; ++cc)
+									if (c0 + cc < n_chunks) {
+#pragma unroll
+										for (int j = 0; j < 4; ++j)
+#pragma unroll
+											for (int un = 0; un < MAXU; ++un)
+												if (un < my_units)
+													tot[j][un] = add2(tot[j][un], pack2(v[cc][j][un].x, v[cc][j][un].y));
+									}
+							}
+						}
+					}
+					if (chunked) {
+#pragma unroll
+						for (int j = 0; j < 4; ++j)
+#pragma unroll
+							for (int un = 0; un < MAXU; ++un)
+								acc[j][un] = tot[j][un];
+					}
+				}
+				if (failed) {
 					if (lane == 0)
 						atomicExch(dev_status, DEV_TIMEOUT_MMA);
-				} else {
+				} else if (writer) {
 #pragma unroll
 					for (int j = 0; j < 4; ++j) {
 						const int lr = lane0 + r0 + 8 * j;// lane-side row
@@ -636,7 +746,7 @@ namespace nhb {
 	gemm_plan gemm_tc_plan(int64_t rows, int64_t M, int sms) {
 		gemm_plan best{};
 		double best_cost = 1e300;
-		for (int swapped = 0; swapped < 2; ++swapped) {
+		for (int swapped = 0; swapped < (M <= GM_CHUNK_MAX_TOKENS ? 1 : 2); ++swapped) {// up to 32 tokens always sit on the columns
 			const int64_t lane_rows = swapped ? M : rows;
 			const int64_t col_rows	= swapped ? rows : M;
 			const int64_t lane_tiles = (lane_rows + GM_ROWS - 1) / GM_ROWS;
@@ -669,9 +779,37 @@ namespace nhb {
 		return round_up(static_cast<int>(n), 256) + 256;
 	}
 
-	// quantised activations: fp16 quants [M][K], then block-major scales [K/32][pad(M)]
-	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M) {
-		return static_cast<size_t>(((M * K * 2 + 255) & ~int64_t(255)) + (K / 32) * gemm_tc_pad(M) * 4);
+	// How a narrow tile's K chunks are dealt to CTAs: as many CTAs per tile as it takes to put about one CTA on every SM
+	// (never more than there are chunks).  Any answer gives the same bits; this one is about speed only.
+	static int gemm_tc_ctas_per_tile(const gemm_plan& plan, int K, int64_t M, int sms, int* kb_per_cta) {
+		const int n_kb	   = K / GM_KSLICE;
+		const int n_chunks = (n_kb + GM_CHUNK_SLICES - 1) / GM_CHUNK_SLICES;
+		const int tiles	   = plan.lane_tiles * plan.col_tiles;
+		const bool chunked = M <= GM_CHUNK_MAX_TOKENS;
+		int want		   = 1;
+		if (chunked && tiles < sms)
+			want = std::min(n_chunks, std::max(1, sms / tiles));
+		const int chunks_per_cta = (n_chunks + want - 1) / want;
+		*kb_per_cta				 = chunked ? chunks_per_cta * GM_CHUNK_SLICES : n_kb;
+		return chunked ? (n_chunks + chunks_per_cta - 1) / chunks_per_cta : 1;
+	}
+
+	// Scratch of the GEMM: the quantised activations (fp16 quants [M][K], block-major scales [K/32][pad(M)]) and, for split
+	// tiles, the chunk totals [chunk][tile][128][columns].  The arrival counters of split tiles live in a buffer of their own
+	// (gemm_tc_counter_bytes, zero between launches).
+	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M, int64_t rows, int sms) {
+		size_t n = static_cast<size_t>(((M * K * 2 + 255) & ~int64_t(255)) + (K / 32) * gemm_tc_pad(M) * 4);
+		n		 = (n + 255) & ~size_t(255);
+		const gemm_plan plan = gemm_tc_plan(rows, M, sms);
+		int kb_per_cta		 = 0;
+		if (gemm_tc_ctas_per_tile(plan, static_cast<int>(K), M, sms, &kb_per_cta) > 1) {
+			const size_t n_chunks = static_cast<size_t>((K / GM_KSLICE + GM_CHUNK_SLICES - 1) / GM_CHUNK_SLICES);
+			n += n_chunks * plan.lane_tiles * plan.col_tiles * GM_ROWS * plan.n_t * sizeof(float);
+		}
+		return n;
+	}
+	size_t gemm_tc_counter_bytes() {
+		return GM_COUNTER_BYTES;
 	}
 
 	// fp16 copy of the quants and block-major f32 copy of the scales, made once per weight
@@ -690,10 +828,13 @@ namespace nhb {
 	}
 
 	cudaError_t launch_gemm_tc(const __half* w16, const float* wdT, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
-		void* scratch, const launch_cfg& cfg, int* launches, std::string* err, bool activations_ready) {
-		const int m_pad = gemm_tc_pad(M);
-		__half* qa16	= static_cast<__half*>(scratch);
-		float* daT		= reinterpret_cast<float*>(static_cast<char*>(scratch) + ((static_cast<size_t>(M) * K * 2 + 255) & ~size_t(255)));
+		void* scratch, unsigned* counters, const launch_cfg& cfg, int* launches, std::string* err, bool activations_ready) {
+		const int m_pad	   = gemm_tc_pad(M);
+		char* const sbase  = static_cast<char*>(scratch);
+		__half* qa16	   = reinterpret_cast<__half*>(sbase);
+		float* daT		   = reinterpret_cast<float*>(sbase + ((static_cast<size_t>(M) * K * 2 + 255) & ~size_t(255)));
+		float* partial	   = reinterpret_cast<float*>(
+			sbase + ((((static_cast<size_t>(M) * K * 2 + 255) & ~size_t(255)) + static_cast<size_t>(K / 32) * m_pad * 4 + 255) & ~size_t(255)));
 		cudaLaunchAttribute attr[1];
 		attr[0].id										   = cudaLaunchAttributeProgrammaticStreamSerialization;
 		attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -741,6 +882,10 @@ namespace nhb {
 		p.col_rows	  = static_cast<int>(b_rows);
 		p.K			  = K;
 		p.swapped		  = plan.swapped;
+		p.partial		  = partial;
+		p.counters		  = counters;
+		p.chunked				= M <= GM_CHUNK_MAX_TOKENS ? 1 : 0;
+		const int ctas_per_tile = gemm_tc_ctas_per_tile(plan, K, M, cfg.sm_count, &p.kb_per_cta);
 		const int stage_b = gemm_stage_bytes(plan.n_t);
 		p.stages		  = std::min(8, (200 * 1024) / stage_b);
 		if (gemm_stage_cols(plan.n_t) <= 64 && p.stages >= 2)
@@ -781,7 +926,7 @@ namespace nhb {
 			return attr_err;
 		}
 		cudaLaunchConfig_t lc{};
-		lc.gridDim			= dim3(plan.lane_tiles, plan.col_tiles);
+		lc.gridDim			= dim3(plan.lane_tiles, plan.col_tiles, ctas_per_tile);
 		lc.blockDim			= dim3((4 + gemm_epi_warps(plan.n_t)) * 32);
 		lc.dynamicSmemBytes = smem;
 		lc.stream			= cfg.stream;

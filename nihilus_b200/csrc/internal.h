@@ -160,9 +160,10 @@ namespace nhb {
 	gemm_plan gemm_tc_plan(int64_t rows, int64_t M, int sms);
 	bool gemm_tc_supports(int64_t rows, int64_t K, int64_t M);
 	int gemm_tc_pad(int64_t n);
-	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M);
+	size_t gemm_tc_scratch_bytes(int64_t K, int64_t M, int64_t rows, int sms);
+	size_t gemm_tc_counter_bytes();
 	cudaError_t launch_weight_gemm_planes(const int8_t* q, const __half* d, int64_t rows, int64_t K, __half* w16, float* wdT, cudaStream_t s);
-	cudaError_t launch_gemm_tc(const __half* w16, const float* wdT, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M,
-		void* scratch, const launch_cfg& cfg, int* launches, std::string* err, bool activations_ready = false);
+	cudaError_t launch_gemm_tc(const __half* w16, const float* wdT, const float* x, long long ldx, float* y, long long ldy, int rows, int K, int M, void* scratch,
+		unsigned* counters, const launch_cfg& cfg, int* launches, std::string* err, bool activations_ready = false);
 
 }

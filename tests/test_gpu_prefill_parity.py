@@ -132,3 +132,41 @@ def test_wide_tile_row_shards_are_bit_identical_to_one_gpu(capi, ctx, N, K, M):
             hr.free()
             c.close()
         assert torch.equal(y, full), (world, widths)
+
+
+@pytest.mark.parametrize("K", [4096, 14336])
+@pytest.mark.parametrize("M", [9, 16, 32])
+def test_few_tokens_split_k_over_ctas_and_every_split_gives_the_same_bits(capi, ctx, oracle, K, M):
+    """Up to 32 tokens the GEMM sums K in chunks whose totals are added in ascending order, so that a tile's chunks can be
+    dealt to several CTAs when the weight has fewer tiles than the GPU has SMs.  An unsharded weight of 148 tiles is walked
+    by one CTA per tile; its 1/8 shards (19 tiles) by 4 to 7 CTAs per tile; the shards' rows carry the unsharded bits."""
+    import torch
+
+    from nihilus_b200 import synth
+    from oracle import pyoracle as po
+
+    N = 148 * 128
+    w = synth.make_weight(N, K, 4100 + K)
+    x = synth.make_activation(M, K, 4101 + M)
+    xd = torch.from_numpy(x).cuda()
+    h = ctx.upload(w)
+    full = torch.zeros((M, N), device="cuda")
+    ctx.mul_mat(h, xd, full, kernel=capi.KERNEL_GEMM_TC)
+    ctx.mul_mat(h, xd, full, kernel=capi.KERNEL_GEMM_TC)  # a second launch finds the arrival counters back at zero
+    ctx.sync()
+    h.free()
+    rows = slice(0, N, 7)
+    ref = oracle.mul_mat(po.Q8ACT_LANES, w[rows], x)
+    got = full.cpu().numpy()
+    assert float(np.abs(got[:, rows] - ref).max() / np.abs(ref).max()) <= TOL
+    y = torch.zeros((M, N), device="cuda")
+    for r in range(8):
+        c = capi.Context(0, r, 8)
+        c.use_torch_stream()
+        hr = c.upload(w)
+        for _ in range(2):
+            c.mul_mat(hr, xd, y, kernel=capi.KERNEL_GEMM_TC)
+        c.sync()
+        hr.free()
+        c.close()
+    assert torch.equal(y, full)
