@@ -4,11 +4,13 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One step = one token's worth of Q8_0 mul_mats: 32 layers x (q, k, v | o | gate, up | down) + lm_head =
-225 matrices in 129 dependent stages, 7.97 GB of Q8_0 weights streamed once.  The independent projections of a
-stage share one launch and one input vector (q/k/v read the same normalised row, gate/up likewise, as in the
-reference's graph: include/nihilus-incl/infra/core_traits.hpp:575-594, 976-980).  With N > 1 (torchrun, one rank per
-GPU) the larger weights are row-sharded over the ranks and every stage's output slices are delivered to all ranks
-before the next stage reads them.  Prints ONE JSON line (rank 0).  `--impl reference` times the reference's own CPU
+225 matrices in 129 stages (one launch each, in stream order), 7.97 GB of Q8_0 weights streamed once.  The independent
+projections of a stage share one launch and one input vector (q/k/v read the same normalised row, gate/up likewise, as in
+the reference's graph: include/nihilus-incl/infra/core_traits.hpp:575-594, 976-980); every stage reads its own synthetic
+N(0,1) vector.  With N > 1 (torchrun, one rank per GPU) the larger weights are row-sharded over the ranks and every
+stage's output slices are delivered to all ranks; the step ends with a wait for every delivery, launches in between wait
+for the other ranks only where they read delivered rows (none do here: `every_launch_waits_ms_per_step` is the same step
+with every launch waiting).  Prints ONE JSON line (rank 0).  `--impl reference` times the reference's own CPU
 row-dot code (oracle/_ref, built from the reference sources) on the host cores instead, on the same 225 matrices.
 """
 from __future__ import annotations
