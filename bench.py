@@ -574,6 +574,46 @@ def main():
         g0.free()
         ctx.set_option("peer_window", args.peer_window)
 
+    # ---- the step as the data flow of a decode step: every stage reads what the stage before it wrote (down -> q,k,v;
+    #      q -> attn_output; attn_output -> gate,up; gate -> down; the last down -> lm_head), so with N > 1 a stage waits for
+    #      the ranks that deliver its input.  Attention, SwiGLU, norms and residuals are left out: only the dependency is modelled ----
+    dependent_ms = None
+    if chain is not None and graph is not None:
+        dep_in, prev = [], None
+        for s, st in enumerate(stages):
+            names = [ops[j][0] for j in st]
+            if prev is None:
+                dep_in.append(xs[s])
+            elif names[0] in ("attn_q", "output"):
+                dep_in.append(ys[prev["down"]])
+            elif names[0] == "attn_output":
+                dep_in.append(ys[prev["q"]])
+            elif names[0] == "ffn_gate":
+                dep_in.append(ys[prev["o"]])
+            else:
+                dep_in.append(ys[prev["gate"]])
+            prev = dict(prev or {})
+            prev[{"attn_q": "q", "attn_output": "o", "ffn_gate": "gate", "ffn_down": "down"}.get(names[0], "x")] = st[0]
+        dchain = ctx.chain([[(weights[j], dep_in[s], ys[j]) for j in st] for s, st in enumerate(stages)])
+
+        def enqueue_dependent():
+            dchain.launch()
+            if world > 1:
+                ctx.all_gather_batch([ys[j] for j in stages[-1]])
+
+        enqueue_dependent()
+        ctx.sync()
+        ctx.graph_begin()
+        enqueue_dependent()
+        gd = ctx.graph_end()
+        for _ in range(5):
+            gd.launch()
+        ctx.sync()
+        nd = max(20, args.steps // 4)
+        dependent_ms = timed(gd.launch, nd) / nd
+        gd.free()
+        dchain.free()
+
     # ---- each stage type on its own: one launch per layer, recorded and replayed like the step ----
     stage_us = None
     if args.stage_times and act_mode == capi.ACT_Q8 and args.gather != "nccl":
@@ -689,6 +729,7 @@ def main():
                 "note": "per GPU: the bytes this rank streams under the placement policy; launch gaps inside the graph are included in the duration",
             },
             "every_launch_waits_ms_per_step": lockstep_ms,
+            "dependent_chain_ms_per_step": dependent_ms,
             "stage_us": stage_us,
             "parity": {"all_ranks_hold_the_same_outputs": all_equal, "bit_identical_to_one_gpu": one_gpu_equal},
             "prefill": prefill,
