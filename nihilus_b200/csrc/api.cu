@@ -599,14 +599,33 @@ namespace {
 			rc = wait_pending(ctx);
 		if (rc != NHB_OK)
 			return rc;
-		int launches = 0;
-		if (!w->w16) {
-			// the tensor cores take fp16 operands: keep an exact fp16 copy of the int8 plane (2 bytes per weight) and the
-			// scales as f32, block-major, so that a tile's scales of one block are contiguous
+		int launches		= 0;
+		const __half* w16	= w->w16;
+		const float* wdT	= w->wdT;
+		const size_t sb		= static_cast<size_t>(w->K / 32) * gemm_tc_pad(rows) * sizeof(float);
+		const size_t w16_b	= (static_cast<size_t>(rows) * w->K * sizeof(__half) + 255) & ~size_t(255);
+		if (!w->w16 && !ctx->gemm_keep_planes) {
+			// The tensor cores take fp16 operands.  Option "gemm_keep_planes" = 0: the fp16 copy of the quants and the
+			// block-major scales are rebuilt into one buffer of the context in front of every GEMM (2 bytes per weight of
+			// the largest weight instead of 2 bytes per weight of the whole model; 45 us more per GEMM of a 14336 x 4096 weight).
+			// Rows past the shard in the scale plane hold whatever was there: their outputs are never stored.
+			rc = ensure(ctx, &ctx->plane_buf, &ctx->plane_cap, w16_b + sb, "GEMM weight planes");
+			if (rc != NHB_OK)
+				return rc;
+			__half* p16 = static_cast<__half*>(ctx->plane_buf);
+			float* pdT	= reinterpret_cast<float*>(static_cast<char*>(ctx->plane_buf) + w16_b);
+			cudaError_t ew = launch_weight_gemm_planes(w->q, w->d, rows, w->K, p16, pdT, ctx->stream);
+			if (ew != cudaSuccess)
+				return fail_cuda(ctx, ew, "GEMM weight planes");
+			launches += 2;
+			w16 = p16;
+			wdT = pdT;
+		} else if (!w->w16) {
+			// keep an exact fp16 copy of the int8 plane (2 bytes per weight) and the scales as f32, block-major, so that a
+			// tile's scales of one block are contiguous
 			if (ctx->capturing)
 				return fail(ctx, NHB_ERR_UNSUPPORTED, "the weight's GEMM planes must exist before graph capture; run the GEMM once first");
 			nhb_weight* wm = const_cast<nhb_weight*>(w);
-			const size_t sb = static_cast<size_t>(w->K / 32) * gemm_tc_pad(rows) * sizeof(float);
 			NHB_CUDA(ctx, cudaMalloc(&wm->w16, static_cast<size_t>(rows) * w->K * sizeof(__half)));
 			cudaError_t ew = cudaMalloc(&wm->wdT, sb);
 			if (ew == cudaSuccess)
@@ -623,9 +642,11 @@ namespace {
 			}
 			NHB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));// a programmatic-dependent launch after it must not overtake it
 			launches += 2;
+			w16 = wm->w16;
+			wdT = wm->wdT;
 		}
 		std::string err;
-		cudaError_t e = launch_gemm_tc(w->w16, w->wdT, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
+		cudaError_t e = launch_gemm_tc(w16, wdT, op.x, op.ldx, op.y + w->n0, op.ldy, rows, static_cast<int>(w->K), static_cast<int>(op.M), ctx->scratch,
 			ctx->gemm_counters, cfg_of(ctx), &launches, &err, same_input);
 		ctx->launches += launches;
 		if (e != cudaSuccess)
@@ -807,6 +828,8 @@ int nhb_ctx_destroy(nhb_ctx* ctx) {
 		cudaFree(ctx->scratch);
 	if (ctx->gemm_counters)
 		cudaFree(ctx->gemm_counters);
+	if (ctx->plane_buf)
+		cudaFree(ctx->plane_buf);
 	if (ctx->norm_buf)
 		cudaFree(ctx->norm_buf);
 	if (ctx->io)
@@ -848,6 +871,8 @@ int nhb_ctx_set_option(nhb_ctx* ctx, const char* name, int value) {
 		ctx->rows_cps = value < 1 ? 1 : (value > 8 ? 8 : value);
 	else if (!std::strcmp(name, "prequantize"))
 		ctx->preq = value != 0;
+	else if (!std::strcmp(name, "gemm_keep_planes"))
+		ctx->gemm_keep_planes = value != 0;
 	else if (!std::strcmp(name, "peer_window"))
 		ctx->peer_window = value < 0 ? 0 : value;
 	else if (!std::strcmp(name, "rows_double_buffer"))

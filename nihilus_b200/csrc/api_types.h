@@ -21,6 +21,9 @@ struct nhb_ctx {
 	void* scratch	   = nullptr;
 	size_t scratch_cap = 0;
 	unsigned* gemm_counters = nullptr;// arrival counters of the GEMM's split tiles
+	bool gemm_keep_planes	= true;// false: a weight's fp16 operand planes are rebuilt before every GEMM instead of kept with the weight
+	void* plane_buf			= nullptr;
+	size_t plane_cap		= 0;
 	void* io		   = nullptr;
 	size_t io_cap	   = 0;
 	ncclComm_t comm	   = nullptr;

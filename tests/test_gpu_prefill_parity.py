@@ -170,3 +170,30 @@ def test_few_tokens_split_k_over_ctas_and_every_split_gives_the_same_bits(capi, 
         hr.free()
         c.close()
     assert torch.equal(y, full)
+
+
+def test_operand_planes_rebuilt_per_call_give_the_same_bits_as_kept_ones(capi, oracle):
+    """Option gemm_keep_planes = 0: no fp16 copy stays with the weight; q, k, v sharing one input still quantise it once."""
+    import torch
+
+    from nihilus_b200 import synth
+
+    M, K = 200, 4096
+    ws = [synth.make_weight(n, K, 4200 + n) for n in (4096, 1024, 1031)]
+    xd = torch.from_numpy(synth.make_activation(M, K, 4203)).cuda()
+    outs = []
+    for keep in (1, 0):
+        c = capi.Context(0)
+        c.use_torch_stream()
+        c.set_option("gemm_keep_planes", keep)
+        hs = [c.upload(w) for w in ws]
+        ys = [torch.zeros((M, h.N), device="cuda") for h in hs]
+        for _ in range(2):
+            c.mul_mat_batch([(h, xd, y) for h, y in zip(hs, ys)], kernel=capi.KERNEL_GEMM_TC)
+        c.sync()
+        outs.append([y.clone() for y in ys])
+        for h in hs:
+            h.free()
+        c.close()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
