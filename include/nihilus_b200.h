@@ -142,7 +142,8 @@ int nhb_weight_info_get(const nhb_weight* w, nhb_weight_info* info);
 /* planes back to 34-byte blocks on the host (rows n0..n1 only) -- for round-trip checks */
 int nhb_weight_download_q8_0(nhb_ctx* ctx, const nhb_weight* w, void* host_blocks34_shard);
 
-/* ---- the operator: fills the empty GPU cores of cuda/cuda_12.hpp:803-952; arithmetic of cpu/avx_2.hpp:4749-5004 ---- */
+/* ---- the operator: fills the empty GPU cores of cuda/cuda_12.hpp:803-952; arithmetic of cpu/avx_2.hpp:4749-5004 ----
+ * X and Y must not overlap (NHB_ERR_ARG). */
 int nhb_mul_mat(nhb_ctx* ctx, const nhb_weight* w, const float* x_dev, int64_t ldx, float* y_dev, int64_t ldy, int64_t M, int act_mode,
 	int kernel);
 /* several independent mul_mats (q/k/v of one layer, gate/up of one layer ...) in one persistent launch */
@@ -357,6 +358,11 @@ int nhb_wait_planner_launch(nhb_wait_planner* p, const void* const* in, const si
 	int n_out, int delivers, int* waits, int* lag);
 int nhb_wait_planner_wait_all(nhb_wait_planner* p);
 long long nhb_wait_planner_seq(const nhb_wait_planner* p);
+/* what nhb_graph_begin / nhb_graph_end / nhb_graph_launch do to the bookkeeping: the launches planned between begin and end keep
+ * their answers for every replay; _capture_end returns the recording's number, _replayed accounts for one replay of it */
+void nhb_wait_planner_capture_begin(nhb_wait_planner* p);
+int nhb_wait_planner_capture_end(nhb_wait_planner* p);
+int nhb_wait_planner_replayed(nhb_wait_planner* p, int recording);
 /* complete Y[M][N] (ldy) on every rank from the column slices each rank wrote */
 int nhb_all_gather(nhb_ctx* ctx, float* y_dev, int64_t ldy, int64_t M, int64_t N);
 /* several outputs in one grouped collective (q/k/v, gate/up) */

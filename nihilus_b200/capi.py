@@ -36,7 +36,8 @@ EXPORTS = (
     "nhb_mul_mat_batch", "nhb_mul_mat_host", "nhb_mul_mat_block_dots", "nhb_quantize_q8_0", "nhb_graph_begin", "nhb_graph_end",
     "nhb_graph_launch", "nhb_graph_free", "nhb_comm_unique_id", "nhb_comm_init", "nhb_all_gather", "nhb_all_gather_batch",
     "nhb_mul_mat_q8_0_noalloc", "nhb_noalloc_max_bytes", "nhb_noalloc_last_error", "nhb_device_alloc", "nhb_device_free", "nhb_symm_alloc", "nhb_symm_free", "nhb_symm_alloc_local", "nhb_all_gather_local", "nhb_sync_all", "nhb_wait_planner_create", "nhb_wait_planner_destroy", "nhb_wait_planner_add_region",
-    "nhb_wait_planner_launch", "nhb_wait_planner_wait_all", "nhb_wait_planner_seq", "nhb_place_rows", "nhb_gemm_tile_plan",
+    "nhb_wait_planner_launch", "nhb_wait_planner_wait_all", "nhb_wait_planner_seq", "nhb_wait_planner_capture_begin", "nhb_wait_planner_capture_end",
+    "nhb_wait_planner_replayed", "nhb_place_rows", "nhb_gemm_tile_plan",
     "nhb_rms_norm_mul", "nhb_rms_norm_mul_q8_0", "nhb_rms_norm_mul_mat_batch",
     "nhb_gguf_open", "nhb_gguf_last_error", "nhb_gguf_close", "nhb_gguf_tensor_count", "nhb_gguf_find", "nhb_gguf_tensor_get",
     "nhb_gguf_get_number", "nhb_gguf_get_string", "nhb_gguf_upload_q8_0", "nhb_gguf_read_f32",
@@ -112,6 +113,9 @@ _sig("nhb_wait_planner_add_region", _i, _vp, _vp, C.c_size_t)
 _sig("nhb_wait_planner_launch", _i, _vp, C.POINTER(_vp), C.POINTER(C.c_size_t), _i, C.POINTER(_vp), C.POINTER(C.c_size_t), _i, _i, C.POINTER(_i), C.POINTER(_i))
 _sig("nhb_wait_planner_wait_all", _i, _vp)
 _sig("nhb_wait_planner_seq", C.c_longlong, _vp)
+_sig("nhb_wait_planner_capture_begin", None, _vp)
+_sig("nhb_wait_planner_capture_end", _i, _vp)
+_sig("nhb_wait_planner_replayed", _i, _vp, _i)
 _sig("nhb_symm_free", _i, _vp, _vp)
 _sig("nhb_weight_upload_q8_0", _i, _vp, _vp, _i64, _i64, C.POINTER(_vp))
 _sig("nhb_weight_free", _i, _vp, _vp)
@@ -620,6 +624,15 @@ class WaitPlanner:
 
     def wait_all(self) -> bool:
         return bool(lib.nhb_wait_planner_wait_all(self.handle))
+
+    def capture_begin(self):
+        lib.nhb_wait_planner_capture_begin(self.handle)
+
+    def capture_end(self) -> int:
+        return int(lib.nhb_wait_planner_capture_end(self.handle))
+
+    def replayed(self, recording: int):
+        _check(lib.nhb_wait_planner_replayed(self.handle, recording))
 
     @property
     def seq(self) -> int:

@@ -148,6 +148,16 @@ namespace {
 			return fail(ctx, NHB_ERR_ARG, "activations must be 16-byte aligned with ldx a multiple of 4");
 		if (M > (int64_t(1) << 20))
 			return fail(ctx, NHB_ERR_ARG, "M too large");
+		if (y && w->N > 0) {
+			// y = W x is never computed in place: rows of y are stored while other rows of x are still being read (and, with
+			// several GPUs, delivered into the peers' copies while they still read theirs)
+			const char* x0 = reinterpret_cast<const char*>(x);
+			const char* x1 = reinterpret_cast<const char*>(x + (M - 1) * ldx + w->K);
+			const char* y0 = reinterpret_cast<const char*>(y);
+			const char* y1 = reinterpret_cast<const char*>(y + (M - 1) * ldy + w->N);
+			if (x0 < y1 && y0 < x1)
+				return fail(ctx, NHB_ERR_ARG, "activations and outputs overlap");
+		}
 		return NHB_OK;
 	}
 
@@ -377,8 +387,6 @@ namespace {
 
 namespace {
 
-	// "any symmetric memory": stands for what happened before a capture began
-	const nhb_span ALL_MEMORY{ reinterpret_cast<const char*>(uintptr_t(1)), reinterpret_cast<const char*>(~uintptr_t(0)), 0 };
 
 }
 
@@ -1619,13 +1627,8 @@ int nhb_graph_begin(nhb_ctx* ctx) {
 	device_guard g(ctx->device);
 	NHB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
 	ctx->capturing = true;
-	// A replay may follow anything: the recorded launches must take every earlier delivery for unconfirmed and every
-	// symmetric row for just read, whatever the bookkeeping says at this moment.
-	ctx->cap_seq0 = ctx->dl.seq;
-	if (ctx->world > 1 && ctx->dl.seq > 0) {
-		note_span(ctx->dl.pending, nhb_span{ ALL_MEMORY.b, ALL_MEMORY.e, ctx->dl.seq });
-		note_span(ctx->dl.reads, nhb_span{ ALL_MEMORY.b, ALL_MEMORY.e, ctx->dl.seq });
-	}
+	// a replay may follow anything (deliveries.h: capture_begin)
+	ctx->cap_seq0 = ctx->world > 1 ? capture_begin(ctx->dl) : ctx->dl.seq;
 	return NHB_OK;
 }
 
@@ -1646,14 +1649,7 @@ int nhb_graph_end(nhb_ctx* ctx, nhb_graph** out) {
 		delete gr;
 		return fail_cuda(ctx, e, "graph capture");
 	}
-	// what a replay leaves behind, relative to where it starts
-	gr->n_deliver = ctx->dl.seq - ctx->cap_seq0;
-	for (const nhb_span& p: ctx->dl.pending)
-		if (p.seq > ctx->cap_seq0)
-			gr->pending.push_back(nhb_span{ p.b, p.e, p.seq - ctx->cap_seq0 });
-	for (const nhb_span& r: ctx->dl.reads)
-		if (r.seq > ctx->cap_seq0)
-			gr->reads.push_back(nhb_span{ r.b, r.e, r.seq - ctx->cap_seq0 });
+	gr->replay = capture_end(ctx->dl, ctx->cap_seq0);// what a replay leaves behind, relative to where it starts
 	*out = gr;
 	return NHB_OK;
 }
@@ -1663,12 +1659,7 @@ int nhb_graph_launch(nhb_ctx* ctx, nhb_graph* gr) {
 		return fail(ctx, NHB_ERR_ARG, "nhb_graph_launch: null argument");
 	device_guard g(ctx->device);
 	NHB_CUDA(ctx, cudaGraphLaunch(gr->exec, ctx->stream));
-	const unsigned long long base = ctx->dl.seq;
-	ctx->dl.seq += gr->n_deliver;
-	for (const nhb_span& p: gr->pending)
-		note_span(ctx->dl.pending, nhb_span{ p.b, p.e, base + p.seq });
-	for (const nhb_span& r: gr->reads)
-		note_span(ctx->dl.reads, nhb_span{ r.b, r.e, base + r.seq });
+	replayed(ctx->dl, gr->replay);
 	return NHB_OK;
 }
 

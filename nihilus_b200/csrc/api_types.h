@@ -98,9 +98,7 @@ struct nhb_chain {
 struct nhb_graph {
 	cudaGraph_t graph	 = nullptr;
 	cudaGraphExec_t exec = nullptr;
-	// what one replay adds to the context's delivery bookkeeping (sequence numbers relative to the replay's start)
-	unsigned long long n_deliver = 0;
-	std::vector<nhb_span> pending, reads;
+	nhb::replay_record replay;// what one replay adds to the context's delivery bookkeeping
 };
 
 namespace nhb {

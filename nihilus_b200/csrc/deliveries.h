@@ -110,6 +110,44 @@ namespace nhb {
 		return plan;
 	}
 
+	// ---- recorded launch sequences (CUDA graphs) ----
+	// The lag of a recorded launch is frozen, and a replay may follow any history.  So a capture begins by assuming that
+	// every earlier delivery is unconfirmed and every symmetric row was just read (the first recorded launches then wait for
+	// "everything before the graph"), and what one replay leaves behind is kept relative to where the replay starts.
+	struct replay_record {
+		unsigned long long n_deliver = 0;// delivering launches in the recording
+		std::vector<nhb_span> pending, reads;// left unconfirmed at its end, seq relative to its start
+	};
+	inline nhb_span all_memory(unsigned long long seq) {
+		return nhb_span{ reinterpret_cast<const char*>(uintptr_t(1)), reinterpret_cast<const char*>(~uintptr_t(0)), seq };
+	}
+	inline unsigned long long capture_begin(nhb_deliveries& d) {
+		if (d.seq > 0) {
+			note_span(d.pending, all_memory(d.seq));
+			note_span(d.reads, all_memory(d.seq));
+		}
+		return d.seq;
+	}
+	inline replay_record capture_end(const nhb_deliveries& d, unsigned long long seq0) {
+		replay_record r;
+		r.n_deliver = d.seq - seq0;
+		for (const nhb_span& p: d.pending)
+			if (p.seq > seq0)
+				r.pending.push_back(nhb_span{ p.b, p.e, p.seq - seq0 });
+		for (const nhb_span& x: d.reads)
+			if (x.seq > seq0)
+				r.reads.push_back(nhb_span{ x.b, x.e, x.seq - seq0 });
+		return r;
+	}
+	inline void replayed(nhb_deliveries& d, const replay_record& r) {
+		const unsigned long long base = d.seq;
+		d.seq += r.n_deliver;
+		for (const nhb_span& p: r.pending)
+			note_span(d.pending, nhb_span{ p.b, p.e, base + p.seq });
+		for (const nhb_span& x: r.reads)
+			note_span(d.reads, nhb_span{ x.b, x.e, base + x.seq });
+	}
+
 	// a wait for everything delivered so far (nhb_sync, nhb_all_gather*, in front of kernels that do not wait themselves)
 	inline bool plan_wait_all(nhb_deliveries& d) {
 		if (d.pending.empty())

@@ -218,6 +218,8 @@ struct nhb_wait_planner {
 	nhb_deliveries d;
 	std::vector<nhb_span> regions;
 	int window = 4;
+	unsigned long long cap_seq0 = 0;
+	std::vector<nhb::replay_record> recordings;
 };
 
 extern "C" {
@@ -260,5 +262,24 @@ int nhb_wait_planner_wait_all(nhb_wait_planner* p) {
 
 long long nhb_wait_planner_seq(const nhb_wait_planner* p) {
 	return p ? static_cast<long long>(p->d.seq) : 0;
+}
+
+void nhb_wait_planner_capture_begin(nhb_wait_planner* p) {
+	if (p)
+		p->cap_seq0 = nhb::capture_begin(p->d);
+}
+
+int nhb_wait_planner_capture_end(nhb_wait_planner* p) {
+	if (!p)
+		return -1;
+	p->recordings.push_back(nhb::capture_end(p->d, p->cap_seq0));
+	return static_cast<int>(p->recordings.size()) - 1;
+}
+
+int nhb_wait_planner_replayed(nhb_wait_planner* p, int recording) {
+	if (!p || recording < 0 || recording >= static_cast<int>(p->recordings.size()))
+		return NHB_ERR_ARG;
+	nhb::replayed(p->d, p->recordings[static_cast<size_t>(recording)]);
+	return NHB_OK;
 }
 }

@@ -243,6 +243,7 @@ def test_empty_inputs_and_argument_errors(capi, ctx, torch_mod):
     assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, 1, 9, 0) == capi.ERR_ARG  # mode
     assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr() + 4, 64, yb.data_ptr(), 16, 1, 0, 0) == capi.ERR_ARG  # misaligned
     assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, 1, 0, 99) == capi.ERR_ARG  # kernel id
+    assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, x.data_ptr() + 128, 16, 1, 0, 0) == capi.ERR_ARG  # y inside x
     assert lib.nhb_mul_mat(ctx.handle, h.handle, x.data_ptr(), 64, yb.data_ptr(), 16, 1, 0, capi.KERNEL_GEMV_STREAM) == capi.ERR_UNSUPPORTED
     assert "K" in capi.last_error(ctx.handle)
     import ctypes as C

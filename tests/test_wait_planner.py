@@ -218,3 +218,53 @@ def test_the_model_catches_a_missing_wait(capi):
     p.steps = broken
     assert any(replay(p, 2, seed) is not None for seed in range(20))
     p.close()
+
+
+def _record(p, body):
+    """Plans `body` (a list of (reads, writes, delivers) or "sync") between capture_begin and capture_end; returns the recording's
+    number and the planned steps, whose answers are frozen."""
+    p.planner.capture_begin()
+    first = len(p.steps)
+    for item in body:
+        if item == "sync":
+            p.sync()
+        else:
+            p.launch(*item)
+    return p.planner.capture_end(), p.steps[first:]
+
+
+@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("window", [0, 4])
+def test_a_recorded_step_replayed_after_any_history(capi, world, window):
+    """What nhb_graph_begin / _end / _launch do: the recorded launches keep the waits they were planned with, whatever ran
+    before a replay -- eager launches that deliver into the recording's buffers, other recordings, nothing at all."""
+    for trial in range(12):
+        rng = random.Random(4000 + trial)
+        nb = 6
+        p = Prog(capi, nb, window)
+        # some history before the first capture, ending with a delivering launch that nobody has waited for
+        p.launch([], [0], True)
+        p.launch([0], [1], True)
+        # recording A: a dependent chain that rewrites buffers 0..2; recording B: reads A's results, delivers into 3..5
+        rec_a, steps_a = _record(p, [([], [0], True), ([0], [1], True), ([1], [2], True), ([2], [0], True)])
+        rec_b, steps_b = _record(p, [([0], [3], True), ([3, 1], [4], False), ([], [5], True), ([5], [3], True), "sync"])
+        for _ in range(10):
+            kind = rng.choice(["a", "b", "eager", "sync"])
+            if kind == "a":
+                p.steps.extend(steps_a)
+                p.planner.replayed(rec_a)
+            elif kind == "b":
+                p.steps.extend(steps_b)
+                p.planner.replayed(rec_b)
+            elif kind == "eager":
+                # (a launch that delivers nothing is followed by a delivering one before anything it touched is delivered into)
+                w = rng.randrange(3, nb)
+                p.launch([rng.choice([b for b in range(nb) if b != w])], [w], True)  # (a mul_mat never reads what it writes)
+                p.launch([rng.randrange(5)], [5], True)
+            else:
+                p.sync()
+        p.sync()
+        for seed in range(10):
+            err = replay(p, world, seed)
+            assert err is None, (trial, seed, err)
+        p.close()
