@@ -327,8 +327,9 @@ int nhb_comm_init(nhb_ctx* ctx, const void* id128);
  * host after their nhb_sync.  "peer_window" = 0 makes every launch wait for every earlier delivery (ranks in lock step).
  *
  * Every wait is bounded by option "peer_wait_us" (default 2 000 000): a peer that never shows up ends it, the kernel
- * carries on and finishes, and nhb_sync returns NHB_ERR_TIMEOUT and resets the exchange (all ranks must then sync
- * before they continue).  Option "fused_gather" = 0 keeps NCCL. */
+ * carries on and finishes, and nhb_sync returns NHB_ERR_TIMEOUT and resets this rank's side of the exchange (every rank
+ * must then pass an nhb_sync, and the ranks must meet on the host, before the next delivering launch).  Option
+ * "fused_gather" = 0 keeps NCCL. */
 int nhb_symm_alloc(nhb_ctx* ctx, size_t bytes, void** out_dev);
 int nhb_symm_free(nhb_ctx* ctx, void* dev);
 /* The same for ONE process that drives several GPUs from one thread, as the reference's host does (one process, one
